@@ -1,0 +1,139 @@
+/* rptc_b200 — C ABI of the B200 (sm_100a) RPTC decode / fused dequant-matmul library.
+ *
+ * Every entry point takes plain device pointers and sizes, runs on the CUDA stream it is given
+ * (0 = the legacy default stream), allocates nothing unless it says so, never creates streams,
+ * never exits or traps, and returns RPTC_OK (0) or a negative rptc_status.  All tensors are
+ * caller-owned device memory.  This is the boundary the reference's pybind module
+ * `rptc_kernels` (rptc_kernels/csrc/rptc_kernels/wrapper.cpp:59-67) binds for its seven
+ * functions; the Python shim of the same name calls these through ctypes.
+ *
+ * Terms.  A weight matrix W is [m, n] (out_features, in_features).  Each row is one trellis
+ * bitstream, packed MSB-first into 32-bit words (inference.cu:70-71); a "unit" is 128 bits
+ * (4 words).  The shift-register state is the last 16 bits of the row's stream, zero before the
+ * row start (rptc.py:77-83) or `carry_in[row]` when the tensor is a column shard.
+ */
+#ifndef RPTC_B200_H
+#define RPTC_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *rptc_stream_t; /* a cudaStream_t */
+
+typedef enum {
+    RPTC_OK = 0,
+    RPTC_ERR_ARG = -1,         /* null pointer, bad enum value */
+    RPTC_ERR_SHAPE = -2,       /* m, n, batch violate a divisibility rule */
+    RPTC_ERR_ALIGN = -3,       /* pointer not 16-byte aligned / leading dimension not a multiple of 8 */
+    RPTC_ERR_UNSUPPORTED = -4, /* combination of code / K / layout not implemented */
+    RPTC_ERR_CUDA = -5,        /* a CUDA runtime call failed; see rptc_last_cuda_error() */
+    RPTC_ERR_TIMEOUT = -6,     /* a bounded device-side wait ran out (see rptc_device_status) */
+    RPTC_ERR_TOO_LARGE = -7,   /* size beyond a documented maximum */
+    RPTC_ERR_DEVICE = -8       /* the current device is not compute capability 10.x */
+} rptc_status;
+
+/* Trellis codes.
+ *   RPTC_CODE_LUT  : w = lut[state & (2^L-1)], K bits per weight (rptc.py:74-85; decompress_kernel,
+ *                    inference.cu:66-94, is L=16 K=2).  lut: fp16 [2^L].
+ *   RPTC_CODE_HASH : the fused reference kernel's code (inference.cu:250-262): 4 bits per step, two
+ *                    weights per step, h = t(t+1), entry (h>>8)&(2^S-1) of 2^S fp16 pairs, sign of the
+ *                    low half := bit 15 of h.  K must be 2.  lut: fp16 [2^(S+1)], S = 6 or 8.
+ *   RPTC_CODE_LITE : rptc_lite.py:12-16,63-73: h = x(2x+1); h ^= h>>(L-S); entry h&(2^S-1) of 2^S
+ *                    fp16 pairs; 2K bits per step.  lut: fp16 [2^S][2], S <= 10. */
+enum { RPTC_CODE_LUT = 0, RPTC_CODE_HASH = 1, RPTC_CODE_LITE = 2 };
+
+/* Layouts of the packed words (int32).
+ *   ROWMAJOR  [m][units*4]            decompress_kernel, inference.cu:53-66
+ *   CHUNKED   [units/32][m][32*4]     decompress_matvec_kernel, inference.cu:229
+ *   UNITMAJOR [units][m][4]           decompress_matvec_t_kernel, inference_t.cu:116 — the native,
+ *                                     fastest layout: 32 consecutive rows of one unit are 512 contiguous
+ *                                     bytes, which one warp streams as coalesced 128-bit loads. */
+enum { RPTC_LAYOUT_ROWMAJOR = 0, RPTC_LAYOUT_CHUNKED = 1, RPTC_LAYOUT_UNITMAJOR = 2 };
+
+/* Optional reproduction of two defects of the reference kernels, so that results can be compared
+ * element for element with the reference binary.  0 = the self-consistent stream of rptc.py. */
+enum {
+    RPTC_QUIRK_NONE = 0,
+    RPTC_QUIRK_K1_LANE0_SEED = 1, /* inference.cu:61-62: every 32nd unit seeds from the high half of the previous word */
+    RPTC_QUIRK_K2_LANE0_CARRY = 2 /* inference.cu:232: every 32nd unit takes its own last word as the carry */
+};
+
+/* How the activation vector is paired with the stream in rptc_gemv.
+ *   NATURAL   : column c of W multiplies x[c].
+ *   K2_LEGACY : the staging permutation of decompress_matvec_kernel (inference.cu:216-221,249);
+ *               needs n % 2048 == 0. */
+enum { RPTC_XORDER_NATURAL = 0, RPTC_XORDER_K2_LEGACY = 1 };
+
+typedef struct {
+    int32_t code;   /* RPTC_CODE_* */
+    int32_t K;      /* bits per weight: 2, 3 or 4 */
+    int32_t L;      /* state bits, <= 16 */
+    int32_t S;      /* log2(number of LUT pairs) for HASH / LITE; ignored for LUT */
+    int32_t layout; /* RPTC_LAYOUT_* */
+    int32_t quirk;  /* RPTC_QUIRK_* */
+} rptc_format;
+
+const char *rptc_strerror(int status);
+int rptc_version(void);
+/* cudaError_t of the last failing runtime call made by this library on the calling thread. */
+int rptc_last_cuda_error(void);
+/* RPTC_OK when the current device is a compute-capability 10.x GPU, else RPTC_ERR_DEVICE. */
+int rptc_check_device(void);
+/* Reads (and clears) the device-side status word: 0, or RPTC_ERR_TIMEOUT when a kernel gave up a
+ * bounded wait on one of its own asynchronous copies.  Synchronises the device. */
+int rptc_device_status(void);
+/* Launch kernels with programmatic dependent launch (1) or plainly (0, default). */
+void rptc_set_pdl(int enable);
+
+/* Re-tiles packed codes between layouts (a pure permutation of 128-bit units).
+ * Replaces nothing in the reference: it connects the reference's three layouts.  m % 32 == 0. */
+int rptc_repack(const void *src, int src_layout, void *dst, int dst_layout, int64_t m, int64_t n_units,
+                rptc_stream_t stream);
+
+/* Packed codes -> dense fp16 out[m][ld_out] (first n columns written).
+ * Replaces decompress(compressed, codebook, out), inference.cu:99-160 / wrapper.cpp:60, and
+ * generalises it to K = 2,3,4, all three codes and layouts, n % (128*P/K) == 0 (P = 3 for K = 3,
+ * else 1), m % 32 == 0.  carry_in may be NULL. */
+int rptc_decompress(const void *codes, const void *lut, const uint32_t *carry_in, void *out, int64_t ld_out,
+                    int64_t m, int64_t n, const rptc_format *fmt, rptc_stream_t stream);
+
+/* Fused decode + matvec, batch 1..8:  acc[b][row] += sum_c W[row][c] * x[b][c]   (fp32 acc).
+ * Replaces the kernels behind decompress_matvec_{16,20}_{6,8}_1 (inference.cu:189-277) and
+ * decompress_matvec_t_{16,14} (inference_t.cu:68-175).  `acc` is fp32 SCRATCH of [batch][ld_acc]
+ * that the caller zeroes (or pre-loads) and later converts with rptc_gemv_finish; partial sums
+ * are added with atomics, so the low bits of a result can differ between runs.
+ * x: fp16 [batch][ld_x].  K = 2 or 4.  m % 32 == 0, n % (128/K) == 0. */
+int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
+              float *acc, int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
+              rptc_stream_t stream);
+
+/* y[b][i] = fp16(scale * acc[b][i] (+ y[b][i] if accumulate));  acc[b][i] = 0 if clear.
+ * accumulate = 1 gives decompress_matvec_t's `out +=` (inference_t.cu:170-171). */
+int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t m, int batch, float scale,
+                     int accumulate, int clear, rptc_stream_t stream);
+
+/* Fused decode + GEMM for prefill (tcgen05 tensor cores, TMEM accumulators):
+ * y[t][row] = fp16( sum_c x[t][c] * W[row][c] ),  x fp16 [tokens][ld_x], y fp16 [tokens][ld_y].
+ * No reference counterpart (the reference has batch-1 kernels only); the equivalent reference
+ * computation is decompress followed by a dense matmul (rptc_kernels/tests/test_decompress.py:41-43).
+ * UNITMAJOR layout, K = 2 or 4, m % 128 == 0, n % 64 == 0. */
+int rptc_gemm(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x, void *y,
+              int64_t ld_y, int64_t m, int64_t n, int64_t tokens, const rptc_format *fmt, rptc_stream_t stream);
+
+/* Block-diagonal randomized Hadamard transform along rows of length n (block = power of two <= 4096
+ * dividing n).  No reference counterpart (incoherence processing is an extension of this build).
+ *   in_is_f32 = 0: in is fp16 [rows][ld_in];  1: in is fp32 (e.g. the rptc_gemv accumulator).
+ *   transpose = 0: out = H (s * in) * scale        (activation side)
+ *   transpose = 1: out = s * (H in) * scale        (output side)
+ *   clear_in  = 1 (fp32 input only): zero the input after reading it.
+ * signs: fp16 [n] of +-1, or NULL for all +1.  out: fp16 [rows][ld_out]; may alias an fp16 input. */
+int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void *out, int64_t ld_out, const void *signs,
+                  int64_t rows, int64_t n, int block, int transpose, float scale, int clear_in, rptc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RPTC_B200_H */

@@ -1,0 +1,267 @@
+// Shared device/host helpers for the sm_100a RPTC kernels: status plumbing, bounded mbarrier waits,
+// 1-D bulk (TMA) copies, and the unit decoder every kernel is built around.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rptc_b200.h"
+
+namespace rptc {
+
+constexpr int kNumSMsFallback = 148;
+constexpr uint32_t kSpinLimit = 1u << 22;   // bounded wait: try_wait attempts before a kernel gives up
+
+// ---- host side -------------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+int cuda_fail(cudaError_t e);                 // records e, returns RPTC_ERR_CUDA
+int num_sms();                                // SM count of the current device (cached per device)
+bool pdl_enabled();
+unsigned int *device_status_word();           // device address of the status word (per device)
+
+#define RPTC_CUDA(call)                                      \
+    do {                                                     \
+        cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return ::rptc::cuda_fail(e__); \
+    } while (0)
+
+// Launches `kernel` with or without the programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    RPTC_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    return RPTC_OK;
+}
+
+// ---- device side -----------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// Programmatic dependent launch: both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_allow_next_grid() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after raising the device status word) when the limit runs out, so
+// that the caller can stop issuing work, drain what is in flight and return.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int *status) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(status, 1u);
+    return false;
+}
+// 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
+// Both addresses and the size must be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg128_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t half2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+
+// ---- packed-code addressing -------------------------------------------------------------------
+// Index (in 128-bit units) of unit u of row r:  (u >> 5) * hi + (u & 31) * lo + r * row.
+struct UnitStrides {
+    int64_t hi, lo, row;
+};
+__host__ __device__ inline UnitStrides unit_strides(int layout, int64_t m, int64_t n_units) {
+    switch (layout) {
+        case RPTC_LAYOUT_ROWMAJOR: return {32, 1, n_units};
+        case RPTC_LAYOUT_CHUNKED: return {32 * m, 1, 32};
+        default: return {32 * m, m, 1};
+    }
+}
+__device__ __forceinline__ int64_t unit_index(const UnitStrides &s, int64_t u, int64_t r) {
+    return (u >> 5) * s.hi + (u & 31) * s.lo + r * s.row;
+}
+
+// ---- shared-memory lookup tables ---------------------------------------------------------------
+// LUT code   : fp16 [2^L], flat.
+// HASH code  : 256 rows of 256 bytes; row e (= bits 8..15 of the hash) holds, at byte 4*lane, the
+//              fp16 pair of entry e & (2^S-1) with the low half's sign already set to bit 7 of e
+//              (which is bit 15 of the hash).  The table must start on a 64 KiB boundary of the shared
+//              window so that (hash & 0xFF00) | 4*lane is the whole address computation.
+// LITE code  : 2^S rows of 128 bytes, the pair of entry e at byte 4*lane of row e.
+constexpr uint32_t kHashLutBytes = 65536;
+constexpr uint32_t kHashLutWindow = 0x10000;   // shared-window address the HASH table is placed at
+
+template <int CODE>
+struct Lut {
+    uint32_t base;   // LUT: table address.  HASH: kHashLutWindow | 4*lane.  LITE: table address + 4*lane.
+    uint32_t mask;   // LUT: 2^L-1.  LITE: 2^S-1.
+    uint32_t shift;  // LITE: L-S.
+};
+
+template <int CODE>
+__device__ __forceinline__ uint32_t lut_bytes(int L, int S) {
+    if (CODE == RPTC_CODE_LUT) return 2u << L;
+    if (CODE == RPTC_CODE_HASH) return kHashLutBytes;
+    return 128u << S;
+}
+
+// Fills the table from the global codebook.  All threads of the CTA take part; the caller
+// synchronises afterwards.
+template <int CODE>
+__device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restrict__ g, int L, int S) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
+    if (CODE == RPTC_CODE_LUT) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(g);
+        for (int i = tid; i < (1 << L) / 8; i += nt) {
+            uint4 v = __ldg(src + i);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16u * i), "r"(v.x), "r"(v.y), "r"(v.z),
+                         "r"(v.w)
+                         : "memory");
+        }
+    } else if (CODE == RPTC_CODE_HASH) {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
+        for (int e = tid >> 5; e < 256; e += nt >> 5) {
+            uint32_t v = __ldg(src + (e & ((1 << S) - 1)));
+            v = (v & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + 256u * e + 4u * lane), "r"(v) : "memory");
+        }
+    } else {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
+        for (int e = tid >> 5; e < (1 << S); e += nt >> 5) {
+            uint32_t v = __ldg(src + e);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + 128u * e + 4u * lane), "r"(v) : "memory");
+        }
+    }
+}
+
+template <int CODE>
+__device__ __forceinline__ Lut<CODE> lut_view(uint32_t table, int L, int S) {
+    const uint32_t lane4 = 4u * (threadIdx.x & 31);
+    Lut<CODE> v;
+    if (CODE == RPTC_CODE_LUT) {
+        v.base = table;
+        v.mask = (1u << L) - 1u;
+        v.shift = 0;
+    } else if (CODE == RPTC_CODE_HASH) {
+        v.base = table | lane4;
+        v.mask = 0;
+        v.shift = 0;
+    } else {
+        v.base = table + lane4;
+        v.mask = (1u << S) - 1u;
+        v.shift = (uint32_t)(L - S);
+    }
+    return v;
+}
+
+// ---- the unit decoder --------------------------------------------------------------------------
+// A "group" is P consecutive 128-bit units of one row (P = 3 when K = 3 so that a group holds a whole
+// number of weights, else 1).  decode_group turns the group's words plus the 16 stream bits before
+// it (`halo`, low half) into fp16 weight pairs and hands pair p (columns 2p, 2p+1 of the group) to
+// emit(p, pair).  Every weight is a pure function of the 16-bit window ending at its last bit, so
+// nothing here is sequential: window registers R[o] cover stream bits [16o-16, 16o+16) of the group
+// and a weight ending at bit e reads (R[(e-1)>>4] >> (16*((e-1)>>4)+16-e)) & 0xFFFF.
+template <int K>
+struct GroupShape {
+    static constexpr int P = (K == 3) ? 3 : 1;          // units per group
+    static constexpr int kWords = 4 * P;
+    static constexpr int kWeights = 128 * P / K;        // 64, 128, 32
+    static constexpr int kPairs = kWeights / 2;
+};
+
+template <int CODE, int K, typename Emit>
+__device__ __forceinline__ void decode_group(const uint32_t (&w)[GroupShape<K>::kWords], uint32_t halo,
+                                             const Lut<CODE> &lut, Emit &&emit) {
+    constexpr int NW = GroupShape<K>::kWords;
+    uint32_t R[2 * NW];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        R[2 * i] = __funnelshift_l(w[i], i == 0 ? halo : w[i - 1], 16);
+        R[2 * i + 1] = w[i];
+    }
+    if (CODE == RPTC_CODE_LUT) {
+#pragma unroll
+        for (int p = 0; p < GroupShape<K>::kPairs; ++p) {
+            uint32_t h[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int e = K * (2 * p + q + 1);
+                const int o = (e - 1) >> 4;
+                const int sh = 16 * (o + 1) - e;
+                const uint32_t state = (R[o] >> sh) & lut.mask;
+                h[q] = lds16(lut.base + 2u * state);
+            }
+            emit(p, u32_as_half2(h[0] | (h[1] << 16)));
+        }
+    } else {
+        constexpr int BPS = 2 * K;   // bits per step
+#pragma unroll
+        for (int p = 0; p < GroupShape<K>::kPairs; ++p) {
+            const int e = BPS * (p + 1);
+            const int o = (e - 1) >> 4;
+            const int sh = 16 * (o + 1) - e;
+            const uint32_t t = R[o] >> sh;
+            if (CODE == RPTC_CODE_HASH) {
+                const uint32_t h = t * t + t;
+                emit(p, u32_as_half2(lds32((h & 0xFF00u) | lut.base)));
+            } else {
+                // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
+                // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.
+                uint32_t h = t * (2u * t + 1u);
+                h ^= h >> lut.shift;
+                emit(p, u32_as_half2(lds32(lut.base + ((h & lut.mask) << 7))));
+            }
+        }
+    }
+}
+
+#endif  // __CUDACC__
+}  // namespace rptc

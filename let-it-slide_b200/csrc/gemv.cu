@@ -1,0 +1,383 @@
+// Fused RPTC decode + matvec for decode batches 1..8 on sm_100a.
+//
+// Work decomposition.  Rows are taken 32 at a time (a "row block": lane l owns row 32*rb + l) and a
+// row's stream is cut into 128-bit units.  The (row block, unit) grid is flattened row-block-major
+// and cut into equal contiguous ranges, one per warp of a persistent grid of one 512-thread CTA per
+// SM, so that every SM gets the same number of units whatever m and n are.  In the native UNITMAJOR
+// layout the 32 rows of one unit are 512 contiguous bytes: lane 0 of each warp streams them into a
+// private shared-memory ring with 1-D bulk (TMA) copies completing on mbarriers, several units
+// ahead, and every lane then takes its own 128 bits with one conflict-free LDS.128.  The 16-bit
+// shift-register windows are rebuilt in registers with funnel shifts, hashed / looked up in a
+// bank-replicated shared-memory table, and multiplied into half2 accumulators that are flushed to
+// fp32 every unit.  A warp walks along its rows, so the 16 bits of history a unit needs are simply
+// the last word of the unit before it (one extra 32-bit load at the start of a range).  Partial
+// row sums are added to the fp32 accumulator in global memory with atomics.
+//
+// Activations are staged once per CTA in shared memory and read back as warp-broadcast LDS.128.
+#include "common.cuh"
+
+namespace rptc {
+
+constexpr int kGemvThreads = 512;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kStages = 6;                       // ring depth per warp (units in flight)
+constexpr uint32_t kStageBytes = 512;
+constexpr uint32_t kBarBytes = 1024;             // kGemvWarps * kStages * 8 <= 1024
+constexpr uint32_t kRingBytes = kGemvWarps * kStages * kStageBytes;
+static_assert(kGemvWarps * kStages * 8 <= kBarBytes, "barrier area too small");
+static_assert(kBarBytes + kRingBytes + 2048 <= kHashLutWindow, "ring must fit below the HASH table window");
+
+struct GemvParams {
+    const uint4 *codes;
+    UnitStrides st;
+    const __half *lut;
+    const uint32_t *carry_in;
+    const __half *x;
+    int64_t ld_x;
+    float *acc;
+    int64_t ld_acc;
+    int64_t m, n;
+    int32_t n_units, seg_units;
+    int32_t L, S, quirk, x_order;
+    unsigned int *status;
+};
+
+// Source pair of stream pair s under the fused reference kernel's x staging (inference.cu:216-221,249).
+__device__ __forceinline__ int64_t k2_legacy_pair(int64_t s, int64_t n) {
+    const int64_t it = s >> 10;
+    const int lane = (int)(s >> 5) & 31, o = (int)(s >> 2) & 7, j = (int)s & 3;
+    const int k = (0x36251407 >> (4 * o)) & 7;       // window register met at stream position o: 7,0,4,1,5,2,6,3
+    const int64_t p = ((it * 8 + k) * 4 + j) * 32 + lane;
+    const int64_t q8 = n >> 3;
+    return 4 * (p % q8) + p / q8;
+}
+
+template <int CODE, int K, int BATCH, bool TMA>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
+    constexpr int WPU = 128 / K;          // weights per unit
+    constexpr int PAIRS = WPU / 2;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t s0 = smem_addr(smem_raw);
+    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
+    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
+    uint32_t lut_tab, xs;
+    if (CODE == RPTC_CODE_HASH) {
+        lut_tab = kHashLutWindow;
+        xs = kHashLutWindow + kHashLutBytes;
+    } else {
+        lut_tab = s0 + kBarBytes + (TMA ? kRingBytes : 0u);
+        xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
+    }
+
+    if (CODE == RPTC_CODE_HASH && TMA && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
+        // the dynamic area starts later in the shared window than this kernel was laid out for
+        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        return;
+    }
+    // ---- prologue: nothing here depends on the kernels before this one ----
+    lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
+    if (TMA && lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
+    pdl_allow_next_grid();
+
+    const int64_t n_rb = p.m >> 5;
+    const int64_t gw = (int64_t)blockIdx.x * kGemvWarps + warp, GW = (int64_t)gridDim.x * kGemvWarps;
+    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;     // bytes of one batch row in shared memory
+    uint32_t issued = 0, consumed = 0;      // per-warp ring counters (monotonic over the whole kernel)
+    bool ok = true;
+    bool waited_prior = false;
+
+    for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
+        const int32_t nu = min(p.seg_units, p.n_units - useg0);
+        const int64_t T = n_rb * nu;
+        const int64_t f0 = T * gw / GW, f1 = T * (gw + 1) / GW;
+        const uint32_t count = (uint32_t)(f1 - f0);
+
+        auto unit_ptr = [&](int64_t f) -> const uint4 * {
+            const int64_t rb = f / nu;
+            const int64_t u = useg0 + (f - rb * nu);
+            return p.codes + unit_index(p.st, u, rb << 5);
+        };
+        // start streaming this range's codes before anything else
+        uint32_t issued_here = 0;
+        if (TMA) {
+            if (lane == 0) {
+                const uint32_t ahead = min(count, (uint32_t)kStages);
+                for (uint32_t i = 0; i < ahead; ++i) {
+                    const uint32_t st = (issued + i) % kStages;
+                    mbar_expect_tx(bars + 8u * st, kStageBytes);
+                    bulk_g2s(ring + st * kStageBytes, unit_ptr(f0 + i), kStageBytes, bars + 8u * st);
+                }
+            }
+            issued_here = min(count, (uint32_t)kStages);
+        }
+
+        // ---- activations of this column segment -> shared memory ----
+        if (!waited_prior) {
+            pdl_wait_prior_grids();
+            waited_prior = true;
+        }
+        if (useg0 > 0) __syncthreads();          // everyone is done with the previous segment's x
+        {
+            const int64_t col0 = (int64_t)useg0 * WPU;
+            const int pairs = nu * PAIRS;
+            for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
+                const int b = i / pairs, s = i - b * pairs;
+                int64_t src = (col0 >> 1) + s;
+                if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+            }
+        }
+        __syncthreads();
+
+        // ---- main loop over this warp's units ----
+        float facc[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
+        int64_t cur_rb = -1;
+        uint32_t prevw = 0;
+        uint4 nextv = make_uint4(0, 0, 0, 0);
+        if (!TMA && count > 0) nextv = ldg128_stream(unit_ptr(f0) + (int64_t)lane * p.st.row);
+
+        for (uint32_t i = 0; i < count && ok; ++i) {
+            const int64_t f = f0 + i;
+            const int64_t rb = f / nu;
+            const int32_t ul = (int32_t)(f - rb * nu);
+            const int32_t u = useg0 + ul;
+            const int64_t row = (rb << 5) + lane;
+            if (rb != cur_rb) {
+                if (cur_rb >= 0) {
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) {
+                        atomicAdd(p.acc + (int64_t)b * p.ld_acc + (cur_rb << 5) + lane, facc[b]);
+                        facc[b] = 0.f;
+                    }
+                }
+                cur_rb = rb;
+                if (u == 0)
+                    prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
+                else
+                    prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u - 1, row)) + 3);
+            }
+            uint4 v;
+            if (TMA) {
+                const uint32_t st = consumed % kStages;
+                ok = mbar_wait(bars + 8u * st, (consumed / kStages) & 1u, p.status);
+                v = lds128(ring + st * kStageBytes + 16u * lane);
+                ++consumed;
+                __syncwarp();
+                if (lane == 0 && ok && issued_here < count) {
+                    mbar_expect_tx(bars + 8u * st, kStageBytes);
+                    bulk_g2s(ring + st * kStageBytes, unit_ptr(f0 + issued_here), kStageBytes, bars + 8u * st);
+                }
+                if (issued_here < count) ++issued_here;
+            } else {
+                v = nextv;
+                if (i + 1 < count) nextv = ldg128_stream(unit_ptr(f + 1) + (int64_t)lane * p.st.row);
+            }
+            uint32_t halo = prevw;
+            if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
+                if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
+                else if (u > 0) halo = prevw >> 16;
+            }
+            prevw = v.w;
+
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t xu = xs + (uint32_t)ul * (WPU * 2u);
+            __half2 hacc[BATCH][4];
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b)
+#pragma unroll
+                for (int a = 0; a < 4; ++a) hacc[b][a] = __float2half2_rn(0.f);
+            uint4 xv[BATCH];
+            decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                if ((pi & 3) == 0) {
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                }
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                    hacc[b][pi & 3] = __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
+                }
+            });
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+                const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
+                const float2 f2 = __half22float2(s);
+                facc[b] += f2.x + f2.y;
+            }
+        }
+        if (cur_rb >= 0) {
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + (cur_rb << 5) + lane, facc[b]);
+        }
+        if (TMA) {
+            issued += issued_here;
+            // After a failed wait: give the copies still in flight a bounded chance to land before
+            // the shared memory they target is released.
+            while (consumed < issued) {
+                const uint32_t st = consumed % kStages;
+                mbar_wait(bars + 8u * st, (consumed / kStages) & 1u, p.status);
+                ++consumed;
+            }
+        }
+    }
+    if (!waited_prior) pdl_wait_prior_grids();
+}
+
+__global__ void gemv_finish_kernel(float *__restrict__ acc, int64_t ld_acc, __half *__restrict__ y, int64_t ld_y,
+                                   int64_t m, int batch, float scale, int accumulate, int clear) {
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m * batch) return;
+    const int64_t b = i / m, r = i - b * m;
+    float v = acc[b * ld_acc + r] * scale;
+    if (accumulate) {
+        // the reference accumulates in fp16: out = out + delta (inference_t.cu:170-171)
+        y[b * ld_y + r] = __hadd(y[b * ld_y + r], __float2half_rn(v));
+    } else {
+        y[b * ld_y + r] = __float2half_rn(v);
+    }
+    if (clear) acc[b * ld_acc + r] = 0.f;
+}
+
+template <int CODE, int K, int BATCH, bool TMA>
+static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
+    static bool configured = false;
+    auto kern = gemv_kernel<CODE, K, BATCH, TMA>;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
+}
+
+template <int CODE, int K, bool TMA>
+static int dispatch_batch(const GemvParams &p, int batch, size_t smem, cudaStream_t stream) {
+    switch (batch) {
+        case 1: return launch_gemv<CODE, K, 1, TMA>(p, smem, stream);
+        case 2: return launch_gemv<CODE, K, 2, TMA>(p, smem, stream);
+        case 4: return launch_gemv<CODE, K, 4, TMA>(p, smem, stream);
+        case 8: return launch_gemv<CODE, K, 8, TMA>(p, smem, stream);
+    }
+    return RPTC_ERR_ARG;
+}
+
+template <int CODE, int K>
+static int dispatch_tma(const GemvParams &p, int batch, bool tma, size_t smem, cudaStream_t stream) {
+    if (tma) return dispatch_batch<CODE, K, true>(p, batch, smem, stream);
+    if (batch != 1) return RPTC_ERR_UNSUPPORTED;
+    return launch_gemv<CODE, K, 1, false>(p, smem, stream);
+}
+
+// One launch for batch in {1,2,4,8}.
+static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in, const __half *x, int64_t ld_x, float *acc,
+                    int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format &f, cudaStream_t stream) {
+    const int K = f.K;
+    const int wpu = 128 / K;
+    GemvParams p;
+    p.codes = static_cast<const uint4 *>(codes);
+    p.n_units = (int32_t)(n / wpu);
+    p.st = unit_strides(f.layout, m, p.n_units);
+    p.lut = static_cast<const __half *>(lut);
+    p.carry_in = carry_in;
+    p.x = x;
+    p.ld_x = ld_x;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.m = m;
+    p.n = n;
+    p.L = f.L;
+    p.S = f.S;
+    p.quirk = f.quirk;
+    p.x_order = x_order;
+    p.status = device_status_word();
+    if (!p.status) return RPTC_ERR_CUDA;
+    const bool tma = f.layout == RPTC_LAYOUT_UNITMAJOR;
+
+    // shared-memory plan (must mirror the kernel's)
+    const size_t kMaxSmem = 227 * 1024 - 1024;     // leave room for the 1 KiB the system may reserve
+    size_t fixed;
+    if (f.code == RPTC_CODE_HASH) fixed = kHashLutWindow + kHashLutBytes;      // addresses are absolute in the window
+    else fixed = kBarBytes + (tma ? kRingBytes : 0) + (f.code == RPTC_CODE_LUT ? (size_t(2) << f.L) : (size_t(128) << f.S)) + 128;
+    if (fixed + 1024 > kMaxSmem) return RPTC_ERR_UNSUPPORTED;
+    size_t x_budget = kMaxSmem - fixed;
+    if (x_budget > 96 * 1024) x_budget = 96 * 1024;
+    const size_t unit_x_bytes = size_t(batch) * wpu * 2;
+    int64_t seg = (int64_t)(x_budget / unit_x_bytes);
+    if (x_order == RPTC_XORDER_K2_LEGACY) seg = seg / 32 * 32;
+    if (seg < 1) return RPTC_ERR_TOO_LARGE;
+    if (seg > p.n_units) seg = p.n_units;
+    p.seg_units = (int32_t)seg;
+    const size_t smem = fixed + size_t(seg) * unit_x_bytes;
+
+    switch (f.code) {
+        case RPTC_CODE_LUT:
+            if (K == 2) return dispatch_tma<RPTC_CODE_LUT, 2>(p, batch, tma, smem, stream);
+            if (K == 4) return dispatch_tma<RPTC_CODE_LUT, 4>(p, batch, tma, smem, stream);
+            break;
+        case RPTC_CODE_HASH:
+            if (K == 2) return dispatch_tma<RPTC_CODE_HASH, 2>(p, batch, tma, smem, stream);
+            break;
+        case RPTC_CODE_LITE:
+            if (K == 2) return dispatch_tma<RPTC_CODE_LITE, 2>(p, batch, tma, smem, stream);
+            if (K == 4) return dispatch_tma<RPTC_CODE_LITE, 4>(p, batch, tma, smem, stream);
+            break;
+    }
+    return RPTC_ERR_UNSUPPORTED;
+}
+
+int check_format(const rptc_format *f);   // api.cu
+
+}  // namespace rptc
+
+using namespace rptc;
+
+extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
+                         float *acc, int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
+                         rptc_stream_t stream) {
+    if (!codes || !lut || !x || !acc || !fmt) return RPTC_ERR_ARG;
+    if (int e = check_format(fmt)) return e;
+    if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
+    if (batch < 1 || batch > 8) return RPTC_ERR_ARG;
+    if (x_order != RPTC_XORDER_NATURAL && x_order != RPTC_XORDER_K2_LEGACY) return RPTC_ERR_ARG;
+    if (m <= 0 || n <= 0 || (m % 32) || (n % (128 / fmt->K))) return RPTC_ERR_SHAPE;
+    if (x_order == RPTC_XORDER_K2_LEGACY && (n % 2048 || fmt->K != 2)) return RPTC_ERR_SHAPE;
+    if (fmt->layout == RPTC_LAYOUT_CHUNKED && (n / (128 / fmt->K)) % 32) return RPTC_ERR_SHAPE;
+    if (m > (int64_t(1) << 30) || n > (int64_t(1) << 30)) return RPTC_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(lut) & 15) ||
+        (reinterpret_cast<uintptr_t>(x) & 3) || (ld_x & 1))
+        return RPTC_ERR_ALIGN;
+    if (ld_x < n || ld_acc < m) return RPTC_ERR_SHAPE;
+    if (int e = rptc_check_device()) return e;
+    // batches that are not a power of two run as a short sequence of launches
+    int done = 0;
+    while (done < batch) {
+        int b = 8;
+        while (b > batch - done) b >>= 1;
+        int e = gemv_one(codes, lut, carry_in, static_cast<const __half *>(x) + (int64_t)done * ld_x, ld_x,
+                         acc + (int64_t)done * ld_acc, ld_acc, m, n, b, x_order, *fmt, static_cast<cudaStream_t>(stream));
+        if (e) return e;
+        done += b;
+    }
+    return RPTC_OK;
+}
+
+extern "C" int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t m, int batch, float scale,
+                                int accumulate, int clear, rptc_stream_t stream) {
+    if (!acc || !y) return RPTC_ERR_ARG;
+    if (m <= 0 || batch < 1 || ld_acc < m || ld_y < m) return RPTC_ERR_SHAPE;
+    if (int e = rptc_check_device()) return e;
+    const int64_t total = m * batch;
+    return launch(gemv_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                  acc, ld_acc, static_cast<__half *>(y), ld_y, m, batch, scale, accumulate, clear);
+}

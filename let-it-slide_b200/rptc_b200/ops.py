@@ -1,0 +1,162 @@
+"""Tensor-level front end of the C ABI: thin argument checking, no arithmetic of its own."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import (CODE_HASH, CODE_LITE, CODE_LUT, LAYOUT_CHUNKED, LAYOUT_ROWMAJOR, LAYOUT_UNITMAJOR, XORDER_NATURAL,
+                   Format, check, lib, ptr, stream_ptr)
+
+
+def _cuda_contig(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+
+
+def units_per_row(n: int, K: int) -> int:
+    if (n * K) % 128:
+        raise RuntimeError(f"n*K = {n * K} bits per row is not a whole number of 128-bit units")
+    return n * K // 128
+
+
+def codes_shape(m: int, n: int, K: int, layout: int) -> tuple[int, ...]:
+    nu = units_per_row(n, K)
+    if layout == LAYOUT_ROWMAJOR:
+        return (m, nu * 4)
+    if layout == LAYOUT_CHUNKED:
+        return (nu // 32, m, 128)
+    return (nu, m, 4)
+
+
+def repack(codes: torch.Tensor, src_layout: int, dst_layout: int, m: int, n_units: int) -> torch.Tensor:
+    """Packed codes in `src_layout` -> a new tensor in `dst_layout` (rptc_repack)."""
+    _cuda_contig(codes, "codes", torch.int32)
+    if codes.numel() != m * n_units * 4:
+        raise RuntimeError("codes has the wrong number of elements")
+    if dst_layout == LAYOUT_ROWMAJOR:
+        shape = (m, n_units * 4)
+    elif dst_layout == LAYOUT_CHUNKED:
+        shape = (n_units // 32, m, 128)
+    else:
+        shape = (n_units, m, 4)
+    out = torch.empty(shape, dtype=torch.int32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_repack(ptr(codes), src_layout, ptr(out), dst_layout, m, n_units, stream_ptr()), "rptc_repack")
+    return out
+
+
+def decompress(codes: torch.Tensor, lut: torch.Tensor, m: int, n: int, fmt: Format, out: torch.Tensor | None = None,
+               carry_in: torch.Tensor | None = None) -> torch.Tensor:
+    """Packed codes -> dense fp16 [m, n] (rptc_decompress)."""
+    _cuda_contig(codes, "codes", torch.int32)
+    _cuda_contig(lut, "lut", torch.float16)
+    if lut.numel() != fmt.lut_numel():
+        raise RuntimeError(f"lut must have {fmt.lut_numel()} elements, got {lut.numel()}")
+    if codes.numel() * 32 != m * n * fmt.K:
+        raise RuntimeError("codes has the wrong number of elements for m, n, K")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
+    else:
+        if not out.is_cuda or out.dtype != torch.float16 or out.dim() != 2 or out.shape != (m, n) or out.stride(1) != 1:
+            raise RuntimeError("out must be a CUDA fp16 [m, n] tensor with unit column stride")
+    if carry_in is not None:
+        _cuda_contig(carry_in, "carry_in", torch.int32)
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_decompress(ptr(codes), ptr(lut), ptr(carry_in), ptr(out), out.stride(0), m, n, ctypes.byref(fmt),
+                                    stream_ptr()), "rptc_decompress")
+    return out
+
+
+def gemv_acc(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, acc: torch.Tensor, m: int, n: int, fmt: Format,
+             x_order: int = XORDER_NATURAL, carry_in: torch.Tensor | None = None) -> None:
+    """acc[b, :m] += W x[b]  (fp32 accumulator; rptc_gemv).  x: fp16 [b, n] or [n]."""
+    _cuda_contig(codes, "codes", torch.int32)
+    _cuda_contig(lut, "lut", torch.float16)
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    if acc.dim() == 1:
+        acc = acc.unsqueeze(0)
+    if not x.is_cuda or x.dtype != torch.float16 or x.stride(1) != 1 or x.shape[1] != n:
+        raise RuntimeError("x must be a CUDA fp16 [batch, n] tensor with unit column stride")
+    if not acc.is_cuda or acc.dtype != torch.float32 or acc.stride(1) != 1 or acc.shape[1] < m or acc.shape[0] != x.shape[0]:
+        raise RuntimeError("acc must be a CUDA fp32 [batch, >=m] tensor")
+    if codes.numel() * 32 != m * n * fmt.K:
+        raise RuntimeError("codes has the wrong number of elements for m, n, K")
+    if lut.numel() != fmt.lut_numel():
+        raise RuntimeError(f"lut must have {fmt.lut_numel()} elements, got {lut.numel()}")
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_gemv(ptr(codes), ptr(lut), ptr(carry_in), ptr(x), x.stride(0) if x.shape[0] > 1 else max(n, x.stride(0)),
+                              ptr(acc), acc.stride(0) if acc.shape[0] > 1 else max(m, acc.stride(0)), m, n, x.shape[0],
+                              x_order, ctypes.byref(fmt), stream_ptr()), "rptc_gemv")
+
+
+def gemv_finish(acc: torch.Tensor, y: torch.Tensor, m: int, scale: float = 1.0, accumulate: bool = False,
+                clear: bool = True) -> None:
+    """y = fp16(scale * acc) (+ y); optionally zero acc (rptc_gemv_finish)."""
+    if acc.dim() == 1:
+        acc = acc.unsqueeze(0)
+    if y.dim() == 1:
+        y = y.unsqueeze(0)
+    with torch.cuda.device(acc.device):
+        check(lib().rptc_gemv_finish(ptr(acc), acc.stride(0) if acc.shape[0] > 1 else max(m, acc.stride(0)), ptr(y),
+                                     y.stride(0) if y.shape[0] > 1 else max(m, y.stride(0)), m, acc.shape[0], scale,
+                                     int(accumulate), int(clear), stream_ptr()), "rptc_gemv_finish")
+
+
+def gemv(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, m: int, n: int, fmt: Format,
+         x_order: int = XORDER_NATURAL, carry_in: torch.Tensor | None = None) -> torch.Tensor:
+    """Convenience: allocate a zeroed fp32 accumulator, run the fused matvec, return fp16 [b, m]."""
+    xb = x.unsqueeze(0) if x.dim() == 1 else x
+    acc = torch.zeros((xb.shape[0], m), dtype=torch.float32, device=x.device)
+    gemv_acc(codes, lut, xb, acc, m, n, fmt, x_order, carry_in)
+    y = torch.empty((xb.shape[0], m), dtype=torch.float16, device=x.device)
+    gemv_finish(acc, y, m, clear=False)
+    return y[0] if x.dim() == 1 else y
+
+
+def gemm(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, m: int, n: int, fmt: Format,
+         out: torch.Tensor | None = None, carry_in: torch.Tensor | None = None) -> torch.Tensor:
+    """y[t] = W x[t] for a block of tokens on the tensor cores (rptc_gemm).  x: fp16 [tokens, n]."""
+    _cuda_contig(codes, "codes", torch.int32)
+    _cuda_contig(lut, "lut", torch.float16)
+    if not x.is_cuda or x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != n:
+        raise RuntimeError("x must be a CUDA fp16 [tokens, n] tensor with unit column stride")
+    if out is None:
+        out = torch.empty((x.shape[0], m), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_gemm(ptr(codes), ptr(lut), ptr(carry_in), ptr(x), x.stride(0), ptr(out), out.stride(0), m, n,
+                              x.shape[0], ctypes.byref(fmt), stream_ptr()), "rptc_gemm")
+    return out
+
+
+def hadamard(x: torch.Tensor, signs: torch.Tensor | None, block: int, transpose: bool = False, scale: float = 1.0,
+             out: torch.Tensor | None = None, clear_in: bool = False) -> torch.Tensor:
+    """Block-diagonal randomized Hadamard transform along the last axis (rptc_hadamard).
+
+    x: fp16 or fp32 [rows, n]; result fp16 [rows, n]."""
+    squeeze = x.dim() == 1
+    if squeeze:
+        x = x.unsqueeze(0)
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("x must be a CUDA fp16/fp32 [rows, n] tensor with unit column stride")
+    rows, n = x.shape
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.float16, device=x.device)
+    if signs is not None:
+        _cuda_contig(signs, "signs", torch.float16)
+    with torch.cuda.device(x.device):
+        check(lib().rptc_hadamard(ptr(x), int(x.dtype == torch.float32), x.stride(0) if rows > 1 else max(n, x.stride(0)),
+                                  ptr(out), out.stride(0) if rows > 1 else max(n, out.stride(0)), ptr(signs), rows, n, block,
+                                  int(transpose), scale, int(clear_in), stream_ptr()), "rptc_hadamard")
+    return out[0] if squeeze else out
+
+
+def device_status() -> None:
+    """Raises if a kernel reported a timed-out wait since the last call."""
+    check(lib().rptc_device_status(), "rptc_device_status")

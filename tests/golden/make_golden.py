@@ -1,0 +1,102 @@
+"""Generates tests/golden/rptc_reference_golden.npz by running the reference's OWN Python code.
+
+    python tests/golden/make_golden.py [reference_root]     (default /root/reference)
+
+The reference's rptc.py and rptc_lite.py are imported unmodified (with tests/golden/jax_shim.py
+standing in for JAX, which is not installed) and their `dequantize` / `quantize` functions are run
+on small seeded inputs.  The outputs are the golden vectors the CPU oracle is pinned against in
+tests/test_oracle.py.  The reference checkout is only needed to REGENERATE the file; the tests read
+the committed .npz.
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import jax_shim  # noqa: E402
+
+
+def _load(path: str, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main(ref_root: str) -> None:
+    jax_shim.install()
+    rptc = _load(os.path.join(ref_root, "rptc.py"), "ref_rptc")
+    lite = _load(os.path.join(ref_root, "rptc_lite.py"), "ref_rptc_lite")
+    jnp = jax_shim.jnp
+    rng = np.random.default_rng(42)
+    out = {}
+
+    # --- code A decode (rptc.py:74-85), L = 16 and L = 14, random symbol rows -----------------
+    for L in (16, 14):
+        alphabet = rng.standard_normal(1 << L).astype(np.float32)
+        sym = rng.integers(0, 4, size=(3, 192)).astype(np.int32)
+        dec = np.stack([np.asarray(rptc.dequantize(jnp.array(alphabet), jnp.array(s))) for s in sym])
+        out[f"a{L}_alphabet"] = alphabet
+        out[f"a{L}_symbols"] = sym
+        out[f"a{L}_decoded"] = dec.astype(np.float32)
+
+    # --- code A encode + decode (rptc.py:13-71) at a small state width so that it runs in seconds
+    L = 8
+    M = 1 << L
+    alphabet = np.sort(rng.standard_normal(M)).astype(np.float32)
+    alphabet = alphabet[rng.permutation(M)]
+    samples = rng.standard_normal((2, 48)).astype(np.float32)
+    corrections = np.eye(48, dtype=np.float32)
+    qs, losses, recs = [], [], []
+    for s in samples:
+        q, loss = rptc.quantize(jnp.array(alphabet), jnp.array(corrections), jnp.array(s))
+        qs.append(np.asarray(q))
+        losses.append(float(loss))
+        recs.append(np.asarray(rptc.dequantize(jnp.array(alphabet), q)))
+    out["enc8_alphabet"] = alphabet
+    out["enc8_samples"] = samples
+    out["enc8_symbols"] = np.stack(qs).astype(np.int32)
+    out["enc8_loss"] = np.array(losses, dtype=np.float64)
+    out["enc8_decoded"] = np.stack(recs).astype(np.float32)
+
+    # --- code C decode (rptc_lite.py:63-73), L=16 S=9 R=4 V=2 ----------------------------------
+    L, S, R, V = 16, 9, 4, 2
+    alphabet = rng.standard_normal((1 << S, V)).astype(np.float32)
+    sym = rng.integers(0, 1 << R, size=(3, 96)).astype(np.int32)
+    dec = np.stack([np.asarray(lite.dequantize(jnp.array(alphabet), L, S, R, jnp.array(s))) for s in sym])
+    out["c_alphabet"] = alphabet
+    out["c_symbols"] = sym
+    out["c_decoded"] = dec.astype(np.float32)
+    states = rng.integers(0, 1 << 16, size=512).astype(np.int32)
+    out["c_index_states"] = states
+    out["c_index"] = np.asarray(lite.index_fn(jnp.array(states), L, S)).astype(np.int32)
+
+    # --- code C encode + decode (rptc_lite.py:19-60) at a small state width ---------------------
+    L, S, R, V = 8, 5, 4, 2
+    alphabet = rng.standard_normal((1 << S, V)).astype(np.float32)
+    samples = rng.standard_normal((2, 24, V)).astype(np.float32)
+    importance = np.ones((24, V), dtype=np.float32)
+    qs, losses, recs = [], [], []
+    for s in samples:
+        q, loss = lite.quantize(jnp.array(alphabet), L, S, R, jnp.array(importance), jnp.array(s))
+        qs.append(np.asarray(q))
+        losses.append(float(loss))
+        recs.append(np.asarray(lite.dequantize(jnp.array(alphabet), L, S, R, q)))
+    out["encc_alphabet"] = alphabet
+    out["encc_samples"] = samples
+    out["encc_symbols"] = np.stack(qs).astype(np.int32)
+    out["encc_loss"] = np.array(losses, dtype=np.float64)
+    out["encc_decoded"] = np.stack(recs).astype(np.float32)
+
+    path = os.path.join(HERE, "rptc_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,149 @@
+"""GPU parity of the drop-in `rptc_kernels` module: against the CPU oracle, and (when oracle/_ref holds
+the compiled, unmodified reference extension) against the reference's own kernels on the same
+inputs.  The reference runs in a child process (see tests/ref_runner.py)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import rptc_oracle as o
+from gpu_util import bits, to_dev
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run_reference(which, m, n, seed, tmp_path):
+    path = str(tmp_path / f"{which}.npz")
+    r = subprocess.run([sys.executable, os.path.join(HERE, "ref_runner.py"), which, path, str(m), str(n), str(seed)],
+                       capture_output=True, text=True, timeout=600)
+    if r.returncode == 3:
+        pytest.skip("oracle/_ref reference extension not built")
+    if r.returncode != 0:
+        pytest.skip(f"the reference extension failed on this GPU (exit {r.returncode}): {r.stderr[-300:]}")
+    return np.load(path)
+
+
+def test_reference_decompress_pins_oracle_and_drop_in(tmp_path):
+    import rptc_kernels
+    m, n = 64, 6144
+    d = _run_reference("decompress", m, n, 1, tmp_path)
+    ref_out = d["out"]
+    # (1) the oracle in refkernel mode reproduces the reference kernel on EVERY element
+    assert np.array_equal(bits(o.decode(d["words"], d["lut"], n, quirk=o.QUIRK_K1_LANE0_SEED)), bits(ref_out))
+    # (2) so does the drop-in with the quirk switched on
+    out = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    rptc_kernels.set_reference_quirks(True)
+    try:
+        ms = rptc_kernels.decompress(to_dev(d["words"]), to_dev(d["lut"]), out)
+    finally:
+        rptc_kernels.set_reference_quirks(False)
+    assert isinstance(ms, float) and ms > 0
+    assert np.array_equal(bits(out), bits(ref_out))
+    # (3) and the default (self-consistent) decode differs only where inference.cu:61-62 reads the wrong half
+    rptc_kernels.decompress(to_dev(d["words"]), to_dev(d["lut"]), out)
+    diff = np.nonzero((bits(out) != bits(ref_out)).any(axis=0))[0]
+    assert all(c >= 2048 and c % 2048 < 7 for c in diff)
+    assert np.array_equal(bits(out), bits(o.decode(d["words"], d["lut"], n)))
+
+
+@pytest.mark.parametrize("S", [8, 6])
+def test_reference_fused_matvec_pins_oracle_and_drop_in(tmp_path, S):
+    import rptc_kernels
+    m, n = 128, 4096
+    d = _run_reference(f"matvec_16_{S}_1", m, n, 2 + S, tmp_path)
+    ref_out = d["out"].astype(np.float64)
+    chunked = o.from_rowmajor(d["words"], o.LAYOUT_CHUNKED)
+    # (1) step-for-step fp16 emulation of the reference kernel (quirk included)
+    emu = o.matvec_k2_fp16(chunked, d["lut"], d["x"], S).astype(np.float64)
+    ulp = np.maximum(np.abs(ref_out), 1.0) * 2.0**-10
+    assert (np.abs(emu - ref_out) <= 2 * ulp).all(), "oracle's refkernel emulation disagrees with the reference kernel"
+    assert np.mean(emu == ref_out) > 0.9
+    # (2) the drop-in in quirk mode computes the same product with better accumulation
+    out = torch.zeros((m,), dtype=torch.float16, device="cuda")
+    fn = getattr(rptc_kernels, f"decompress_matvec_16_{S}_1")
+    rptc_kernels.set_reference_quirks(True)
+    try:
+        fn(to_dev(chunked), to_dev(d["lut"]), to_dev(d["x"]), out)
+    finally:
+        rptc_kernels.set_reference_quirks(False)
+    w16 = o.decode(chunked, d["lut"], n, code=o.CODE_B, S=S, layout=o.LAYOUT_CHUNKED, quirk=o.QUIRK_K2_LANE0_CARRY)
+    exact = o.matvec_exact(w16, o.permute_x_k2(d["x"])[None])[0]
+    scale = np.linalg.norm(w16.astype(np.float64), axis=1) * np.linalg.norm(d["x"].astype(np.float64))
+    ours = out.float().cpu().numpy().astype(np.float64)
+    assert (np.abs(ours - exact) <= 2e-3 * scale + 1e-3 * np.abs(exact) + 1e-3).all()
+    # the reference accumulates in fp16 throughout: it must sit within ITS error band of the same exact product
+    assert (np.abs(ref_out - exact) <= 3e-2 * scale).all()
+    assert np.abs(ours - exact).mean() <= np.abs(ref_out - exact).mean()
+
+
+def test_reference_transposed_matvec_as_written_pins_oracle(tmp_path):
+    m, n = 256, 1024
+    d = _run_reference("matvec_t_16", m, n, 5, tmp_path)
+    um = o.from_rowmajor(d["words"], o.LAYOUT_UNITMAJOR)
+    emu = o.matvec_k3_as_written(um, d["lut"], d["x"], d["init"]).astype(np.float64)
+    ref_out = d["out"].astype(np.float64)
+    ulp = np.maximum(np.abs(ref_out), 1.0) * 2.0**-10
+    assert (np.abs(emu - ref_out) <= 2 * ulp).all()
+
+
+def test_legacy_fused_matvec_strict_against_oracle():
+    import rptc_kernels
+    rng = np.random.default_rng(81)
+    m, n = 256, 8192
+    words = rng.integers(0, 2**32, (m, n // 16), dtype=np.uint64).astype(np.uint32)
+    chunked = o.from_rowmajor(words, o.LAYOUT_CHUNKED)
+    x = rng.standard_normal(n).astype(np.float16)
+    for S, names in ((8, ("decompress_matvec_16_8_1", "decompress_matvec_20_8_1")),
+                     (6, ("decompress_matvec_16_6_1", "decompress_matvec_20_6_1"))):
+        lut = rng.standard_normal(2 << S).astype(np.float16)
+        w16 = o.decode(words, lut, n, code=o.CODE_B, S=S)
+        exact = o.matvec_exact(w16, o.permute_x_k2(x)[None])[0]
+        scale = np.linalg.norm(w16.astype(np.float64), axis=1) * np.linalg.norm(x.astype(np.float64))
+        for name in names:
+            out = torch.full((m,), 3.0, dtype=torch.float16, device="cuda")     # overwritten, not accumulated
+            ms = getattr(rptc_kernels, name)(to_dev(chunked), to_dev(lut), to_dev(x), out)
+            assert ms > 0
+            err = np.abs(out.float().cpu().numpy() - exact)
+            assert (err <= 2e-3 * scale + 1e-3 * np.abs(exact) + 1e-3).all()
+
+
+@pytest.mark.parametrize("L", [16, 14])
+def test_legacy_transposed_matvec_intended_semantics(L):
+    import rptc_kernels
+    rng = np.random.default_rng(91 + L)
+    m, n = 256, 4096
+    words = rng.integers(0, 2**32, (m, n // 16), dtype=np.uint64).astype(np.uint32)
+    um = o.from_rowmajor(words, o.LAYOUT_UNITMAJOR)
+    lut = rng.standard_normal(1 << L).astype(np.float16)
+    x = rng.standard_normal(n).astype(np.float16)
+    init = rng.standard_normal(m).astype(np.float16)
+    out = to_dev(init.copy())
+    fn = getattr(rptc_kernels, f"decompress_matvec_t_{L}")
+    fn(to_dev(um), to_dev(lut), to_dev(x), out)
+    w16 = o.decode(words, lut, n, L=L)
+    exact = o.matvec_exact(w16, x[None])[0] + init.astype(np.float64)      # out is accumulated into (inference_t.cu:170-171)
+    scale = np.linalg.norm(w16.astype(np.float64), axis=1) * np.linalg.norm(x.astype(np.float64))
+    err = np.abs(out.float().cpu().numpy() - exact)
+    assert (err <= 2e-3 * scale + 2e-3 * np.abs(exact) + 2e-3).all()
+
+
+def test_legacy_argument_errors():
+    import rptc_kernels
+    cb = torch.zeros(65536, dtype=torch.float16, device="cuda")
+    comp = torch.zeros((32, 128), dtype=torch.int32, device="cuda")
+    out = torch.zeros((32, 2048), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        rptc_kernels.decompress(comp.cpu(), cb, out)                     # CHECK_CUDA
+    with pytest.raises(RuntimeError):
+        rptc_kernels.decompress(comp.t(), cb, out)                       # CHECK_CONTIGUOUS
+    with pytest.raises(RuntimeError):
+        rptc_kernels.decompress(comp, cb[:100], out)                     # codebook size
+    with pytest.raises(RuntimeError):
+        rptc_kernels.decompress(comp, cb, out.float())                   # dtype
+    with pytest.raises(RuntimeError):
+        rptc_kernels.decompress_matvec_16_8_1(torch.zeros((1, 32, 64), dtype=torch.int32, device="cuda"),
+                                              cb[:512], out[0], out[:, 0].contiguous())
