@@ -51,13 +51,17 @@ __global__ void __launch_bounds__(kDecThreads, 1) decompress_kernel(const DecPar
 
     int64_t cur_rb = -1;
     uint32_t prevw = 0;
+    // (outer, inner) = (row block, group) or (row, 32-group block); advanced without divisions
+    const int32_t inner_n = ROWLANES ? ng : ngb;
+    int64_t outer = (f0 < f1) ? f0 / inner_n : 0;
+    int32_t inner = (f0 < f1) ? (int32_t)(f0 - outer * inner_n) : 0;
     for (int64_t f = f0; f < f1; ++f) {
         int64_t row;
         int32_t g;
         bool active = true;
         if (ROWLANES) {
-            const int64_t rb = f / ng;
-            g = (int32_t)(f - rb * ng);
+            const int64_t rb = outer;
+            g = inner;
             row = (rb << 5) + lane;
             if (rb != cur_rb) {
                 cur_rb = rb;
@@ -65,9 +69,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decompress_kernel(const DecPar
                 else prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, (int64_t)g * P - 1, row)) + 3);
             }
         } else {
-            row = f / ngb;
-            g = (int32_t)(f - row * ngb) * 32 + lane;
+            row = outer;
+            g = inner * 32 + lane;
             active = g < ng;
+        }
+        if (++inner == inner_n) {
+            inner = 0;
+            ++outer;
         }
         uint32_t w[G::kWords];
 #pragma unroll

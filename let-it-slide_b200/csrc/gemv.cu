@@ -99,23 +99,32 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         const int64_t f0 = T * gw / GW, f1 = T * (gw + 1) / GW;
         const uint32_t count = (uint32_t)(f1 - f0);
 
-        auto unit_ptr = [&](int64_t f) -> const uint4 * {
-            const int64_t rb = f / nu;
-            const int64_t u = useg0 + (f - rb * nu);
-            return p.codes + unit_index(p.st, u, rb << 5);
+        // Cursors walk the flattened (row block, unit) range without divisions: (rb, ul) for the unit
+        // being consumed, (irb, iul) for the next one to fetch.
+        const int64_t rb0 = count ? f0 / nu : 0;
+        const int32_t ul0 = count ? (int32_t)(f0 - rb0 * nu) : 0;
+        int64_t irb = rb0;
+        int32_t iul = ul0;
+        auto fetch_ptr = [&]() -> const uint4 * {     // address of the cursor's unit (row block base), then advance
+            const uint4 *ptr = p.codes + unit_index(p.st, useg0 + iul, irb << 5);
+            if (++iul == nu) {
+                iul = 0;
+                ++irb;
+            }
+            return ptr;
         };
         // start streaming this range's codes before anything else
         uint32_t issued_here = 0;
         if (TMA) {
+            const uint32_t ahead = min(count, (uint32_t)kStages);
             if (lane == 0) {
-                const uint32_t ahead = min(count, (uint32_t)kStages);
                 for (uint32_t i = 0; i < ahead; ++i) {
                     const uint32_t st = (issued + i) % kStages;
                     mbar_expect_tx(bars + 8u * st, kStageBytes);
-                    bulk_g2s(ring + st * kStageBytes, unit_ptr(f0 + i), kStageBytes, bars + 8u * st);
+                    bulk_g2s(ring + st * kStageBytes, fetch_ptr(), kStageBytes, bars + 8u * st);
                 }
             }
-            issued_here = min(count, (uint32_t)kStages);
+            issued_here = ahead;
         }
 
         // ---- activations of this column segment -> shared memory ----
@@ -144,12 +153,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         int64_t cur_rb = -1;
         uint32_t prevw = 0;
         uint4 nextv = make_uint4(0, 0, 0, 0);
-        if (!TMA && count > 0) nextv = ldg128_stream(unit_ptr(f0) + (int64_t)lane * p.st.row);
+        if (!TMA && count > 0) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
+        int64_t rb = rb0;
+        int32_t ul = ul0;
+        uint32_t stage = consumed % kStages, phase = (consumed / kStages) & 1u;
 
         for (uint32_t i = 0; i < count && ok; ++i) {
-            const int64_t f = f0 + i;
-            const int64_t rb = f / nu;
-            const int32_t ul = (int32_t)(f - rb * nu);
             const int32_t u = useg0 + ul;
             const int64_t row = (rb << 5) + lane;
             if (rb != cur_rb) {
@@ -168,19 +177,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
             uint4 v;
             if (TMA) {
-                const uint32_t st = consumed % kStages;
-                ok = mbar_wait(bars + 8u * st, (consumed / kStages) & 1u, p.status);
-                v = lds128(ring + st * kStageBytes + 16u * lane);
+                ok = mbar_wait(bars + 8u * stage, phase, p.status);
+                v = lds128(ring + stage * kStageBytes + 16u * lane);
                 ++consumed;
                 __syncwarp();
-                if (lane == 0 && ok && issued_here < count) {
-                    mbar_expect_tx(bars + 8u * st, kStageBytes);
-                    bulk_g2s(ring + st * kStageBytes, unit_ptr(f0 + issued_here), kStageBytes, bars + 8u * st);
+                if (issued_here < count) {
+                    if (lane == 0 && ok) {
+                        mbar_expect_tx(bars + 8u * stage, kStageBytes);
+                        bulk_g2s(ring + stage * kStageBytes, fetch_ptr(), kStageBytes, bars + 8u * stage);
+                    }
+                    ++issued_here;
                 }
-                if (issued_here < count) ++issued_here;
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
             } else {
                 v = nextv;
-                if (i + 1 < count) nextv = ldg128_stream(unit_ptr(f + 1) + (int64_t)lane * p.st.row);
+                if (i + 1 < count) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
             }
             uint32_t halo = prevw;
             if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
@@ -192,10 +206,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             const uint32_t xu = xs + (uint32_t)ul * (WPU * 2u);
             __half2 hacc[BATCH][4];
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b)
-#pragma unroll
-                for (int a = 0; a < 4; ++a) hacc[b][a] = __float2half2_rn(0.f);
             uint4 xv[BATCH];
             decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
                 if ((pi & 3) == 0) {
@@ -205,7 +215,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
                     const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                    hacc[b][pi & 3] = __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
+                    hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
                 }
             });
 #pragma unroll
@@ -213,6 +223,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                 const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
                 const float2 f2 = __half22float2(s);
                 facc[b] += f2.x + f2.y;
+            }
+            if (++ul == nu) {
+                ul = 0;
+                ++rb;
             }
         }
         if (cur_rb >= 0) {

@@ -51,33 +51,58 @@ def test_reference_decompress_pins_oracle_and_drop_in(tmp_path):
 
 
 @pytest.mark.parametrize("S", [8, 6])
-def test_reference_fused_matvec_pins_oracle_and_drop_in(tmp_path, S):
-    import rptc_kernels
+def test_reference_fused_matvec_against_oracle_emulation(tmp_path, S):
+    """The fused reference kernel splices table-entry bits into the low 32 bits of a shared-memory
+    pointer and relies on its table starting at a 32 KiB-aligned shared address (inference.cu:206,
+    252-257).  Where the first KiB of the shared window is reserved by the system the table starts at
+    0x400 instead, every lookup lands 8 entries low, and lookups of entries 0..7 read reserved
+    memory.  The test accepts either outcome and says which one it saw: an exact match with the
+    oracle's step-for-step fp16 emulation (then the pin holds), or the displaced-table signature."""
     m, n = 128, 4096
     d = _run_reference(f"matvec_16_{S}_1", m, n, 2 + S, tmp_path)
     ref_out = d["out"].astype(np.float64)
     chunked = o.from_rowmajor(d["words"], o.LAYOUT_CHUNKED)
-    # (1) step-for-step fp16 emulation of the reference kernel (quirk included)
     emu = o.matvec_k2_fp16(chunked, d["lut"], d["x"], S).astype(np.float64)
     ulp = np.maximum(np.abs(ref_out), 1.0) * 2.0**-10
-    assert (np.abs(emu - ref_out) <= 2 * ulp).all(), "oracle's refkernel emulation disagrees with the reference kernel"
-    assert np.mean(emu == ref_out) > 0.9
-    # (2) the drop-in in quirk mode computes the same product with better accumulation
+    if (np.abs(emu - ref_out) <= 2 * ulp).all():
+        assert np.mean(emu == ref_out) > 0.9
+        return
+    pairs = d["lut"].reshape(-1, 2)
+    displaced = np.zeros_like(pairs)
+    displaced[8:] = pairs[:-8]              # entry e now answers with entry e-8; 0..7 are unknown (zero here)
+    emu_d = o.matvec_k2_fp16(chunked, displaced.reshape(-1), d["x"], S).astype(np.float64)
+    corr_plain = np.corrcoef(emu, ref_out)[0, 1]
+    corr_disp = np.corrcoef(emu_d, ref_out)[0, 1]
+    assert corr_disp > 0.9 and corr_disp > corr_plain + 0.3, (corr_plain, corr_disp)
+    pytest.skip(f"reference fused kernel reads its table 1 KiB low on this GPU (corr with displaced-table "
+                f"emulation {corr_disp:.3f}, with the intended table {corr_plain:.3f}); not usable as a pin")
+
+
+@pytest.mark.parametrize("S", [8, 6])
+def test_drop_in_fused_matvec_quirk_mode_against_oracle(S):
+    import rptc_kernels
+    rng = np.random.default_rng(2 + S)
+    m, n = 128, 4096
+    words = rng.integers(0, 2**32, (m, n // 16), dtype=np.uint64).astype(np.uint32)
+    x = rng.standard_normal(n).astype(np.float16)
+    lut = rng.standard_normal(2 << S).astype(np.float16)
+    chunked = o.from_rowmajor(words, o.LAYOUT_CHUNKED)
     out = torch.zeros((m,), dtype=torch.float16, device="cuda")
     fn = getattr(rptc_kernels, f"decompress_matvec_16_{S}_1")
     rptc_kernels.set_reference_quirks(True)
     try:
-        fn(to_dev(chunked), to_dev(d["lut"]), to_dev(d["x"]), out)
+        fn(to_dev(chunked), to_dev(lut), to_dev(x), out)
     finally:
         rptc_kernels.set_reference_quirks(False)
-    w16 = o.decode(chunked, d["lut"], n, code=o.CODE_B, S=S, layout=o.LAYOUT_CHUNKED, quirk=o.QUIRK_K2_LANE0_CARRY)
-    exact = o.matvec_exact(w16, o.permute_x_k2(d["x"])[None])[0]
-    scale = np.linalg.norm(w16.astype(np.float64), axis=1) * np.linalg.norm(d["x"].astype(np.float64))
+    w16 = o.decode(chunked, lut, n, code=o.CODE_B, S=S, layout=o.LAYOUT_CHUNKED, quirk=o.QUIRK_K2_LANE0_CARRY)
+    exact = o.matvec_exact(w16, o.permute_x_k2(x)[None])[0]
+    scale = np.linalg.norm(w16.astype(np.float64), axis=1) * np.linalg.norm(x.astype(np.float64))
     ours = out.float().cpu().numpy().astype(np.float64)
     assert (np.abs(ours - exact) <= 2e-3 * scale + 1e-3 * np.abs(exact) + 1e-3).all()
-    # the reference accumulates in fp16 throughout: it must sit within ITS error band of the same exact product
-    assert (np.abs(ref_out - exact) <= 3e-2 * scale).all()
-    assert np.abs(ours - exact).mean() <= np.abs(ref_out - exact).mean()
+    # the fp16 emulation of the reference's accumulation sits inside a much wider band around the same product
+    emu = o.matvec_k2_fp16(chunked, lut, x, S).astype(np.float64)
+    assert (np.abs(emu - exact) <= 3e-2 * scale).all()
+    assert np.abs(ours - exact).mean() <= np.abs(emu - exact).mean()
 
 
 def test_reference_transposed_matvec_as_written_pins_oracle(tmp_path):
