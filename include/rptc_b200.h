@@ -48,10 +48,13 @@ enum { RPTC_CODE_LUT = 0, RPTC_CODE_HASH = 1, RPTC_CODE_LITE = 2 };
 /* Layouts of the packed words (int32).
  *   ROWMAJOR  [m][units*4]            decompress_kernel, inference.cu:53-66
  *   CHUNKED   [units/32][m][32*4]     decompress_matvec_kernel, inference.cu:229
- *   UNITMAJOR [units][m][4]           decompress_matvec_t_kernel, inference_t.cu:116 — the native,
- *                                     fastest layout: 32 consecutive rows of one unit are 512 contiguous
- *                                     bytes, which one warp streams as coalesced 128-bit loads. */
-enum { RPTC_LAYOUT_ROWMAJOR = 0, RPTC_LAYOUT_CHUNKED = 1, RPTC_LAYOUT_UNITMAJOR = 2 };
+ *   UNITMAJOR [units][m][4]           decompress_matvec_t_kernel, inference_t.cu:116
+ *   TILED     [m/32][units][32][4]    the native layout of this library (no reference counterpart):
+ *                                     the 32 rows of one unit are 512 contiguous bytes that one warp takes
+ *                                     as coalesced 128-bit loads, and consecutive units of a 32-row block
+ *                                     follow one another, so a warp's whole share of the matrix is one
+ *                                     linear stream for the bulk-copy (TMA) engine. */
+enum { RPTC_LAYOUT_ROWMAJOR = 0, RPTC_LAYOUT_CHUNKED = 1, RPTC_LAYOUT_UNITMAJOR = 2, RPTC_LAYOUT_TILED = 3 };
 
 /* Optional reproduction of two defects of the reference kernels, so that results can be compared
  * element for element with the reference binary.  0 = the self-consistent stream of rptc.py. */
@@ -119,7 +122,7 @@ int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t 
  * y[t][row] = fp16( sum_c x[t][c] * W[row][c] ),  x fp16 [tokens][ld_x], y fp16 [tokens][ld_y].
  * No reference counterpart (the reference has batch-1 kernels only); the equivalent reference
  * computation is decompress followed by a dense matmul (rptc_kernels/tests/test_decompress.py:41-43).
- * UNITMAJOR layout, K = 2 or 4, m % 128 == 0, n % 64 == 0. */
+ * TILED layout, K = 2 or 4, m % 128 == 0, n % 64 == 0. */
 int rptc_gemm(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x, void *y,
               int64_t ld_y, int64_t m, int64_t n, int64_t tokens, const rptc_format *fmt, rptc_stream_t stream);
 

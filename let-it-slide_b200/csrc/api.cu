@@ -57,7 +57,7 @@ unsigned int *device_status_word() {
 int check_format(const rptc_format *f) {
     if (!f) return RPTC_ERR_ARG;
     if (f->code < RPTC_CODE_LUT || f->code > RPTC_CODE_LITE) return RPTC_ERR_ARG;
-    if (f->layout < RPTC_LAYOUT_ROWMAJOR || f->layout > RPTC_LAYOUT_UNITMAJOR) return RPTC_ERR_ARG;
+    if (f->layout < RPTC_LAYOUT_ROWMAJOR || f->layout > RPTC_LAYOUT_TILED) return RPTC_ERR_ARG;
     if (f->quirk < RPTC_QUIRK_NONE || f->quirk > RPTC_QUIRK_K2_LANE0_CARRY) return RPTC_ERR_ARG;
     if (f->K < 2 || f->K > 4) return RPTC_ERR_ARG;
     if (f->L < 1 || f->L > 16) return RPTC_ERR_ARG;

@@ -75,11 +75,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after raising the device status word) when the limit runs out, so
 // that the caller can stop issuing work, drain what is in flight and return.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int *status) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, unsigned int *status) {
+#pragma unroll 1
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
     atomicExch(status, 1u);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, status);
 }
 // 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // Both addresses and the size must be multiples of 16 bytes.
@@ -98,6 +103,12 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+// HASH-table lookup: the table's window address is a literal folded into the load's address field.
+__device__ __forceinline__ uint32_t lds32_hash(uint32_t offset) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1 + 65536];" : "=r"(v) : "r"(offset));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -114,19 +125,21 @@ __device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpre
 __device__ __forceinline__ uint32_t half2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 
 // ---- packed-code addressing -------------------------------------------------------------------
-// Index (in 128-bit units) of unit u of row r:  (u >> 5) * hi + (u & 31) * lo + r * row.
+// Index (in 128-bit units) of unit u of row r:
+//   (u >> 5) * hi + (u & 31) * lo + (r >> 5) * rb + (r & 31) * row.
 struct UnitStrides {
-    int64_t hi, lo, row;
+    int64_t hi, lo, rb, row;
 };
 __host__ __device__ inline UnitStrides unit_strides(int layout, int64_t m, int64_t n_units) {
     switch (layout) {
-        case RPTC_LAYOUT_ROWMAJOR: return {32, 1, n_units};
-        case RPTC_LAYOUT_CHUNKED: return {32 * m, 1, 32};
-        default: return {32 * m, m, 1};
+        case RPTC_LAYOUT_ROWMAJOR: return {32, 1, 32 * n_units, n_units};
+        case RPTC_LAYOUT_CHUNKED: return {32 * m, 1, 32 * 32, 32};
+        case RPTC_LAYOUT_UNITMAJOR: return {32 * m, m, 32, 1};
+        default: return {32 * 32, 32, 32 * n_units, 1};     // TILED
     }
 }
 __device__ __forceinline__ int64_t unit_index(const UnitStrides &s, int64_t u, int64_t r) {
-    return (u >> 5) * s.hi + (u & 31) * s.lo + r * s.row;
+    return (u >> 5) * s.hi + (u & 31) * s.lo + (r >> 5) * s.rb + (r & 31) * s.row;
 }
 
 // ---- shared-memory lookup tables ---------------------------------------------------------------
@@ -137,11 +150,12 @@ __device__ __forceinline__ int64_t unit_index(const UnitStrides &s, int64_t u, i
 //              window so that (hash & 0xFF00) | 4*lane is the whole address computation.
 // LITE code  : 2^S rows of 128 bytes, the pair of entry e at byte 4*lane of row e.
 constexpr uint32_t kHashLutBytes = 65536;
-constexpr uint32_t kHashLutWindow = 0x10000;   // shared-window address the HASH table is placed at
+constexpr uint32_t kHashLutWindow = 0x10000;   // shared-window address the HASH table is placed at (literal in lds32_hash)
+static_assert(kHashLutWindow == 65536, "lds32_hash spells this address out");
 
 template <int CODE>
 struct Lut {
-    uint32_t base;   // LUT: table address.  HASH: kHashLutWindow | 4*lane.  LITE: table address + 4*lane.
+    uint32_t base;   // LUT: table address.  HASH: 4*lane (the window address is a literal in the load).  LITE: table address + 4*lane.
     uint32_t mask;   // LUT: 2^L-1.  LITE: 2^S-1.
     uint32_t shift;  // LITE: L-S.
 };
@@ -154,30 +168,46 @@ __device__ __forceinline__ uint32_t lut_bytes(int L, int S) {
 }
 
 // Fills the table from the global codebook.  All threads of the CTA take part; the caller
-// synchronises afterwards.
+// synchronises afterwards.  Global loads are issued in independent batches (one coalesced load
+// per warp feeding up to 32 shared-memory rows through shuffles) so that the prologue costs about
+// one L2 round trip rather than one per row.
 template <int CODE>
 __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restrict__ g, int L, int S) {
-    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
     if (CODE == RPTC_CODE_LUT) {
         const uint4 *src = reinterpret_cast<const uint4 *>(g);
-        for (int i = tid; i < (1 << L) / 8; i += nt) {
-            uint4 v = __ldg(src + i);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16u * i), "r"(v.x), "r"(v.y), "r"(v.z),
-                         "r"(v.w)
-                         : "memory");
-        }
-    } else if (CODE == RPTC_CODE_HASH) {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
-        for (int e = tid >> 5; e < 256; e += nt >> 5) {
-            uint32_t v = __ldg(src + (e & ((1 << S) - 1)));
-            v = (v & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + 256u * e + 4u * lane), "r"(v) : "memory");
+        const int total = (1 << L) / 8;
+        for (int i0 = tid; i0 < total; i0 += 4 * nt) {
+            uint4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (i0 + k * nt < total) v[k] = __ldg(src + i0 + k * nt);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (i0 + k * nt < total)
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16u * (i0 + k * nt)), "r"(v[k].x),
+                                 "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                 : "memory");
         }
     } else {
         const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
-        for (int e = tid >> 5; e < (1 << S); e += nt >> 5) {
-            uint32_t v = __ldg(src + e);
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + 128u * e + 4u * lane), "r"(v) : "memory");
+        const int rows = (CODE == RPTC_CODE_HASH) ? 256 : (1 << S);
+        const uint32_t row_bytes = (CODE == RPTC_CODE_HASH) ? 256u : 128u;
+        const int smask = (1 << S) - 1;
+        int per = (rows + nw - 1) / nw;           // rows per warp per pass, at most 32
+        if (per > 32) per = 32;
+        for (int base = warp * per; base < rows; base += nw * per) {
+            uint32_t mine = 0;
+            if (lane < per && base + lane < rows) mine = __ldg(src + ((base + lane) & smask));
+#pragma unroll 8
+            for (int k = 0; k < per; ++k) {
+                uint32_t v = __shfl_sync(0xFFFFFFFFu, mine, k);
+                const int e = base + k;
+                if (e < rows) {
+                    if (CODE == RPTC_CODE_HASH) v = (v & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + row_bytes * e + 4u * lane), "r"(v) : "memory");
+                }
+            }
         }
     }
 }
@@ -191,7 +221,7 @@ __device__ __forceinline__ Lut<CODE> lut_view(uint32_t table, int L, int S) {
         v.mask = (1u << L) - 1u;
         v.shift = 0;
     } else if (CODE == RPTC_CODE_HASH) {
-        v.base = table | lane4;
+        v.base = lane4;
         v.mask = 0;
         v.shift = 0;
     } else {
@@ -251,7 +281,7 @@ __device__ __forceinline__ void decode_group(const uint32_t (&w)[GroupShape<K>::
             const uint32_t t = R[o] >> sh;
             if (CODE == RPTC_CODE_HASH) {
                 const uint32_t h = t * t + t;
-                emit(p, u32_as_half2(lds32((h & 0xFF00u) | lut.base)));
+                emit(p, u32_as_half2(lds32_hash((h & 0xFF00u) | lut.base)));
             } else {
                 // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
                 // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.

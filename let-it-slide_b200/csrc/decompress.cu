@@ -1,20 +1,23 @@
 // Standalone RPTC decompress: packed trellis codes -> dense fp16 [m][n] on sm_100a.
 //
-// A persistent grid of one 1024-thread CTA per SM keeps the lookup table in shared memory for the
+// A persistent grid of one 512-thread CTA per SM keeps the lookup table in shared memory for the
 // whole launch.  Work is cut into warp tasks of 32 "groups" (a group is one 128-bit unit, or three
 // units when K = 3) and the flattened task list is split evenly over all warps.  Two lane mappings:
-//   ROWLANES  (UNITMAJOR codes): lane = row of a 32-row block, the warp walks along the rows group
+//   ROWLANES  (TILED / UNITMAJOR codes): lane = row of a 32-row block, the warp walks along the rows group
 //             by group; the load of a group is one coalesced 512-byte request and the 16 bits of
 //             history come from the previous iteration's last word.
 //   !ROWLANES (ROWMAJOR / CHUNKED codes): lane = one of 32 consecutive groups of one row; history
 //             comes from the lane to the left by shuffle.
-// Each lane decodes its group in registers (funnel-shift windows -> table lookups) and writes its
-// contiguous run of fp16 weights with 128-bit stores, four pairs at a time.
+// Each lane decodes its group in registers (funnel-shift windows -> table lookups) into its own row
+// of a per-warp shared-memory tile (XOR-swizzled in 16-byte chunks, so the writes are conflict
+// free); the warp then copies the tile out with 128-bit stores in which every group of lanes covers
+// whole 128-byte lines of the output.  Output is 8x (K=2) the input, so this kernel lives or dies by
+// the store pattern.
 #include "common.cuh"
 
 namespace rptc {
 
-constexpr int kDecThreads = 1024;
+constexpr int kDecThreads = 512;
 constexpr int kDecWarps = kDecThreads / 32;
 
 struct DecParams {
@@ -30,24 +33,46 @@ struct DecParams {
     unsigned int *status;
 };
 
+template <int K>
+struct DecTile {
+    static constexpr int kRowBytes = 2 * GroupShape<K>::kWeights;      // 128, 256, 64
+    static constexpr int kChunks = kRowBytes / 16;                     // 8, 16, 4
+    static constexpr int kBytes = 32 * kRowBytes;
+    // 16-byte chunk c of tile row r lives at chunk swz(r, c) of that row
+    __device__ static __forceinline__ uint32_t swz(uint32_t r, uint32_t c) {
+        return kChunks == 4 ? (c ^ ((r >> 1) & 3u)) : (c ^ (r & 7u));
+    }
+};
+
 template <int CODE, int K, bool ROWLANES>
 __global__ void __launch_bounds__(kDecThreads, 1) decompress_kernel(const DecParams p) {
     using G = GroupShape<K>;
+    using T = DecTile<K>;
     constexpr int P = G::P;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t lut_tab = (CODE == RPTC_CODE_HASH) ? kHashLutWindow : smem_addr(smem_raw);
+    const uint32_t s0 = smem_addr(smem_raw);
+    uint32_t lut_tab, tiles;
+    if (CODE == RPTC_CODE_HASH) {
+        lut_tab = kHashLutWindow;
+        tiles = kHashLutWindow + kHashLutBytes;
+    } else {
+        lut_tab = s0;
+        tiles = s0 + lut_bytes<CODE>(p.L, p.S);
+    }
+    const uint32_t tile = tiles + (uint32_t)warp * T::kBytes;
     lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
     const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     __syncthreads();
 
-    const int64_t gw = (int64_t)blockIdx.x * kDecWarps + warp, GW = (int64_t)gridDim.x * kDecWarps;
+    const int nwarps = blockDim.x >> 5;
+    const int64_t gw = (int64_t)blockIdx.x * nwarps + warp, GW = (int64_t)gridDim.x * nwarps;
     const int32_t ng = p.n_groups;
     const int32_t ngb = (ng + 31) >> 5;                                   // 32-group blocks per row (!ROWLANES)
-    const int64_t T = ROWLANES ? (p.m >> 5) * (int64_t)ng : p.m * (int64_t)ngb;
-    const int64_t f0 = T * gw / GW, f1 = T * (gw + 1) / GW;
+    const int64_t Ttot = ROWLANES ? (p.m >> 5) * (int64_t)ng : p.m * (int64_t)ngb;
+    const int64_t f0 = Ttot * gw / GW, f1 = Ttot * (gw + 1) / GW;
 
     int64_t cur_rb = -1;
     uint32_t prevw = 0;
@@ -55,35 +80,47 @@ __global__ void __launch_bounds__(kDecThreads, 1) decompress_kernel(const DecPar
     const int32_t inner_n = ROWLANES ? ng : ngb;
     int64_t outer = (f0 < f1) ? f0 / inner_n : 0;
     int32_t inner = (f0 < f1) ? (int32_t)(f0 - outer * inner_n) : 0;
+
+    auto load_group = [&](int64_t o, int32_t in, uint32_t (&w)[G::kWords]) {
+        const int64_t row = ROWLANES ? (o << 5) + lane : o;
+        const int32_t g = ROWLANES ? in : in * 32 + lane;
+#pragma unroll
+        for (int k = 0; k < P; ++k) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (g < ng) v = ldg128_stream(p.codes + unit_index(p.st, (int64_t)g * P + k, row));
+            w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
+        }
+    };
+    uint32_t wnext[G::kWords];
+    if (f0 < f1) load_group(outer, inner, wnext);
+
     for (int64_t f = f0; f < f1; ++f) {
+        const int64_t o = outer;
+        const int32_t in = inner;
         int64_t row;
         int32_t g;
-        bool active = true;
         if (ROWLANES) {
-            const int64_t rb = outer;
-            g = inner;
-            row = (rb << 5) + lane;
-            if (rb != cur_rb) {
-                cur_rb = rb;
+            g = in;
+            row = (o << 5) + lane;
+            if (o != cur_rb) {
+                cur_rb = o;
                 if (g == 0) prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
                 else prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, (int64_t)g * P - 1, row)) + 3);
             }
         } else {
-            row = outer;
-            g = inner * 32 + lane;
-            active = g < ng;
+            row = o;
+            g = in * 32 + lane;
         }
+        const bool active = g < ng;
         if (++inner == inner_n) {
             inner = 0;
             ++outer;
         }
         uint32_t w[G::kWords];
 #pragma unroll
-        for (int k = 0; k < P; ++k) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (active) v = ldg128_stream(p.codes + unit_index(p.st, (int64_t)g * P + k, row));
-            w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
-        }
+        for (int k = 0; k < G::kWords; ++k) w[k] = wnext[k];
+        if (f + 1 < f1) load_group(outer, inner, wnext);       // next task's codes are in flight while this one decodes
+
         const uint32_t lastw = w[G::kWords - 1];
         if (!ROWLANES) {
             prevw = __shfl_up_sync(0xFFFFFFFFu, lastw, 1);
@@ -98,30 +135,58 @@ __global__ void __launch_bounds__(kDecThreads, 1) decompress_kernel(const DecPar
             else if (g > 0) halo = prevw >> 16;
         }
         if (ROWLANES) prevw = lastw;
-        if (!active) continue;
 
-        __half *dst = p.out + row * p.ld_out + (int64_t)g * G::kWeights;
-        uint32_t buf[4];
-        decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
-            buf[pi & 3] = half2_as_u32(wp);
-            if ((pi & 3) == 3) {
-                asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 2 * (pi - 3)), "r"(buf[0]), "r"(buf[1]),
-                             "r"(buf[2]), "r"(buf[3])
-                             : "memory");
+        // decode into this lane's row of the tile
+        if (active) {
+            const uint32_t my_row = tile + (uint32_t)lane * T::kRowBytes;
+            uint32_t buf[4];
+            decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                buf[pi & 3] = half2_as_u32(wp);
+                if ((pi & 3) == 3) {
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(my_row + 16u * T::swz(lane, pi >> 2)), "r"(buf[0]),
+                                 "r"(buf[1]), "r"(buf[2]), "r"(buf[3])
+                                 : "memory");
+                }
+            });
+        }
+        __syncwarp();
+        // copy the tile out: chunk q = i*32 + lane  ->  tile row q / kChunks, chunk q % kChunks
+#pragma unroll
+        for (int i = 0; i < T::kChunks; ++i) {
+            const uint32_t q = (uint32_t)i * 32u + lane;
+            const uint32_t r = q / T::kChunks, c = q % T::kChunks;
+            __half *dst;
+            bool ok;
+            if (ROWLANES) {
+                dst = p.out + ((o << 5) + r) * p.ld_out + (int64_t)g * G::kWeights + 8 * c;
+                ok = true;
+            } else {
+                const int32_t gr = in * 32 + (int32_t)r;
+                dst = p.out + row * p.ld_out + (int64_t)gr * G::kWeights + 8 * c;
+                ok = gr < ng;
             }
-        });
+            if (ok) {
+                const uint4 v = lds128(tile + r * T::kRowBytes + 16u * T::swz(r, c));
+                asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            }
+        }
+        __syncwarp();
     }
 }
 
+// `smem` is the table's share; the per-warp tiles are added here, with fewer warps when they do not fit.
 template <int CODE, int K, bool ROWLANES>
 static int launch_dec(const DecParams &p, size_t smem, cudaStream_t stream) {
+    int threads = kDecThreads;
+    while (threads > 64 && smem + size_t(threads / 32) * DecTile<K>::kBytes > 226 * 1024) threads >>= 1;
+    smem += size_t(threads / 32) * DecTile<K>::kBytes;
     static bool configured = false;
     auto kern = decompress_kernel<CODE, K, ROWLANES>;
     if (!configured) {
         RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
-    return launch(kern, dim3(num_sms()), dim3(kDecThreads), smem, stream, p);
+    return launch(kern, dim3(num_sms()), dim3(threads), smem, stream, p);
 }
 
 template <int CODE, int K>
@@ -165,7 +230,7 @@ extern "C" int rptc_decompress(const void *codes, const void *lut, const uint32_
     p.quirk = fmt->quirk;
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
-    const bool rowlanes = fmt->layout == RPTC_LAYOUT_UNITMAJOR;
+    const bool rowlanes = fmt->layout == RPTC_LAYOUT_UNITMAJOR || fmt->layout == RPTC_LAYOUT_TILED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     size_t smem;
     switch (fmt->code) {

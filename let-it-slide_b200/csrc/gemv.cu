@@ -3,25 +3,29 @@
 // Work decomposition.  Rows are taken 32 at a time (a "row block": lane l owns row 32*rb + l) and a
 // row's stream is cut into 128-bit units.  The (row block, unit) grid is flattened row-block-major
 // and cut into equal contiguous ranges, one per warp of a persistent grid of one 512-thread CTA per
-// SM, so that every SM gets the same number of units whatever m and n are.  In the native UNITMAJOR
-// layout the 32 rows of one unit are 512 contiguous bytes: lane 0 of each warp streams them into a
-// private shared-memory ring with 1-D bulk (TMA) copies completing on mbarriers, several units
-// ahead, and every lane then takes its own 128 bits with one conflict-free LDS.128.  The 16-bit
-// shift-register windows are rebuilt in registers with funnel shifts, hashed / looked up in a
-// bank-replicated shared-memory table, and multiplied into half2 accumulators that are flushed to
-// fp32 every unit.  A warp walks along its rows, so the 16 bits of history a unit needs are simply
-// the last word of the unit before it (one extra 32-bit load at the start of a range).  Partial
-// row sums are added to the fp32 accumulator in global memory with atomics.
+// SM, so that every SM gets the same number of units whatever m and n are.  In the native TILED
+// layout that flattened order is the memory order: a warp's range is one linear stream of 512-byte
+// units.  Lane 0 of each warp streams it into a private shared-memory ring with 1-D bulk (TMA)
+// copies of two units each, completing on mbarriers, several units ahead; every lane then takes its
+// own 128 bits with one conflict-free LDS.128.  The 16-bit shift-register windows are rebuilt in
+// registers with funnel shifts, hashed / looked up in a bank-replicated shared-memory table, and
+// multiplied into half2 accumulators that are flushed to fp32 every unit.  A warp walks along its
+// rows, so the 16 bits of history a unit needs are simply the last word of the unit before it (one
+// extra 32-bit load at the start of a run).  Partial row sums are added to the fp32 accumulator in
+// global memory with atomics.
 //
 // Activations are staged once per CTA in shared memory and read back as warp-broadcast LDS.128.
+// Other layouts (and the reference-quirk modes) take a plain 128-bit-load path in the same kernel.
 #include "common.cuh"
 
 namespace rptc {
 
 constexpr int kGemvThreads = 512;
 constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kStages = 6;                       // ring depth per warp (units in flight)
-constexpr uint32_t kStageBytes = 512;
+constexpr int kStages = 3;                       // ring depth per warp
+constexpr int kStageUnits = 2;                   // units per bulk copy
+constexpr uint32_t kUnitBytes = 512;             // 32 rows x 128 bits
+constexpr uint32_t kStageBytes = kStageUnits * kUnitBytes;
 constexpr uint32_t kBarBytes = 1024;             // kGemvWarps * kStages * 8 <= 1024
 constexpr uint32_t kRingBytes = kGemvWarps * kStages * kStageBytes;
 static_assert(kGemvWarps * kStages * 8 <= kBarBytes, "barrier area too small");
@@ -89,7 +93,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     const int64_t n_rb = p.m >> 5;
     const int64_t gw = (int64_t)blockIdx.x * kGemvWarps + warp, GW = (int64_t)gridDim.x * kGemvWarps;
     const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;     // bytes of one batch row in shared memory
-    uint32_t issued = 0, consumed = 0;      // per-warp ring counters (monotonic over the whole kernel)
+    uint32_t consumed = 0;                  // stages this warp has used up (monotonic over the whole kernel)
     bool ok = true;
     bool waited_prior = false;
 
@@ -99,33 +103,46 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         const int64_t f0 = T * gw / GW, f1 = T * (gw + 1) / GW;
         const uint32_t count = (uint32_t)(f1 - f0);
 
-        // Cursors walk the flattened (row block, unit) range without divisions: (rb, ul) for the unit
-        // being consumed, (irb, iul) for the next one to fetch.
         const int64_t rb0 = count ? f0 / nu : 0;
         const int32_t ul0 = count ? (int32_t)(f0 - rb0 * nu) : 0;
-        int64_t irb = rb0;
-        int32_t iul = ul0;
+        // ---- TMA path: the range is a list of stages of up to kStageUnits units -------------------
+        const bool linear = nu == p.n_units;          // whole rows in one segment: range is contiguous in memory
+        const uint32_t n_stage = (count + kStageUnits - 1) / kStageUnits;
+        const uint4 *range_base = p.codes + (f0 << 5);      // TILED: unit f of the flattened grid starts at 32*f
+        auto issue_stage = [&](uint32_t k, uint32_t slot) {  // lane 0 only
+            const uint32_t first = k * kStageUnits;
+            const uint32_t units = min((uint32_t)kStageUnits, count - first);
+            const uint32_t bar = bars + 8u * slot, dst = ring + slot * kStageBytes;
+            mbar_expect_tx(bar, units * kUnitBytes);
+            if (linear) {
+                bulk_g2s(dst, range_base + ((int64_t)first << 5), units * kUnitBytes, bar);
+            } else {
+                for (uint32_t q = 0; q < units; ++q) {
+                    const int64_t f = f0 + first + q, rbq = f / nu;
+                    bulk_g2s(dst + q * kUnitBytes, p.codes + unit_index(p.st, useg0 + (f - rbq * nu), rbq << 5), kUnitBytes, bar);
+                }
+            }
+        };
+        uint32_t next_stage = 0;          // next stage to issue
+        uint32_t slot = 0, phase = 0;
+        if (TMA) {
+            slot = consumed % kStages, phase = (consumed / kStages) & 1u;
+            const uint32_t ahead = min(n_stage, (uint32_t)kStages);
+            if (lane == 0)
+                for (uint32_t k = 0; k < ahead; ++k) issue_stage(k, (consumed + k) % kStages);
+            next_stage = ahead;
+        }
+        // ---- plain-load path: cursor over (row block, unit) ----------------------------------------
+        int64_t frb = rb0;
+        int32_t ful = ul0;
         auto fetch_ptr = [&]() -> const uint4 * {     // address of the cursor's unit (row block base), then advance
-            const uint4 *ptr = p.codes + unit_index(p.st, useg0 + iul, irb << 5);
-            if (++iul == nu) {
-                iul = 0;
-                ++irb;
+            const uint4 *ptr = p.codes + unit_index(p.st, useg0 + ful, frb << 5);
+            if (++ful == nu) {
+                ful = 0;
+                ++frb;
             }
             return ptr;
         };
-        // start streaming this range's codes before anything else
-        uint32_t issued_here = 0;
-        if (TMA) {
-            const uint32_t ahead = min(count, (uint32_t)kStages);
-            if (lane == 0) {
-                for (uint32_t i = 0; i < ahead; ++i) {
-                    const uint32_t st = (issued + i) % kStages;
-                    mbar_expect_tx(bars + 8u * st, kStageBytes);
-                    bulk_g2s(ring + st * kStageBytes, fetch_ptr(), kStageBytes, bars + 8u * st);
-                }
-            }
-            issued_here = ahead;
-        }
 
         // ---- activations of this column segment -> shared memory ----
         if (!waited_prior) {
@@ -136,112 +153,138 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         {
             const int64_t col0 = (int64_t)useg0 * WPU;
             const int pairs = nu * PAIRS;
-            for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
-                const int b = i / pairs, s = i - b * pairs;
-                int64_t src = (col0 >> 1) + s;
-                if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
-                asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+            if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+                // 128-bit copies, four loads in flight per thread
+                const int vecs = pairs >> 2;                 // PAIRS is a multiple of 4
+                for (int i0 = threadIdx.x; i0 < BATCH * vecs; i0 += 4 * kGemvThreads) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int i = i0 + k * kGemvThreads;
+                        if (i < BATCH * vecs) {
+                            const int b = i / vecs, s = i - b * vecs;
+                            v[k] = __ldg(reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0) + s);
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int i = i0 + k * kGemvThreads;
+                        if (i < BATCH * vecs) {
+                            const int b = i / vecs, s = i - b * vecs;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs + (uint32_t)b * x_batch_stride + 16u * s),
+                                         "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                         : "memory");
+                        }
+                    }
+                }
+            } else {
+                for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
+                    const int b = i / pairs, s = i - b * pairs;
+                    int64_t src = (col0 >> 1) + s;
+                    if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+                }
             }
         }
         __syncthreads();
 
-        // ---- main loop over this warp's units ----
-        float facc[BATCH];
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
-        int64_t cur_rb = -1;
-        uint32_t prevw = 0;
-        uint4 nextv = make_uint4(0, 0, 0, 0);
-        if (!TMA && count > 0) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
+        // ---- main loop over this warp's units: runs of consecutive units inside one row block ----
         int64_t rb = rb0;
         int32_t ul = ul0;
-        uint32_t stage = consumed % kStages, phase = (consumed / kStages) & 1u;
+        uint32_t i = 0;                                   // index of the unit within the warp's range
+        uint4 nextv = make_uint4(0, 0, 0, 0);
+        if (!TMA && count > 0) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
 
-        for (uint32_t i = 0; i < count && ok; ++i) {
-            const int32_t u = useg0 + ul;
+        while (i < count && ok) {
+            const uint32_t run_end = min(count, i + (uint32_t)(nu - ul));
             const int64_t row = (rb << 5) + lane;
-            if (rb != cur_rb) {
-                if (cur_rb >= 0) {
+            const int32_t u0 = useg0 + ul;
+            uint32_t prevw;
+            if (u0 == 0)
+                prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
+            else
+                prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u0 - 1, row)) + 3);
+            float facc[BATCH];
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
+            uint32_t xu = xs + (uint32_t)ul * (WPU * 2u);
+            int32_t u = u0;
+
+#pragma unroll 1
+            for (; i < run_end; ++i, ++u) {
+                uint4 v;
+                if (TMA) {
+                    const uint32_t sub = i % kStageUnits;
+                    if (sub == 0) {
+                        ok = mbar_wait(bars + 8u * slot, phase, p.status);
+                        if (!ok) break;
+                    }
+                    v = lds128(ring + slot * kStageBytes + sub * kUnitBytes + 16u * lane);
+                    if (sub == kStageUnits - 1 || i + 1 == count) {      // the stage is used up: refill its slot
+                        ++consumed;
+                        __syncwarp();
+                        if (next_stage < n_stage) {
+                            if (lane == 0) issue_stage(next_stage, slot);
+                            ++next_stage;
+                        }
+                        if (++slot == kStages) {
+                            slot = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                } else {
+                    v = nextv;
+                    if (i + 1 < count) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
+                }
+                uint32_t halo = prevw;
+                if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
+                    if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
+                        if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
+                        else if (u > 0) halo = prevw >> 16;
+                    }
+                }
+                prevw = v.w;
+
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                __half2 hacc[BATCH][4];
+                uint4 xv[BATCH];
+                decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                    if ((pi & 3) == 0) {
+#pragma unroll
+                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                    }
 #pragma unroll
                     for (int b = 0; b < BATCH; ++b) {
-                        atomicAdd(p.acc + (int64_t)b * p.ld_acc + (cur_rb << 5) + lane, facc[b]);
-                        facc[b] = 0.f;
+                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                        hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
                     }
-                }
-                cur_rb = rb;
-                if (u == 0)
-                    prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
-                else
-                    prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u - 1, row)) + 3);
-            }
-            uint4 v;
-            if (TMA) {
-                ok = mbar_wait(bars + 8u * stage, phase, p.status);
-                v = lds128(ring + stage * kStageBytes + 16u * lane);
-                ++consumed;
-                __syncwarp();
-                if (issued_here < count) {
-                    if (lane == 0 && ok) {
-                        mbar_expect_tx(bars + 8u * stage, kStageBytes);
-                        bulk_g2s(ring + stage * kStageBytes, fetch_ptr(), kStageBytes, bars + 8u * stage);
-                    }
-                    ++issued_here;
-                }
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
-            } else {
-                v = nextv;
-                if (i + 1 < count) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
-            }
-            uint32_t halo = prevw;
-            if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
-                if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
-                else if (u > 0) halo = prevw >> 16;
-            }
-            prevw = v.w;
-
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            const uint32_t xu = xs + (uint32_t)ul * (WPU * 2u);
-            __half2 hacc[BATCH][4];
-            uint4 xv[BATCH];
-            decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
-                if ((pi & 3) == 0) {
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
-                }
+                });
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
-                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                    hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
+                    const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
+                    const float2 f2 = __half22float2(s);
+                    facc[b] += f2.x + f2.y;
                 }
-            });
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) {
-                const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
-                const float2 f2 = __half22float2(s);
-                facc[b] += f2.x + f2.y;
+                xu += WPU * 2u;
             }
-            if (++ul == nu) {
-                ul = 0;
-                ++rb;
-            }
-        }
-        if (cur_rb >= 0) {
 #pragma unroll
-            for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + (cur_rb << 5) + lane, facc[b]);
+            for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row, facc[b]);
+            ul = 0;
+            ++rb;
         }
-        if (TMA) {
-            issued += issued_here;
+        if (TMA && !ok) {
             // After a failed wait: give the copies still in flight a bounded chance to land before
-            // the shared memory they target is released.
-            while (consumed < issued) {
-                const uint32_t st = consumed % kStages;
-                mbar_wait(bars + 8u * st, (consumed / kStages) & 1u, p.status);
-                ++consumed;
+            // the shared memory they target is released, then stop.
+            const uint32_t consumed_here = i / kStageUnits;
+            for (uint32_t k = consumed_here; k < next_stage; ++k) {
+                mbar_wait(bars + 8u * slot, phase, p.status);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
             }
+            break;
         }
     }
     if (!waited_prior) pdl_wait_prior_grids();
@@ -316,7 +359,7 @@ static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in
     p.x_order = x_order;
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
-    const bool tma = f.layout == RPTC_LAYOUT_UNITMAJOR;
+    const bool tma = f.layout == RPTC_LAYOUT_TILED && f.quirk == RPTC_QUIRK_NONE;
 
     // shared-memory plan (must mirror the kernel's)
     const size_t kMaxSmem = 227 * 1024 - 1024;     // leave room for the 1 KiB the system may reserve

@@ -19,9 +19,13 @@ __global__ void repack_kernel(const uint4 *__restrict__ src, UnitStrides ss, uin
         const int64_t chunk = i / (m * 32), rem = i - chunk * (m * 32);
         r = rem >> 5;
         u = chunk * 32 + (rem & 31);
-    } else {
+    } else if (dst_layout == RPTC_LAYOUT_UNITMAJOR) {
         u = i / m;
         r = i - u * m;
+    } else {
+        const int64_t rb = i / (n_units * 32), rem = i - rb * (n_units * 32);
+        u = rem >> 5;
+        r = rb * 32 + (rem & 31);
     }
     dst[i] = src[unit_index(ss, u, r)];
 }
@@ -33,7 +37,7 @@ using namespace rptc;
 extern "C" int rptc_repack(const void *src, int src_layout, void *dst, int dst_layout, int64_t m, int64_t n_units,
                            rptc_stream_t stream) {
     if (!src || !dst || src == dst) return RPTC_ERR_ARG;
-    if (src_layout < 0 || src_layout > 2 || dst_layout < 0 || dst_layout > 2) return RPTC_ERR_ARG;
+    if (src_layout < 0 || src_layout > 3 || dst_layout < 0 || dst_layout > 3) return RPTC_ERR_ARG;
     if (m <= 0 || n_units <= 0 || (m % 32)) return RPTC_ERR_SHAPE;
     if ((src_layout == RPTC_LAYOUT_CHUNKED || dst_layout == RPTC_LAYOUT_CHUNKED) && (n_units % 32)) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return RPTC_ERR_ALIGN;

@@ -14,7 +14,7 @@ _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG, "librptc_b200.so")
 
 CODE_LUT, CODE_HASH, CODE_LITE = 0, 1, 2
-LAYOUT_ROWMAJOR, LAYOUT_CHUNKED, LAYOUT_UNITMAJOR = 0, 1, 2
+LAYOUT_ROWMAJOR, LAYOUT_CHUNKED, LAYOUT_UNITMAJOR, LAYOUT_TILED = 0, 1, 2, 3
 QUIRK_NONE, QUIRK_K1_LANE0_SEED, QUIRK_K2_LANE0_CARRY = 0, 1, 2
 XORDER_NATURAL, XORDER_K2_LEGACY = 0, 1
 
@@ -37,7 +37,7 @@ class Format(ctypes.Structure):
     _fields_ = [("code", ctypes.c_int32), ("K", ctypes.c_int32), ("L", ctypes.c_int32), ("S", ctypes.c_int32),
                 ("layout", ctypes.c_int32), ("quirk", ctypes.c_int32)]
 
-    def __init__(self, code=CODE_HASH, K=2, L=16, S=8, layout=LAYOUT_UNITMAJOR, quirk=QUIRK_NONE):
+    def __init__(self, code=CODE_HASH, K=2, L=16, S=8, layout=LAYOUT_TILED, quirk=QUIRK_NONE):
         super().__init__(code, K, L, S, layout, quirk)
 
     def replace(self, **kw) -> "Format":

@@ -6,7 +6,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import (CODE_HASH, CODE_LITE, CODE_LUT, LAYOUT_CHUNKED, LAYOUT_ROWMAJOR, LAYOUT_UNITMAJOR, XORDER_NATURAL,
+from ._lib import (CODE_HASH, CODE_LITE, CODE_LUT, LAYOUT_CHUNKED, LAYOUT_ROWMAJOR, LAYOUT_TILED, LAYOUT_UNITMAJOR, XORDER_NATURAL,
                    Format, check, lib, ptr, stream_ptr)
 
 
@@ -31,7 +31,9 @@ def codes_shape(m: int, n: int, K: int, layout: int) -> tuple[int, ...]:
         return (m, nu * 4)
     if layout == LAYOUT_CHUNKED:
         return (nu // 32, m, 128)
-    return (nu, m, 4)
+    if layout == LAYOUT_UNITMAJOR:
+        return (nu, m, 4)
+    return (m // 32, nu, 32, 4)
 
 
 def repack(codes: torch.Tensor, src_layout: int, dst_layout: int, m: int, n_units: int) -> torch.Tensor:
@@ -43,8 +45,10 @@ def repack(codes: torch.Tensor, src_layout: int, dst_layout: int, m: int, n_unit
         shape = (m, n_units * 4)
     elif dst_layout == LAYOUT_CHUNKED:
         shape = (n_units // 32, m, 128)
-    else:
+    elif dst_layout == LAYOUT_UNITMAJOR:
         shape = (n_units, m, 4)
+    else:
+        shape = (m // 32, n_units, 32, 4)
     out = torch.empty(shape, dtype=torch.int32, device=codes.device)
     with torch.cuda.device(codes.device):
         check(lib().rptc_repack(ptr(codes), src_layout, ptr(out), dst_layout, m, n_units, stream_ptr()), "rptc_repack")

@@ -25,8 +25,8 @@ Codes (reference file:line each follows):
 Layouts of the packed words (all int32/uint32, 128-bit "units" of 4 words):
   ROWMAJOR  [m, n_units*4]          inference.cu:53-66   (decompress_kernel)
   CHUNKED   [n_units/32, m, 32*4]   inference.cu:229     (decompress_matvec_kernel; lane-major)
-  UNITMAJOR [n_units, m, 4]         inference_t.cu:116   (decompress_matvec_t_kernel); this is also
-                                                         the native layout of the B200 kernels.
+  UNITMAJOR [n_units, m, 4]         inference_t.cu:116   (decompress_matvec_t_kernel)
+  TILED     [m/32, n_units, 32, 4]  the native layout of the B200 kernels (no reference counterpart)
 """
 from __future__ import annotations
 
@@ -39,6 +39,7 @@ CODE_C = 2   # rptc_lite compute-code, R bits per step, two weights per step
 LAYOUT_ROWMAJOR = 0
 LAYOUT_CHUNKED = 1
 LAYOUT_UNITMAJOR = 2
+LAYOUT_TILED = 3
 
 QUIRK_NONE = 0
 QUIRK_K1_LANE0_SEED = 1    # inference.cu:61-62: lane 0 seeds from the HIGH half of the previous word
@@ -66,6 +67,10 @@ def to_rowmajor(words: np.ndarray, layout: int) -> np.ndarray:
         nu, m, k = w.shape
         assert k == 4
         return np.ascontiguousarray(w.transpose(1, 0, 2).reshape(m, nu * 4))
+    if layout == LAYOUT_TILED:
+        nrb, nu, lanes, k = w.shape
+        assert lanes == 32 and k == 4
+        return np.ascontiguousarray(w.transpose(0, 2, 1, 3).reshape(nrb * 32, nu * 4))
     raise ValueError(f"unknown layout {layout}")
 
 
@@ -82,6 +87,9 @@ def from_rowmajor(words: np.ndarray, layout: int) -> np.ndarray:
         return np.ascontiguousarray(w.reshape(m, nu // 32, 128).transpose(1, 0, 2))
     if layout == LAYOUT_UNITMAJOR:
         return np.ascontiguousarray(w.reshape(m, nu, 4).transpose(1, 0, 2))
+    if layout == LAYOUT_TILED:
+        assert m % 32 == 0
+        return np.ascontiguousarray(w.reshape(m // 32, 32, nu, 4).transpose(0, 2, 1, 3))
     raise ValueError(f"unknown layout {layout}")
 
 

@@ -15,7 +15,7 @@ CASES = [  # code, K, L, S
 
 
 @pytest.mark.parametrize("code,K,L,S", CASES)
-@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR])
+@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED])
 @pytest.mark.parametrize("m,n", [(32, 2048), (96, 4096), (64, 6144)])
 def test_decompress_bit_exact(code, K, L, S, layout, m, n):
     from rptc_b200 import Format, ops
@@ -32,7 +32,7 @@ def test_decompress_bit_exact(code, K, L, S, layout, m, n):
     ops.device_status()
 
 
-@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_UNITMAJOR])
+@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED])
 def test_decompress_ragged_width_and_carry(layout):
     # n = 11008 (172 units: not a multiple of 32) with a left-shard halo, and a padded output pitch
     from rptc_b200 import Format, ops
@@ -51,7 +51,7 @@ def test_decompress_ragged_width_and_carry(layout):
 
 
 @pytest.mark.parametrize("quirk,code,S", [(o.QUIRK_K1_LANE0_SEED, o.CODE_A, 0), (o.QUIRK_K2_LANE0_CARRY, o.CODE_B, 8)])
-@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR])
+@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED])
 def test_decompress_reference_quirks(quirk, code, S, layout):
     from rptc_b200 import Format, ops
     rng = np.random.default_rng(31 + quirk)
@@ -70,10 +70,10 @@ def test_decompress_full_size_against_c_oracle(m, n, K):
     import c_oracle
     from rptc_b200 import Format, ops
     rng = np.random.default_rng(m + n + K)
-    w = o.from_rowmajor(rand_words(rng, m, n, K), o.LAYOUT_UNITMAJOR)
+    rm = rand_words(rng, m, n, K)
     lut = rand_lut(rng, o.CODE_A)
-    ref = c_oracle.decompress(w, lut, m, n, code=0, K=K, layout=o.LAYOUT_UNITMAJOR)
-    got = ops.decompress(to_dev(w), to_dev(lut), m, n, Format(o.CODE_A, K, 16, 0, o.LAYOUT_UNITMAJOR))
+    ref = c_oracle.decompress(rm, lut, m, n, code=0, K=K, layout=o.LAYOUT_ROWMAJOR)
+    got = ops.decompress(to_dev(o.from_rowmajor(rm, o.LAYOUT_TILED)), to_dev(lut), m, n, Format(o.CODE_A, K, 16, 0, o.LAYOUT_TILED))
     torch.cuda.synchronize()
     assert np.array_equal(bits(got), bits(ref))
 
@@ -84,7 +84,7 @@ def test_repack_round_trip_and_oracle():
     m, nu = 96, 64
     w = rand_words(rng, m, nu * 64, 2)
     d = to_dev(w)
-    for dst in (o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR):
+    for dst in (o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED):
         r = ops.repack(d, o.LAYOUT_ROWMAJOR, dst, m, nu)
         assert np.array_equal(r.cpu().numpy().view(np.uint32), o.from_rowmajor(w, dst))
         back = ops.repack(r, dst, o.LAYOUT_ROWMAJOR, m, nu)
@@ -92,6 +92,8 @@ def test_repack_round_trip_and_oracle():
     c = ops.repack(d, o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, m, nu)
     u = ops.repack(c, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR, m, nu)
     assert np.array_equal(u.cpu().numpy().view(np.uint32), o.from_rowmajor(w, o.LAYOUT_UNITMAJOR))
+    t = ops.repack(u, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED, m, nu)
+    assert np.array_equal(t.cpu().numpy().view(np.uint32), o.from_rowmajor(w, o.LAYOUT_TILED))
 
 
 def test_bad_arguments_raise():

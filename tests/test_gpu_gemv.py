@@ -31,7 +31,7 @@ CASES = [(o.CODE_B, 2, 16, 8), (o.CODE_B, 2, 16, 6), (o.CODE_A, 2, 16, 0), (o.CO
 @pytest.mark.parametrize("code,K,L,S", CASES)
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("m,n", [(64, 2048), (4096, 4096), (352, 11008)])
-def test_gemv_unitmajor(code, K, L, S, batch, m, n):
+def test_gemv_native_layout(code, K, L, S, batch, m, n):
     from rptc_b200 import Format, ops
     if code != o.CODE_B and batch not in (1, 4) :
         pytest.skip("batch sweep runs on the headline code only")
@@ -40,14 +40,14 @@ def test_gemv_unitmajor(code, K, L, S, batch, m, n):
     lut = rand_lut(rng, code, L, S)
     x = rng.standard_normal((batch, n)).astype(np.float16)
     w16 = o.decode(w, lut_for_oracle(lut, code, S), n, code=code, K=K, L=L, S=S)
-    y = ops.gemv(to_dev(o.from_rowmajor(w, o.LAYOUT_UNITMAJOR)), to_dev(lut), to_dev(x), m, n,
-                 Format(code, K, L, S, o.LAYOUT_UNITMAJOR))
+    y = ops.gemv(to_dev(o.from_rowmajor(w, o.LAYOUT_TILED)), to_dev(lut), to_dev(x), m, n,
+                 Format(code, K, L, S, o.LAYOUT_TILED))
     torch.cuda.synchronize()
     ops.device_status()
     _check(y.float().cpu().numpy(), w16, x)
 
 
-@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED])
+@pytest.mark.parametrize("layout", [o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR])
 def test_gemv_legacy_layouts(layout):
     from rptc_b200 import Format, ops
     rng = np.random.default_rng(51 + layout)
@@ -70,14 +70,15 @@ def test_gemv_carry_in_and_column_sharding():
     lut = rand_lut(rng, o.CODE_B, S=8)
     x = rng.standard_normal((2, n)).astype(np.float16)
     w16 = o.decode(w, lut, n, code=o.CODE_B, S=8)
-    um = o.from_rowmajor(w, o.LAYOUT_UNITMAJOR)            # [units, m, 4]
-    half = um.shape[0] // 2
+    nw = w.shape[1]
+    left, right = w[:, : nw // 2], w[:, nw // 2:]           # two column shards of the row-major stream
     acc = torch.zeros((2, m), dtype=torch.float32, device="cuda")
-    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_UNITMAJOR)
+    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
     xd = to_dev(x)
-    ops.gemv_acc(to_dev(um[:half]), to_dev(lut), xd[:, : n // 2], acc, m, n // 2, fmt)
-    carry = np.ascontiguousarray(um[half - 1, :, 3])
-    ops.gemv_acc(to_dev(um[half:]), to_dev(lut), xd[:, n // 2:], acc, m, n // 2, fmt, carry_in=to_dev(carry))
+    ops.gemv_acc(to_dev(o.from_rowmajor(left, o.LAYOUT_TILED)), to_dev(lut), xd[:, : n // 2], acc, m, n // 2, fmt)
+    carry = np.ascontiguousarray(left[:, -1])               # last word of the left shard = the right shard's history
+    ops.gemv_acc(to_dev(o.from_rowmajor(right, o.LAYOUT_TILED)), to_dev(lut), xd[:, n // 2:], acc, m, n // 2, fmt,
+                 carry_in=to_dev(carry))
     torch.cuda.synchronize()
     _check(acc.cpu().numpy(), w16, x)
 
@@ -100,8 +101,8 @@ def test_gemv_all_ones_codebook_known_answer():
     w = rand_words(rng, m, n, 2)
     lut = np.ones(1 << 16, dtype=np.float16)
     x = rng.standard_normal((1, n)).astype(np.float16)
-    y = ops.gemv(to_dev(o.from_rowmajor(w, o.LAYOUT_UNITMAJOR)), to_dev(lut), to_dev(x), m, n,
-                 Format(o.CODE_A, 2, 16, 0, o.LAYOUT_UNITMAJOR))
+    y = ops.gemv(to_dev(o.from_rowmajor(w, o.LAYOUT_TILED)), to_dev(lut), to_dev(x), m, n,
+                 Format(o.CODE_A, 2, 16, 0, o.LAYOUT_TILED))
     s = x.astype(np.float64).sum()
     assert np.allclose(y.float().cpu().numpy(), s, atol=0.25)
 
@@ -112,10 +113,10 @@ def test_gemv_full_size_linearity(m, n):
     # agreement with decompress-then-matmul on the GPU's own bit-exact decompress output
     from rptc_b200 import Format, ops
     g = torch.Generator(device="cuda").manual_seed(m * 7 + n)
-    codes = torch.randint(-2**31, 2**31 - 1, (n // 64, m, 4), dtype=torch.int32, device="cuda", generator=g)
+    codes = torch.randint(-2**31, 2**31 - 1, (m // 32, n // 64, 32, 4), dtype=torch.int32, device="cuda", generator=g)
     lut = torch.randn(512, dtype=torch.float16, device="cuda", generator=g)
     x = torch.randn((2, n), dtype=torch.float16, device="cuda", generator=g)
-    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_UNITMAJOR)
+    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
     y = ops.gemv(codes, lut, x, m, n, fmt).float()
     ysum = ops.gemv(codes, lut, (x[0] + x[1]).unsqueeze(0), m, n, fmt).float()
     dense = ops.decompress(codes, lut, m, n, fmt)

@@ -88,8 +88,10 @@ def test_layout_round_trips_and_quirks():
     rng = np.random.default_rng(9)
     m, nu = 64, 64
     w = rng.integers(0, 2**32, (m, nu * 4), dtype=np.uint64).astype(np.uint32)
-    for lay in (o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR):
+    for lay in (o.LAYOUT_ROWMAJOR, o.LAYOUT_CHUNKED, o.LAYOUT_UNITMAJOR, o.LAYOUT_TILED):
         assert np.array_equal(o.to_rowmajor(o.from_rowmajor(w, lay), lay), w)
+    t = o.from_rowmajor(w, o.LAYOUT_TILED)
+    assert t.shape == (m // 32, nu, 32, 4) and np.array_equal(t[1, 5, 7], w[32 + 7, 20:24])
     lut = rng.standard_normal(1 << 16).astype(np.float16)
     n = nu * 64
     strict = o.decode(w, lut, n)
