@@ -132,9 +132,38 @@ int rptc_gemm(const void *codes, const void *lut, const uint32_t *carry_in, cons
  *   transpose = 0: out = H (s * in) * scale        (activation side)
  *   transpose = 1: out = s * (H in) * scale        (output side)
  *   clear_in  = 1 (fp32 input only): zero the input after reading it.
- * signs: fp16 [n] of +-1, or NULL for all +1.  out: fp16 [rows][ld_out]; may alias an fp16 input. */
+ * signs: fp16 [n] of +-1, or NULL for all +1.  residual: optional fp16 [rows][ld_res] added to the
+ * result (a transformer block's skip connection).  out: fp16 [rows][ld_out]; may alias an fp16 input
+ * or the residual. */
 int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void *out, int64_t ld_out, const void *signs,
-                  int64_t rows, int64_t n, int block, int transpose, float scale, int clear_in, rptc_stream_t stream);
+                  const void *residual, int64_t ld_res, int64_t rows, int64_t n, int block, int transpose, float scale,
+                  int clear_in, rptc_stream_t stream);
+
+/* Fused middle of a gated MLP between two quantised layers.  acc: fp32 [rows][ld_acc] accumulator of the
+ * fused gate-up layer (gate in columns [0,n), up in [n,2n)).  g,u = s_out * (H acc) * scale_out;
+ * out = H (s_in * (silu(g) * u)) * scale_in, fp16 [rows][ld_out].  No reference counterpart. */
+int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64_t ld_out, const void *signs_out, const void *signs_in,
+                         int64_t rows, int64_t n, int block, float scale_out, float scale_in, int clear, rptc_stream_t stream);
+
+/* --- the non-quantised pieces of a Llama-architecture decode step (no reference counterpart: the
+ * reference evaluates models through Hugging Face transformers, quantize_hf.py:230-236) --- */
+
+/* out = x * rsqrt(mean(x^2) + eps) * w, fp16 rows of length n. */
+int rptc_rmsnorm(const void *x, int64_t ld_x, const void *w, void *out, int64_t ld_out, int64_t rows, int64_t n, float eps,
+                 rptc_stream_t stream);
+/* Rotary embedding (rotate-half pairs (i, i+d/2)) of one token per row of qkv = [q heads | k heads | v heads],
+ * q in place, rotated k and v appended to caches [rows][max_pos][hkv][d] at pos[row]. */
+int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, void *kcache, void *vcache, int64_t rows, int hq, int hkv,
+                    int d, int max_pos, float theta, rptc_stream_t stream);
+/* Single-query attention of each row's q heads over cache positions [0, pos[row]]; d must be 128. */
+int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
+                     int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, rptc_stream_t stream);
+/* Dense fp16 matvec y[b] = W x[b] (fp32 accumulation), batch 1..8: the output head, and the dense-bandwidth
+ * probe the reference's tests call `matvec` (rptc_kernels/tests/test_matvec.py:18, not exported by wrapper.cpp). */
+int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,
+                    int batch, rptc_stream_t stream);
+/* out[r] = table[ids[r]], fp16 rows of length n. */
+int rptc_embed(const void *table, const int32_t *ids, void *out, int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream);
 
 #ifdef __cplusplus
 }

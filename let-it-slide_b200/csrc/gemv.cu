@@ -60,6 +60,7 @@ template <int CODE, int K, int BATCH, bool TMA>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;          // weights per unit
     constexpr int PAIRS = WPU / 2;
+    constexpr int GU = TMA ? kStageUnits : 1;      // units per granule (= per ring stage on the TMA path)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t s0 = smem_addr(smem_raw);
@@ -90,59 +91,63 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
     pdl_allow_next_grid();
 
-    const int64_t n_rb = p.m >> 5;
-    const int64_t gw = (int64_t)blockIdx.x * kGemvWarps + warp, GW = (int64_t)gridDim.x * kGemvWarps;
+    const uint32_t n_rb = (uint32_t)(p.m >> 5);
+    const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
     const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;     // bytes of one batch row in shared memory
-    uint32_t consumed = 0;                  // stages this warp has used up (monotonic over the whole kernel)
+    uint32_t slot = 0, phase = 0;           // ring position of the next stage to consume (kept across segments)
     bool ok = true;
     bool waited_prior = false;
 
     for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
         const int32_t nu = min(p.seg_units, p.n_units - useg0);
-        const int64_t T = n_rb * nu;
-        const int64_t f0 = T * gw / GW, f1 = T * (gw + 1) / GW;
-        const uint32_t count = (uint32_t)(f1 - f0);
+        // A granule is GU consecutive units of one row block (the last one of a block may be short).
+        const int32_t gpr = (nu + GU - 1) / GU;                 // granules per row block
+        const int32_t tail_units = nu - (gpr - 1) * GU;         // units in a block's last granule
+        // Balanced contiguous split of the T granules over the GW warps of the grid, in 32-bit arithmetic:
+        // the first T % GW warps take one granule more than the others.
+        const uint32_t T = (uint32_t)n_rb * (uint32_t)gpr;
+        const uint32_t per = T / GW, extra = T - per * GW;
+        const uint32_t g0 = gw * per + min(gw, extra);
+        const uint32_t count = per + (gw < extra ? 1u : 0u);
+        const uint32_t rb0 = count ? g0 / (uint32_t)gpr : 0u;
+        const int32_t gi0 = count ? (int32_t)(g0 - rb0 * (uint32_t)gpr) : 0;
 
-        const int64_t rb0 = count ? f0 / nu : 0;
-        const int32_t ul0 = count ? (int32_t)(f0 - rb0 * nu) : 0;
-        // ---- TMA path: the range is a list of stages of up to kStageUnits units -------------------
-        const bool linear = nu == p.n_units;          // whole rows in one segment: range is contiguous in memory
-        const uint32_t n_stage = (count + kStageUnits - 1) / kStageUnits;
-        const uint4 *range_base = p.codes + (f0 << 5);      // TILED: unit f of the flattened grid starts at 32*f
-        auto issue_stage = [&](uint32_t k, uint32_t slot) {  // lane 0 only
-            const uint32_t first = k * kStageUnits;
-            const uint32_t units = min((uint32_t)kStageUnits, count - first);
-            const uint32_t bar = bars + 8u * slot, dst = ring + slot * kStageBytes;
+        // ---- fetch cursor (used by lane 0 on the TMA path, by every lane on the plain-load path) ----
+        int64_t frb = rb0;
+        int32_t fgi = gi0;
+        const uint4 *fptr = p.codes + unit_index(p.st, useg0 + gi0 * GU, (int64_t)rb0 << 5);
+        const int64_t seg_skip = (int64_t)(p.n_units - nu) << 5;          // TILED: gap between row blocks of a column segment
+        auto issue_stage = [&](uint32_t at_slot) {                        // lane 0, TMA path: one bulk copy per granule
+            const uint32_t units = (fgi == gpr - 1) ? (uint32_t)tail_units : (uint32_t)GU;
+            const uint32_t bar = bars + 8u * at_slot;
             mbar_expect_tx(bar, units * kUnitBytes);
-            if (linear) {
-                bulk_g2s(dst, range_base + ((int64_t)first << 5), units * kUnitBytes, bar);
-            } else {
-                for (uint32_t q = 0; q < units; ++q) {
-                    const int64_t f = f0 + first + q, rbq = f / nu;
-                    bulk_g2s(dst + q * kUnitBytes, p.codes + unit_index(p.st, useg0 + (f - rbq * nu), rbq << 5), kUnitBytes, bar);
-                }
+            bulk_g2s(ring + at_slot * kStageBytes, fptr, units * kUnitBytes, bar);
+            fptr += units << 5;
+            if (++fgi == gpr) {
+                fgi = 0;
+                fptr += seg_skip;
             }
         };
-        uint32_t next_stage = 0;          // next stage to issue
-        uint32_t slot = 0, phase = 0;
-        if (TMA) {
-            slot = consumed % kStages, phase = (consumed / kStages) & 1u;
-            const uint32_t ahead = min(n_stage, (uint32_t)kStages);
-            if (lane == 0)
-                for (uint32_t k = 0; k < ahead; ++k) issue_stage(k, (consumed + k) % kStages);
-            next_stage = ahead;
-        }
-        // ---- plain-load path: cursor over (row block, unit) ----------------------------------------
-        int64_t frb = rb0;
-        int32_t ful = ul0;
-        auto fetch_ptr = [&]() -> const uint4 * {     // address of the cursor's unit (row block base), then advance
-            const uint4 *ptr = p.codes + unit_index(p.st, useg0 + ful, frb << 5);
-            if (++ful == nu) {
-                ful = 0;
+        auto next_unit_ptr = [&]() -> const uint4 * {                     // plain-load path (GU == 1)
+            const uint4 *ptr = p.codes + unit_index(p.st, useg0 + fgi, (frb << 5) + lane);
+            if (++fgi == gpr) {
+                fgi = 0;
                 ++frb;
             }
             return ptr;
         };
+        uint32_t to_issue = count;
+        if (TMA) {
+            const uint32_t ahead = min(count, (uint32_t)kStages);
+            if (lane == 0) {
+                uint32_t sl = slot;
+                for (uint32_t k = 0; k < ahead; ++k) {
+                    issue_stage(sl);
+                    if (++sl == kStages) sl = 0;
+                }
+            }
+            to_issue -= ahead;
+        }
 
         // ---- activations of this column segment -> shared memory ----
         if (!waited_prior) {
@@ -156,25 +161,21 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
                 // 128-bit copies, four loads in flight per thread
                 const int vecs = pairs >> 2;                 // PAIRS is a multiple of 4
-                for (int i0 = threadIdx.x; i0 < BATCH * vecs; i0 += 4 * kGemvThreads) {
-                    uint4 v[4];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int i = i0 + k * kGemvThreads;
-                        if (i < BATCH * vecs) {
-                            const int b = i / vecs, s = i - b * vecs;
-                            v[k] = __ldg(reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0) + s);
-                        }
-                    }
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
+                    const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
+                    for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
+                        uint4 v[4];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int i = i0 + k * kGemvThreads;
-                        if (i < BATCH * vecs) {
-                            const int b = i / vecs, s = i - b * vecs;
-                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs + (uint32_t)b * x_batch_stride + 16u * s),
-                                         "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
-                                         : "memory");
-                        }
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs)
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
+                                             "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                             : "memory");
                     }
                 }
             } else {
@@ -189,95 +190,105 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         }
         __syncthreads();
 
-        // ---- main loop over this warp's units: runs of consecutive units inside one row block ----
+        // ---- main loop over this warp's granules ----
         int64_t rb = rb0;
-        int32_t ul = ul0;
-        uint32_t i = 0;                                   // index of the unit within the warp's range
+        int32_t gi = gi0;
+        bool fresh = true;                        // the next granule starts a run: fetch its history, zero the sums
+        uint32_t prevw = 0;
+        float facc[BATCH];
         uint4 nextv = make_uint4(0, 0, 0, 0);
-        if (!TMA && count > 0) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
-
-        while (i < count && ok) {
-            const uint32_t run_end = min(count, i + (uint32_t)(nu - ul));
-            const int64_t row = (rb << 5) + lane;
-            const int32_t u0 = useg0 + ul;
-            uint32_t prevw;
-            if (u0 == 0)
-                prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
-            else
-                prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u0 - 1, row)) + 3);
-            float facc[BATCH];
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
-            uint32_t xu = xs + (uint32_t)ul * (WPU * 2u);
-            int32_t u = u0;
+        if (!TMA && count > 0) nextv = ldg128_stream(next_unit_ptr());
 
 #pragma unroll 1
-            for (; i < run_end; ++i, ++u) {
-                uint4 v;
-                if (TMA) {
-                    const uint32_t sub = i % kStageUnits;
-                    if (sub == 0) {
-                        ok = mbar_wait(bars + 8u * slot, phase, p.status);
-                        if (!ok) break;
-                    }
-                    v = lds128(ring + slot * kStageBytes + sub * kUnitBytes + 16u * lane);
-                    if (sub == kStageUnits - 1 || i + 1 == count) {      // the stage is used up: refill its slot
-                        ++consumed;
-                        __syncwarp();
-                        if (next_stage < n_stage) {
-                            if (lane == 0) issue_stage(next_stage, slot);
-                            ++next_stage;
-                        }
-                        if (++slot == kStages) {
-                            slot = 0;
-                            phase ^= 1u;
-                        }
-                    }
-                } else {
-                    v = nextv;
-                    if (i + 1 < count) nextv = ldg128_stream(fetch_ptr() + (int64_t)lane * p.st.row);
-                }
-                uint32_t halo = prevw;
-                if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
-                    if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
-                        if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
-                        else if (u > 0) halo = prevw >> 16;
-                    }
-                }
-                prevw = v.w;
-
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                __half2 hacc[BATCH][4];
-                uint4 xv[BATCH];
-                decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
-                    if ((pi & 3) == 0) {
+        for (uint32_t k = 0; k < count; ++k) {
+            const int64_t row = (rb << 5) + lane;
+            if (fresh) {
+                fresh = false;
+                const int32_t u0 = useg0 + gi * GU;
+                if (u0 == 0)
+                    prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
+                else
+                    prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u0 - 1, row)) + 3);
 #pragma unroll
-                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
+            }
+            const bool last_of_block = gi == gpr - 1;
+            const int units = last_of_block ? tail_units : GU;
+            if (TMA) {
+                ok = mbar_wait(bars + 8u * slot, phase, p.status);
+                if (!ok) break;
+            }
+            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
+            const uint32_t xg = xs + (uint32_t)(gi * GU) * (WPU * 2u);
+#pragma unroll
+            for (int q = 0; q < GU; ++q) {
+                if (q < units) {
+                    uint4 v;
+                    if (TMA) {
+                        v = lds128(stage_base + q * kUnitBytes);
+                    } else {
+                        v = nextv;
+                        if (k + 1 < count) nextv = ldg128_stream(next_unit_ptr());
                     }
+                    uint32_t halo = prevw;
+                    if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
+                        const int32_t u = useg0 + gi;
+                        if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
+                            if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
+                            else if (u > 0) halo = prevw >> 16;
+                        }
+                    }
+                    prevw = v.w;
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    const uint32_t xu = xg + q * (WPU * 2u);
+                    __half2 hacc[BATCH][4];
+                    uint4 xv[BATCH];
+                    decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                        if ((pi & 3) == 0) {
+#pragma unroll
+                            for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                        }
+#pragma unroll
+                        for (int b = 0; b < BATCH; ++b) {
+                            const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                            hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
+                        }
+                    });
 #pragma unroll
                     for (int b = 0; b < BATCH; ++b) {
-                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                        hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
+                        const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
+                        const float2 f2 = __half22float2(s);
+                        facc[b] += f2.x + f2.y;
                     }
-                });
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
-                    const float2 f2 = __half22float2(s);
-                    facc[b] += f2.x + f2.y;
                 }
-                xu += WPU * 2u;
             }
+            if (TMA) {
+                __syncwarp();                     // every lane has taken its words: the slot can be refilled
+                if (to_issue) {
+                    if (lane == 0) issue_stage(slot);
+                    --to_issue;
+                }
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (last_of_block || k + 1 == count) {
 #pragma unroll
-            for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row, facc[b]);
-            ul = 0;
-            ++rb;
+                for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row, facc[b]);
+                fresh = true;
+            }
+            if (last_of_block) {
+                gi = 0;
+                ++rb;
+            } else {
+                ++gi;
+            }
         }
         if (TMA && !ok) {
             // After a failed wait: give the copies still in flight a bounded chance to land before
             // the shared memory they target is released, then stop.
-            const uint32_t consumed_here = i / kStageUnits;
-            for (uint32_t k = consumed_here; k < next_stage; ++k) {
+            for (int s = 0; s < kStages; ++s) {
                 mbar_wait(bars + 8u * slot, phase, p.status);
                 if (++slot == kStages) {
                     slot = 0;
@@ -410,7 +421,8 @@ extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *car
     if (m <= 0 || n <= 0 || (m % 32) || (n % (128 / fmt->K))) return RPTC_ERR_SHAPE;
     if (x_order == RPTC_XORDER_K2_LEGACY && (n % 2048 || fmt->K != 2)) return RPTC_ERR_SHAPE;
     if (fmt->layout == RPTC_LAYOUT_CHUNKED && (n / (128 / fmt->K)) % 32) return RPTC_ERR_SHAPE;
-    if (m > (int64_t(1) << 30) || n > (int64_t(1) << 30)) return RPTC_ERR_TOO_LARGE;
+    if (m > (int64_t(1) << 30) || n > (int64_t(1) << 30) || (m / 32) * (n / (128 / fmt->K)) >= (int64_t(1) << 31))
+        return RPTC_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(lut) & 15) ||
         (reinterpret_cast<uintptr_t>(x) & 3) || (ld_x & 1))
         return RPTC_ERR_ALIGN;

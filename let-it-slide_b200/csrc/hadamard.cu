@@ -15,53 +15,41 @@ struct HadParams {
     __half *out;
     int64_t ld_out;
     const __half *signs;
+    const __half *residual;     // optional fp16 [rows][ld_res], added to the result
+    int64_t ld_res;
     int32_t block, chunk;
     int32_t in_is_f32, transpose, clear_in;
     float scale;
 };
 
-__global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
-    __shared__ float ex[4096];
-    pdl_allow_next_grid();
-    pdl_wait_prior_grids();
+__device__ __forceinline__ void load8_f16(const __half *p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(u32_as_half2(w[i]));
+        v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void load8_f32(float *p, float (&v)[8], bool clear) {
+    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    if (clear) {
+        *reinterpret_cast<float4 *>(p) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4 *>(p + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+__device__ __forceinline__ void store8_f16(__half *p, const float (&v)[8]) {
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = half2_as_u32(__floats2half2_rn(v[2 * i], v[2 * i + 1]));
+    *reinterpret_cast<uint4 *>(p) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Unnormalised Walsh-Hadamard transform of `block`-sized blocks; thread t holds elements 8t..8t+7 of
+// the CTA's chunk.  `ex` is a shared exchange buffer of chunk floats (used when block > 256).
+__device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
     const int t = threadIdx.x;
-    const int64_t row = blockIdx.y;
-    const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
-    float v[8];
-    if (p.in_is_f32) {
-        float *src = const_cast<float *>(static_cast<const float *>(p.in)) + row * p.ld_in + col;
-        const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
-        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-        if (p.clear_in) {
-            *reinterpret_cast<float4 *>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(src + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    } else {
-        const uint4 a = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.in) + row * p.ld_in + col);
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(u32_as_half2(w[i]));
-            v[2 * i] = f.x, v[2 * i + 1] = f.y;
-        }
-    }
-    float sg[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
-    if (p.signs) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(p.signs + col));
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(u32_as_half2(w[i]));
-            sg[2 * i] = f.x, sg[2 * i + 1] = f.y;
-        }
-    }
-    if (!p.transpose) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= sg[i];
-    }
-    // strides 1, 2, 4: in registers
 #pragma unroll
     for (int h = 1; h < 8; h <<= 1) {
 #pragma unroll
@@ -73,8 +61,7 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
             }
         }
     }
-    // strides 8 .. 128: across lanes
-    for (int lm = 1; lm < 32 && 8 * lm < p.block; lm <<= 1) {
+    for (int lm = 1; lm < 32 && 8 * lm < block; lm <<= 1) {
         const bool upper = (t & lm) != 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -82,16 +69,15 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
             v[i] = upper ? o - v[i] : v[i] + o;
         }
     }
-    // strides >= 256: through shared memory
-    if (p.block > 256) {
+    if (block > 256) {
+        __syncthreads();          // the buffer may still be read from an earlier transform
 #pragma unroll
         for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
         __syncthreads();
-        const int pairs_per_thread = 4;   // chunk / 2 pairs over chunk / 8 threads
-        for (int h = 256; h < p.block; h <<= 1) {
+        for (int h = 256; h < block; h <<= 1) {
 #pragma unroll
-            for (int k = 0; k < pairs_per_thread; ++k) {
-                const int q = t + k * (int)blockDim.x;                  // pair number
+            for (int k = 0; k < 4; ++k) {          // chunk / 2 pairs over chunk / 8 threads
+                const int q = t + k * (int)blockDim.x;
                 const int i = ((q / h) * 2 * h) + (q % h);
                 const float a = ex[i], b = ex[i + h];
                 ex[i] = a + b;
@@ -102,14 +88,95 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
     }
-    uint32_t o[4];
+}
+
+__global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
+    __shared__ float ex[4096];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.y;
+    const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
+    float v[8];
+    if (p.in_is_f32) load8_f32(const_cast<float *>(static_cast<const float *>(p.in)) + row * p.ld_in + col, v, p.clear_in != 0);
+    else load8_f16(static_cast<const __half *>(p.in) + row * p.ld_in + col, v);
+    float sg[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float a = v[2 * i] * p.scale, b = v[2 * i + 1] * p.scale;
-        if (p.transpose) a *= sg[2 * i], b *= sg[2 * i + 1];
-        o[i] = half2_as_u32(__floats2half2_rn(a, b));
+    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
+    if (p.signs) load8_f16(p.signs + col, sg);
+    if (!p.transpose) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= sg[i];
     }
-    *reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col) = make_uint4(o[0], o[1], o[2], o[3]);
+    fwht8(v, p.block, ex);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= p.transpose ? p.scale * sg[i] : p.scale;
+    if (p.residual) {
+        float r[8];
+        load8_f16(p.residual + row * p.ld_res + col, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += r[i];
+    }
+    store8_f16(p.out + row * p.ld_out + col, v);
+}
+
+// Fused MLP middle: gate/up pre-activations arrive as the fp32 accumulator of the fused gate-up
+// layer (gate in columns [0, n), up in [n, 2n)).  out = H (s_in * (silu(g) * u)) * scale_in with
+// g, u = s_out * (H acc) * scale_out.  Both transforms use the same block size, so one CTA owns
+// matching blocks of gate and up.
+struct SwigluParams {
+    float *acc;
+    int64_t ld_acc;
+    __half *out;
+    int64_t ld_out;
+    const __half *signs_out;    // [2n] output-side signs of the gate-up layer (may be NULL)
+    const __half *signs_in;     // [n] input-side signs of the down layer (may be NULL)
+    int64_t n;
+    int32_t block, chunk, clear;
+    float scale_out, scale_in;
+};
+
+__global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams p) {
+    __shared__ float ex[4096];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.y;
+    const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
+    float g[8], u[8], sg[8];
+    load8_f32(p.acc + row * p.ld_acc + col, g, p.clear != 0);
+    load8_f32(p.acc + row * p.ld_acc + p.n + col, u, p.clear != 0);
+    fwht8(g, p.block, ex);
+    fwht8(u, p.block, ex);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
+    if (p.signs_out) load8_f16(p.signs_out + col, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= p.scale_out * sg[i];
+    if (p.signs_out) load8_f16(p.signs_out + p.n + col, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u[i] *= p.scale_out * sg[i];
+    // the layer's own output is fp16; round there as the unfused path would
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float gg = __half2float(__float2half_rn(g[i])), uu = __half2float(__float2half_rn(u[i]));
+        g[i] = __half2float(__float2half_rn(gg / (1.f + __expf(-gg)) * uu));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
+    if (p.signs_in) load8_f16(p.signs_in + col, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= sg[i];
+    fwht8(g, p.block, ex);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= p.scale_in;
+    store8_f16(p.out + row * p.ld_out + col, g);
+}
+
+static float hadamard_norm(int block) {
+    float norm = 1.f;
+    for (int b = block; b > 1; b >>= 2) norm *= (b >= 4) ? 0.5f : 0.70710678118654752f;
+    return norm;
 }
 
 }  // namespace rptc
@@ -117,16 +184,17 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
 using namespace rptc;
 
 extern "C" int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void *out, int64_t ld_out, const void *signs,
-                             int64_t rows, int64_t n, int block, int transpose, float scale, int clear_in,
-                             rptc_stream_t stream) {
+                             const void *residual, int64_t ld_res, int64_t rows, int64_t n, int block, int transpose,
+                             float scale, int clear_in, rptc_stream_t stream) {
     if (!in || !out) return RPTC_ERR_ARG;
     if (block < 8 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
-    if (rows <= 0 || n <= 0 || (n % block) || ld_in < n || ld_out < n) return RPTC_ERR_SHAPE;
+    if (rows <= 0 || n <= 0 || (n % block) || ld_in < n || ld_out < n || (residual && ld_res < n)) return RPTC_ERR_SHAPE;
     if (rows > 65535) return RPTC_ERR_TOO_LARGE;
     const int chunk = block < 256 ? 256 : block;
     if (n % chunk) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
-        (signs && (reinterpret_cast<uintptr_t>(signs) & 15)) || (ld_in % 8) || (ld_out % 8))
+        (signs && (reinterpret_cast<uintptr_t>(signs) & 15)) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)) ||
+        (ld_in % 8) || (ld_out % 8) || (residual && (ld_res % 8)))
         return RPTC_ERR_ALIGN;
     if (clear_in && !in_is_f32) return RPTC_ERR_ARG;
     if (int e = rptc_check_device()) return e;
@@ -136,14 +204,45 @@ extern "C" int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void 
     p.out = static_cast<__half *>(out);
     p.ld_out = ld_out;
     p.signs = static_cast<const __half *>(signs);
+    p.residual = static_cast<const __half *>(residual);
+    p.ld_res = ld_res;
     p.block = block;
     p.chunk = chunk;
     p.in_is_f32 = in_is_f32;
     p.transpose = transpose;
     p.clear_in = clear_in;
-    float norm = 1.f;
-    for (int b = block; b > 1; b >>= 2) norm *= (b >= 4) ? 0.5f : 0.70710678118654752f;
-    p.scale = scale * norm;
+    p.scale = scale * hadamard_norm(block);
     return launch(hadamard_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0,
+                  static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64_t ld_out, const void *signs_out,
+                                    const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in,
+                                    int clear, rptc_stream_t stream) {
+    if (!acc || !out) return RPTC_ERR_ARG;
+    if (block < 8 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
+    if (rows <= 0 || n <= 0 || (n % block) || ld_acc < 2 * n || ld_out < n) return RPTC_ERR_SHAPE;
+    if (rows > 65535) return RPTC_ERR_TOO_LARGE;
+    const int chunk = block < 256 ? 256 : block;
+    if (n % chunk) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+        (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (signs_in && (reinterpret_cast<uintptr_t>(signs_in) & 15)) ||
+        (ld_acc % 4) || (ld_out % 8) || (n % 8))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    SwigluParams p;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.out = static_cast<__half *>(out);
+    p.ld_out = ld_out;
+    p.signs_out = static_cast<const __half *>(signs_out);
+    p.signs_in = static_cast<const __half *>(signs_in);
+    p.n = n;
+    p.block = block;
+    p.chunk = chunk;
+    p.clear = clear;
+    p.scale_out = scale_out * hadamard_norm(block);
+    p.scale_in = scale_in * hadamard_norm(block);
+    return launch(swiglu_hadamard_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0,
                   static_cast<cudaStream_t>(stream), p);
 }

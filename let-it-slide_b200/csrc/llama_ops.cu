@@ -1,0 +1,261 @@
+// The non-quantised pieces of a Llama-architecture decode step (RMSNorm, RoPE + KV-cache append,
+// single-query attention, dense fp16 matvec for the output head).  They exist so that the
+// benchmark's decode step is a whole model step launched from one library on one stream; none of
+// them has a counterpart in the reference, which evaluates models through Hugging Face
+// transformers (quantize_hf.py:230-236).
+#include "common.cuh"
+
+namespace rptc {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+// out[r][:] = x[r][:] * rsqrt(mean(x^2) + eps) * w[:]      one CTA of 256 threads per row
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__ x, int64_t ld_x, const __half *__restrict__ w,
+                                                      __half *__restrict__ out, int64_t ld_out, int n, float eps) {
+    __shared__ float red[8];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const __half2 *xr = reinterpret_cast<const __half2 *>(x + (int64_t)blockIdx.x * ld_x);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n / 2; i += 256) {
+        const float2 f = __half22float2(xr[i]);
+        ss += f.x * f.x + f.y * f.y;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = rsqrtf(tot / n + eps);
+    const __half2 *wr = reinterpret_cast<const __half2 *>(w);
+    __half2 *o = reinterpret_cast<__half2 *>(out + (int64_t)blockIdx.x * ld_out);
+    for (int i = threadIdx.x; i < n / 2; i += 256) {
+        const float2 f = __half22float2(xr[i]), g = __half22float2(wr[i]);
+        o[i] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+    }
+}
+
+// Rotary embedding (rotate-half convention, pairs (i, i + d/2)) of the q and k heads of one token per
+// row of `qkv` ([rows][(hq + 2 hkv) * d]), in place for q; k (rotated) and v are appended to the caches
+// at positions pos[row].  Caches: [rows][max_pos][hkv][d].  One CTA per (row, head of q|k|v).
+__global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv, int64_t ld_qkv, const int32_t *__restrict__ pos,
+                                                        __half *__restrict__ kcache, __half *__restrict__ vcache, int hq, int hkv,
+                                                        int d, int max_pos, float theta) {
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int row = blockIdx.y, head = blockIdx.x, t = threadIdx.x;      // t < d/2
+    const int p = pos[row];
+    __half *src = qkv + (int64_t)row * ld_qkv + (int64_t)head * d;
+    if (head < hq + hkv) {
+        float lo = 0.f, hi = 0.f;
+        if (t < d / 2) {
+            const float inv_freq = __powf(theta, -2.f * t / d);
+            float sn, cs;
+            sincosf(p * inv_freq, &sn, &cs);
+            const float a = __half2float(src[t]), b = __half2float(src[t + d / 2]);
+            lo = a * cs - b * sn;
+            hi = b * cs + a * sn;
+        }
+        if (t < d / 2) {
+            if (head < hq) {
+                src[t] = __float2half_rn(lo);
+                src[t + d / 2] = __float2half_rn(hi);
+            } else {
+                __half *dst = kcache + (((int64_t)row * max_pos + p) * hkv + (head - hq)) * d;
+                dst[t] = __float2half_rn(lo);
+                dst[t + d / 2] = __float2half_rn(hi);
+            }
+        }
+    } else {
+        __half *dst = vcache + (((int64_t)row * max_pos + p) * hkv + (head - hq - hkv)) * d;
+        if (t < d / 2) {
+            dst[t] = src[t];
+            dst[t + d / 2] = src[t + d / 2];
+        }
+    }
+}
+
+// Single-query attention over the cache: one CTA of 128 threads per (row, q head); d == 128.
+// scores -> shared memory, softmax, then thread c accumulates output column c.
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv, const int32_t *__restrict__ pos,
+                                                          const __half *__restrict__ kcache, const __half *__restrict__ vcache,
+                                                          __half *__restrict__ out, int64_t ld_out, int hq, int hkv, int max_pos,
+                                                          float scale) {
+    extern __shared__ float sc[];       // [ctx]
+    __shared__ float red[4];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    constexpr int D = 128;
+    const int row = blockIdx.y, head = blockIdx.x, kvh = head / (hq / hkv);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int ctx = pos[row] + 1;
+    const __half *q = qkv + (int64_t)row * ld_qkv + (int64_t)head * D;
+    const float2 q01 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane]);
+    const float2 q23 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane + 1]);
+    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D;
+    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D;
+    float mx = -1e30f;
+    for (int j = warp; j < ctx; j += 4) {
+        const uint2 kk = *reinterpret_cast<const uint2 *>(kb + (int64_t)j * hkv * D + 4 * lane);
+        const float2 k01 = __half22float2(u32_as_half2(kk.x)), k23 = __half22float2(u32_as_half2(kk.y));
+        float s = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+        s = warp_sum(s) * scale;
+        if (lane == 0) sc[j] = s;
+        mx = fmaxf(mx, s);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float sum = 0.f;
+    for (int j = t; j < ctx; j += 128) {
+        const float e = __expf(sc[j] - mx);
+        sc[j] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    const float inv = 1.f / (red[0] + red[1] + red[2] + red[3]);
+    float acc = 0.f;
+    for (int j = 0; j < ctx; ++j) acc += sc[j] * __half2float(vb[(int64_t)j * hkv * D + t]);
+    out[(int64_t)row * ld_out + (int64_t)head * D + t] = __float2half_rn(acc * inv);
+}
+
+// Dense fp16 matvec  y[b][r] = sum_c W[r][c] x[b][c]  (fp32 accumulation), one warp per row of W, the
+// batch (<= 8) handled inside.  Used for the output head; also the dense-bandwidth probe the
+// reference's stale tests call `matvec` (rptc_kernels/tests/test_matvec.py:18).
+template <int BATCH>
+__global__ void __launch_bounds__(256) dense_gemv_kernel(const __half *__restrict__ W, int64_t ld_w, const __half *__restrict__ x,
+                                                         int64_t ld_x, __half *__restrict__ y, int64_t ld_y, int64_t m, int n) {
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= m) return;
+    const uint4 *wr = reinterpret_cast<const uint4 *>(W + row * ld_w);
+    float acc[BATCH];
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) acc[b] = 0.f;
+    for (int i = lane; i < n / 8; i += 32) {
+        const uint4 wv = ldg128_stream(wr + i);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const uint4 xv = __ldg(reinterpret_cast<const uint4 *>(x + (int64_t)b * ld_x) + i);
+            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 a = __half22float2(u32_as_half2(ww[k])), c = __half22float2(u32_as_half2(xx[k]));
+                acc[b] += a.x * c.x + a.y * c.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+        const float s = warp_sum(acc[b]);
+        if (lane == 0) y[(int64_t)b * ld_y + row] = __float2half_rn(s);
+    }
+}
+
+// out[r][:] = table[ids[r]][:]
+__global__ void embed_kernel(const __half *__restrict__ table, const int32_t *__restrict__ ids, __half *__restrict__ out, int64_t ld_out,
+                             int n) {
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const uint4 *src = reinterpret_cast<const uint4 *>(table + (int64_t)ids[blockIdx.x] * n);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + (int64_t)blockIdx.x * ld_out);
+    for (int i = threadIdx.x; i < n / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace rptc
+
+using namespace rptc;
+
+extern "C" int rptc_rmsnorm(const void *x, int64_t ld_x, const void *w, void *out, int64_t ld_out, int64_t rows, int64_t n,
+                            float eps, rptc_stream_t stream) {
+    if (!x || !w || !out) return RPTC_ERR_ARG;
+    if (rows <= 0 || n <= 0 || (n % 2) || ld_x < n || ld_out < n) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(out) & 3) || (ld_x & 1) || (ld_out & 1)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    return launch(rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half *>(x),
+                  ld_x, static_cast<const __half *>(w), static_cast<__half *>(out), ld_out, (int)n, eps);
+}
+
+extern "C" int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, void *kcache, void *vcache, int64_t rows, int hq,
+                               int hkv, int d, int max_pos, float theta, rptc_stream_t stream) {
+    if (!qkv || !pos || !kcache || !vcache) return RPTC_ERR_ARG;
+    if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || d <= 0 || (d % 2) || d > 128 || max_pos <= 0) return RPTC_ERR_SHAPE;
+    if (ld_qkv < (int64_t)(hq + 2 * hkv) * d) return RPTC_ERR_SHAPE;
+    if (int e = rptc_check_device()) return e;
+    return launch(rope_cache_kernel, dim3((unsigned)(hq + 2 * hkv), (unsigned)rows), dim3(64), 0, static_cast<cudaStream_t>(stream),
+                  static_cast<__half *>(qkv), ld_qkv, pos, static_cast<__half *>(kcache), static_cast<__half *>(vcache), hq, hkv, d,
+                  max_pos, theta);
+}
+
+extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
+                                int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, rptc_stream_t stream) {
+    if (!qkv || !pos || !kcache || !vcache || !out) return RPTC_ERR_ARG;
+    if (d != 128) return RPTC_ERR_UNSUPPORTED;
+    if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || max_pos <= 0 || max_pos > 32768) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(kcache) & 7) || (ld_qkv & 3)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    static bool configured = false;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
+        configured = true;
+    }
+    return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(128), (size_t)max_pos * 4, static_cast<cudaStream_t>(stream),
+                  static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
+                  static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale);
+}
+
+extern "C" int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,
+                               int batch, rptc_stream_t stream) {
+    if (!W || !x || !y) return RPTC_ERR_ARG;
+    if (m <= 0 || n <= 0 || (n % 8) || ld_w < n || ld_x < n || ld_y < m) return RPTC_ERR_SHAPE;
+    if (batch < 1 || batch > 8) return RPTC_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || (ld_w % 8) || (ld_x % 8)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    const dim3 grid((unsigned)((m + 7) / 8)), block(256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const __half *Wp = static_cast<const __half *>(W), *xp = static_cast<const __half *>(x);
+    __half *yp = static_cast<__half *>(y);
+    int done = 0;
+    while (done < batch) {
+        int b = 8;
+        while (b > batch - done) b >>= 1;
+        int e;
+        const __half *xb = xp + (int64_t)done * ld_x;
+        __half *yb = yp + (int64_t)done * ld_y;
+        switch (b) {
+            case 8: e = launch(dense_gemv_kernel<8>, grid, block, 0, s, Wp, ld_w, xb, ld_x, yb, ld_y, m, (int)n); break;
+            case 4: e = launch(dense_gemv_kernel<4>, grid, block, 0, s, Wp, ld_w, xb, ld_x, yb, ld_y, m, (int)n); break;
+            case 2: e = launch(dense_gemv_kernel<2>, grid, block, 0, s, Wp, ld_w, xb, ld_x, yb, ld_y, m, (int)n); break;
+            default: e = launch(dense_gemv_kernel<1>, grid, block, 0, s, Wp, ld_w, xb, ld_x, yb, ld_y, m, (int)n); break;
+        }
+        if (e) return e;
+        done += b;
+    }
+    return RPTC_OK;
+}
+
+extern "C" int rptc_embed(const void *table, const int32_t *ids, void *out, int64_t ld_out, int64_t rows, int64_t n,
+                          rptc_stream_t stream) {
+    if (!table || !ids || !out) return RPTC_ERR_ARG;
+    if (rows <= 0 || n <= 0 || (n % 8) || ld_out < n) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(table) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (ld_out % 8)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    return launch(embed_kernel, dim3((unsigned)rows), dim3(128), 0, static_cast<cudaStream_t>(stream), static_cast<const __half *>(table),
+                  ids, static_cast<__half *>(out), ld_out, (int)n);
+}

@@ -1,0 +1,213 @@
+"""A Llama-architecture decoder over RPTC-quantised linears: the decode engine the benchmark times.
+
+Every linear of every block (fused qkv, o, fused gate-up, down) is an RPTCLinear over packed
+codes; embeddings, norms and the output head stay fp16 (the reference quantises only
+self_attn.*_proj and mlp.*_proj, quantize_hf.py:189).  One decode step is a fixed sequence of
+kernel launches on one stream, captured once in a CUDA graph and replayed per token; with
+programmatic dependent launch the table set-up and first weight fetches of each fused
+dequant-GEMV overlap the small kernel in front of it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+from ._lib import CODE_HASH, LAYOUT_TILED, Format, lib
+from .linear import RPTCLinear, hadamard_block
+
+
+@dataclass
+class LlamaConfig:
+    hidden: int = 4096
+    layers: int = 32
+    heads: int = 32
+    kv_heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    head_dim: int = 128
+    rms_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    max_pos: int = 512
+    weight_scale: float = 0.02
+
+    @classmethod
+    def llama2_7b(cls, **kw):
+        return cls(**kw)
+
+    @classmethod
+    def llama2_70b(cls, **kw):
+        return cls(hidden=8192, layers=80, heads=64, kv_heads=8, ffn=28672, **kw)
+
+    def quantised_weights(self) -> int:
+        q = self.heads * self.head_dim
+        kv = self.kv_heads * self.head_dim
+        per_layer = self.hidden * (q + 2 * kv) + q * self.hidden + 3 * self.hidden * self.ffn
+        return per_layer * self.layers
+
+
+class Block:
+    def __init__(self, cfg: LlamaConfig, fmt: Format, seed: int, device, incoherent: bool):
+        q, kv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        mk = lambda i, o, s: RPTCLinear.random(i, o, fmt, cfg.weight_scale, seed * 16 + s, device, incoherent)
+        self.qkv = mk(cfg.hidden, q + 2 * kv, 0)
+        self.o = mk(q, cfg.hidden, 1)
+        self.gate_up = mk(cfg.hidden, 2 * cfg.ffn, 2)
+        # gate and up are transformed separately, so that the fused SwiGLU kernel can own matching blocks of both
+        self.gate_up.block_out = hadamard_block(cfg.ffn)
+        self.down = mk(cfg.ffn, cfg.hidden, 3)
+        g = torch.Generator(device=device).manual_seed(seed * 16 + 9)
+        self.norm1 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
+        self.norm2 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
+
+    def linears(self):
+        return [self.qkv, self.o, self.gate_up, self.down]
+
+
+class RPTCLlama:
+    """Random-init Llama-shape model with all block linears RPTC-quantised; batch-`rows` decode."""
+
+    def __init__(self, cfg: LlamaConfig, fmt: Format | None = None, rows: int = 1, seed: int = 0, device="cuda",
+                 incoherent: bool = True):
+        self.cfg, self.rows, self.device = cfg, rows, torch.device(device)
+        self.fmt = fmt or Format(CODE_HASH, 2, 16, 8, LAYOUT_TILED)
+        self.blocks = [Block(cfg, self.fmt, seed * 1000 + i + 1, device, incoherent) for i in range(cfg.layers)]
+        g = torch.Generator(device=device).manual_seed(seed * 1000 + 999)
+        self.embed = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=device) * 0.02).to(torch.float16)
+        self.head = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=device) * 0.02).to(torch.float16)
+        self.norm_f = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
+        q, kv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        f16 = dict(dtype=torch.float16, device=device)
+        self.kcache = [torch.zeros((rows, cfg.max_pos, cfg.kv_heads, cfg.head_dim), **f16) for _ in range(cfg.layers)]
+        self.vcache = [torch.zeros((rows, cfg.max_pos, cfg.kv_heads, cfg.head_dim), **f16) for _ in range(cfg.layers)]
+        # step workspace (fixed addresses, so that the step can live in a CUDA graph)
+        self.ids = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.h = torch.zeros((rows, cfg.hidden), **f16)
+        self.xn = torch.zeros((rows, cfg.hidden), **f16)
+        self.xt = torch.zeros((rows, max(cfg.hidden, q)), **f16)
+        self.qkv_out = torch.zeros((rows, q + 2 * kv), **f16)
+        self.attn = torch.zeros((rows, q), **f16)
+        self.mlp = torch.zeros((rows, cfg.ffn), **f16)
+        self.logits = torch.zeros((rows, cfg.vocab), **f16)
+        self.next_ids = torch.zeros(rows, dtype=torch.int64, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
+        self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
+        self.acc_gu = torch.zeros((rows, 2 * cfg.ffn), **f32)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.launches_per_step = 0
+
+    # -- one token for every row ---------------------------------------------------------------------
+    def step_eager(self) -> None:
+        cfg, r = self.cfg, self.rows
+        n_launch = 0
+        ops.embed(self.embed, self.ids, self.h)
+        n_launch += 1
+        for i, b in enumerate(self.blocks):
+            ops.rmsnorm(self.h, b.norm1, self.xn, cfg.rms_eps)
+            xt = b.qkv.transform_in(self.xn, out=self.xt[:, : cfg.hidden])
+            b.qkv.matvec_acc(xt, self.acc_qkv)
+            b.qkv.finish(self.acc_qkv, out=self.qkv_out)
+            ops.rope_cache(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], cfg.heads, cfg.kv_heads, cfg.head_dim,
+                           cfg.rope_theta)
+            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, cfg.heads, cfg.kv_heads,
+                            cfg.head_dim)
+            xt = b.o.transform_in(self.attn, out=self.xt[:, : self.attn.shape[1]])
+            b.o.matvec_acc(xt, self.acc_h)
+            b.o.finish(self.acc_h, out=self.h, residual=self.h)
+            ops.rmsnorm(self.h, b.norm2, self.xn, cfg.rms_eps)
+            xt = b.gate_up.transform_in(self.xn, out=self.xt[:, : cfg.hidden])
+            b.gate_up.matvec_acc(xt, self.acc_gu)
+            if b.gate_up.incoherent:
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, cfg.ffn, b.down.block_in,
+                                    b.gate_up.scale, 1.0, clear=True)
+                n_launch += 15
+            else:
+                gu = b.gate_up.finish(self.acc_gu)
+                torch.mul(torch.nn.functional.silu(gu[:, : cfg.ffn]), gu[:, cfg.ffn:], out=self.mlp)
+                n_launch += 15
+            b.down.matvec_acc(self.mlp, self.acc_h)
+            b.down.finish(self.acc_h, out=self.h, residual=self.h)
+        ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        torch.argmax(self.logits, dim=1, out=self.next_ids)
+        self.ids.copy_(self.next_ids)
+        self.pos.add_(1)
+        self.launches_per_step = n_launch + 2
+
+    def capture(self, pdl: bool = True) -> None:
+        """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""
+        lib().rptc_set_pdl(1 if pdl else 0)
+        ids0, pos0 = self.ids.clone(), self.pos.clone()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.step_eager()
+            self.ids.copy_(ids0)
+            self.pos.copy_(pos0)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=s):
+                self.step_eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.ids.copy_(ids0)
+        self.pos.copy_(pos0)
+        lib().rptc_set_pdl(0)
+
+    def step(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_eager()
+
+    def reset(self, ids: torch.Tensor | None = None) -> None:
+        self.pos.zero_()
+        if ids is not None:
+            self.ids.copy_(ids.to(torch.int32))
+
+    def bytes_per_token(self, context: int) -> dict:
+        cfg = self.cfg
+        packed = cfg.quantised_weights() * self.fmt.K // 8
+        head = cfg.vocab * cfg.hidden * 2
+        kv = 2 * cfg.layers * context * cfg.kv_heads * cfg.head_dim * 2
+        return {"packed": packed, "head": head, "kv": kv}
+
+    # -- dense fp32 reference of the same model (decode weights with the GPU's bit-exact decompress) --------
+    @torch.no_grad()
+    def reference_logits(self, tokens: torch.Tensor) -> torch.Tensor:
+        """fp32 torch forward of the same network on `tokens` [rows, T] -> logits [rows, T, vocab]."""
+        cfg = self.cfg
+        T = tokens.shape[1]
+        h = self.embed[tokens.long()].float()
+        half = cfg.head_dim // 2
+        inv = cfg.rope_theta ** (-torch.arange(half, device=self.device, dtype=torch.float32) * 2 / cfg.head_dim)
+        ang = torch.arange(T, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
+        cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+
+        def rms(x, w):
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.rms_eps) * w.float()
+
+        def rope(x):
+            a, b = x[..., :half], x[..., half:]
+            return torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1)
+
+        q_dim, kv_dim = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        mask = torch.full((T, T), float("-inf"), device=self.device).triu(1)
+        for b in self.blocks:
+            x = rms(h, b.norm1)
+            qkv = x @ b.qkv.effective_weight().t()
+            q = rope(qkv[..., :q_dim].reshape(-1, T, cfg.heads, cfg.head_dim))
+            k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(-1, T, cfg.kv_heads, cfg.head_dim))
+            v = qkv[..., q_dim + kv_dim:].reshape(-1, T, cfg.kv_heads, cfg.head_dim)
+            rep = cfg.heads // cfg.kv_heads
+            k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+            att = torch.einsum("bthd,bshd->bhts", q, k) * cfg.head_dim ** -0.5 + mask
+            o = torch.einsum("bhts,bshd->bthd", att.softmax(-1), v).reshape(-1, T, q_dim)
+            h = h + o @ b.o.effective_weight().t()
+            x = rms(h, b.norm2)
+            gu = x @ b.gate_up.effective_weight().t()
+            h = h + (torch.nn.functional.silu(gu[..., : cfg.ffn]) * gu[..., cfg.ffn:]) @ b.down.effective_weight().t()
+        return rms(h, self.norm_f) @ self.head.float().t()

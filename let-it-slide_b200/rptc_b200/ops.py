@@ -139,11 +139,15 @@ def gemm(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, m: int, n: int
     return out
 
 
+def _ld(t: torch.Tensor, width: int) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(width, t.stride(0))
+
+
 def hadamard(x: torch.Tensor, signs: torch.Tensor | None, block: int, transpose: bool = False, scale: float = 1.0,
-             out: torch.Tensor | None = None, clear_in: bool = False) -> torch.Tensor:
+             out: torch.Tensor | None = None, clear_in: bool = False, residual: torch.Tensor | None = None) -> torch.Tensor:
     """Block-diagonal randomized Hadamard transform along the last axis (rptc_hadamard).
 
-    x: fp16 or fp32 [rows, n]; result fp16 [rows, n]."""
+    x: fp16 or fp32 [rows, n]; result fp16 [rows, n] (+ residual)."""
     squeeze = x.dim() == 1
     if squeeze:
         x = x.unsqueeze(0)
@@ -154,11 +158,70 @@ def hadamard(x: torch.Tensor, signs: torch.Tensor | None, block: int, transpose:
         out = torch.empty((rows, n), dtype=torch.float16, device=x.device)
     if signs is not None:
         _cuda_contig(signs, "signs", torch.float16)
+    if residual is not None and residual.dim() == 1:
+        residual = residual.unsqueeze(0)
     with torch.cuda.device(x.device):
-        check(lib().rptc_hadamard(ptr(x), int(x.dtype == torch.float32), x.stride(0) if rows > 1 else max(n, x.stride(0)),
-                                  ptr(out), out.stride(0) if rows > 1 else max(n, out.stride(0)), ptr(signs), rows, n, block,
-                                  int(transpose), scale, int(clear_in), stream_ptr()), "rptc_hadamard")
+        check(lib().rptc_hadamard(ptr(x), int(x.dtype == torch.float32), _ld(x, n), ptr(out), _ld(out, n), ptr(signs),
+                                  ptr(residual), 0 if residual is None else _ld(residual, n), rows, n, block, int(transpose),
+                                  scale, int(clear_in), stream_ptr()), "rptc_hadamard")
     return out[0] if squeeze else out
+
+
+def swiglu_hadamard(acc: torch.Tensor, out: torch.Tensor, signs_out: torch.Tensor | None, signs_in: torch.Tensor | None,
+                    n: int, block: int, scale_out: float, scale_in: float = 1.0, clear: bool = True) -> torch.Tensor:
+    """Fused gated-MLP middle (rptc_swiglu_hadamard): acc fp32 [rows, 2n] -> out fp16 [rows, n]."""
+    with torch.cuda.device(acc.device):
+        check(lib().rptc_swiglu_hadamard(ptr(acc), _ld(acc, 2 * n), ptr(out), _ld(out, n), ptr(signs_out), ptr(signs_in),
+                                         acc.shape[0], n, block, scale_out, scale_in, int(clear), stream_ptr()),
+              "rptc_swiglu_hadamard")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float) -> torch.Tensor:
+    rows, n = x.shape
+    with torch.cuda.device(x.device):
+        check(lib().rptc_rmsnorm(ptr(x), _ld(x, n), ptr(w), ptr(out), _ld(out, n), rows, n, eps, stream_ptr()), "rptc_rmsnorm")
+    return out
+
+
+def rope_cache(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, hq: int, hkv: int, d: int,
+               theta: float) -> None:
+    rows = qkv.shape[0]
+    with torch.cuda.device(qkv.device):
+        check(lib().rptc_rope_cache(ptr(qkv), _ld(qkv, qkv.shape[1]), ptr(pos), ptr(kcache), ptr(vcache), rows, hq, hkv, d,
+                                    kcache.shape[1], theta, stream_ptr()), "rptc_rope_cache")
+
+
+def attn_decode(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, out: torch.Tensor, hq: int,
+                hkv: int, d: int) -> torch.Tensor:
+    rows = qkv.shape[0]
+    with torch.cuda.device(qkv.device):
+        check(lib().rptc_attn_decode(ptr(qkv), _ld(qkv, qkv.shape[1]), ptr(pos), ptr(kcache), ptr(vcache), ptr(out),
+                                     _ld(out, out.shape[1]), rows, hq, hkv, d, kcache.shape[1], d ** -0.5, stream_ptr()),
+              "rptc_attn_decode")
+    return out
+
+
+def dense_gemv(W: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[b] = W x[b] for a dense fp16 W [m, n] (rptc_dense_gemv)."""
+    squeeze = x.dim() == 1
+    if squeeze:
+        x = x.unsqueeze(0)
+    m, n = W.shape
+    if out is None:
+        out = torch.empty((x.shape[0], m), dtype=torch.float16, device=x.device)
+    o2 = out.unsqueeze(0) if out.dim() == 1 else out
+    with torch.cuda.device(W.device):
+        check(lib().rptc_dense_gemv(ptr(W), W.stride(0), ptr(x), _ld(x, n), ptr(o2), _ld(o2, m), m, n, x.shape[0], stream_ptr()),
+              "rptc_dense_gemv")
+    return out[0] if squeeze and out.dim() == 2 else out
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    with torch.cuda.device(table.device):
+        check(lib().rptc_embed(ptr(table), ptr(ids), ptr(out), _ld(out, table.shape[1]), ids.shape[0], table.shape[1],
+                               stream_ptr()), "rptc_embed")
+    return out
 
 
 def device_status() -> None:

@@ -44,5 +44,5 @@ def test_argument_errors_need_no_gpu():
     assert lib().rptc_gemv(1 << 8, 1 << 8, None, 1 << 8, 64, 1 << 8, 32, 32, 64, 9, 0, ctypes.byref(f), None) == -1
     bad = Format(code=1, K=4)
     assert lib().rptc_decompress(1 << 8, 1 << 8, None, 1 << 8, 64, 32, 64, ctypes.byref(bad), None) == -4
-    assert lib().rptc_hadamard(1 << 8, 0, 256, 1 << 8, 256, None, 1, 256, 100, 0, 1.0, 0, None) == -1
+    assert lib().rptc_hadamard(1 << 8, 0, 256, 1 << 8, 256, None, None, 0, 1, 256, 100, 0, 1.0, 0, None) == -1
     assert lib().rptc_repack(1 << 8, 0, 1 << 9, 2, 33, 4, None) == -2

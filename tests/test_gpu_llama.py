@@ -1,0 +1,66 @@
+"""GPU parity of RPTCLinear and of the Llama-shape decode engine against an fp32 torch forward of the
+same network (weights decoded with the library's bit-exact decompress, transforms applied in fp32).
+
+Tolerance (BASELINE: max-rel 1e-2 on logits): max |logit - ref| <= 1e-2 * max |ref| at every position.
+"""
+import numpy as np
+import pytest
+import torch
+
+import rptc_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("code,K,S", [(o.CODE_B, 2, 8), (o.CODE_A, 2, 0), (o.CODE_C, 2, 9)])
+@pytest.mark.parametrize("rows", [1, 5])
+@pytest.mark.parametrize("n,m", [(4096, 1024), (11008, 512)])
+def test_rptc_linear_forward_matches_effective_weight(code, K, S, rows, n, m):
+    from rptc_b200 import Format
+    from rptc_b200.linear import RPTCLinear
+    lin = RPTCLinear.random(n, m, Format(code, K, 16, S), scale=0.02, seed=3)
+    x = torch.randn((rows, n), dtype=torch.float16, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    y = lin(x).float()
+    ref = x.float() @ lin.effective_weight().t()
+    assert (y - ref).abs().max() <= 1e-2 * ref.abs().max()
+    # the decoded matrix itself is bit-exact against the CPU oracle
+    words = o.to_rowmajor(lin.codes.cpu().numpy().view(np.uint32), o.LAYOUT_TILED)
+    lut = lin.lut.cpu().numpy()
+    if code == o.CODE_C:
+        lut = lut.reshape(-1, 2)
+    ref_w = o.decode(words[:64], lut, n, code=code, K=K, L=16, S=S)
+    assert np.array_equal(lin.decoded()[:64].cpu().numpy().view(np.uint16), ref_w.view(np.uint16))
+
+
+def test_rptc_linear_state_dict_round_trip():
+    from rptc_b200.linear import RPTCLinear
+    a = RPTCLinear.random(2048, 256, seed=1)
+    b = RPTCLinear.random(2048, 256, seed=2)
+    b.load_state_dict(a.state_dict())
+    x = torch.randn((2, 2048), dtype=torch.float16, device="cuda")
+    assert torch.equal(a(x), b(x))
+
+
+@pytest.mark.parametrize("incoherent", [True, False])
+def test_decode_engine_logits_match_fp32_reference(incoherent):
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=2, ffn=1024, vocab=1024, max_pos=32, weight_scale=0.05)
+    rows, T = 2, 10
+    model = RPTCLlama(cfg, rows=rows, seed=7, incoherent=incoherent)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
+    ref = model.reference_logits(tokens)                      # [rows, T, vocab] fp32
+    for use_graph in (False, True):
+        model.reset()
+        if use_graph:
+            model.capture(pdl=True)
+        for t in range(T):
+            model.ids.copy_(tokens[:, t].to(torch.int32))
+            model.step()
+            torch.cuda.synchronize()
+            got = model.logits.float()
+            err = (got - ref[:, t]).abs().max().item()
+            assert err <= 1e-2 * ref[:, t].abs().max().item(), (use_graph, t, err)
+        assert model.pos.tolist() == [T] * rows
+    from rptc_b200 import ops
+    ops.device_status()
