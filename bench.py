@@ -198,13 +198,13 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
 
-    cfg = LlamaConfig(max_pos=PROMPT + args.warmup + 2 * args.steps + 8, **cfg_kw)
+    cfg = LlamaConfig(max_pos=args.prompt + max(3, args.warmup) + 2 * args.steps + 8, **cfg_kw)
     model = RPTCLlama(cfg, rows=1, seed=rank)
     g = torch.Generator(device="cuda").manual_seed(42 + rank)
-    prompt = torch.randint(0, cfg.vocab, (PROMPT,), device="cuda", generator=g, dtype=torch.int32)
+    prompt = torch.randint(0, cfg.vocab, (args.prompt,), device="cuda", generator=g, dtype=torch.int32)
     model.reset()
     model.capture(pdl=True)
-    for t in range(PROMPT):                                # the prompt goes through the decode step, token by token
+    for t in range(args.prompt):                           # the prompt goes through the decode step, token by token
         model.ids.copy_(prompt[t:t + 1])
         model.step()
     for _ in range(max(3, args.warmup)):
@@ -253,13 +253,13 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     if rank == 0:
         roof = gemv_roofline(model, torch)
         cpu_s, cores, sample = cpu_block_seconds(cfg_dims, 3)
-        ctx = PROMPT + args.warmup + args.steps // 2
+        ctx = args.prompt + args.warmup + args.steps // 2
         bt = model.bytes_per_token(ctx)
         out = {"metric": METRIC, "value": world * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                "config": {"workload": args.workload, "code": "HASH S=8 K=2 L=16", "layout": "TILED", "incoherence": "RHT both sides",
-                          "prompt": PROMPT, "batch_per_gpu": 1, "parallelism": "replicas" if world > 1 else "single",
+                          "prompt": args.prompt, "batch_per_gpu": 1, "parallelism": "replicas" if world > 1 else "single",
                           "l2": "weights 1.6 GB per token exceed L2", "bytes_per_token": bt},
                "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 8},
                "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks, "roofline": roof,
@@ -282,6 +282,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama2-7b-decode-bs1")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens pushed through the decode step before timing")
     args = ap.parse_args()
     if args.workload == "llama2-70b-tp":
         from bench_tp import run_tp          # the partitioned workload lives beside this file
