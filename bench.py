@@ -198,9 +198,13 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
 
+    tp = args.workload.endswith("-tp")
     cfg = LlamaConfig(max_pos=args.prompt + max(3, args.warmup) + 2 * args.steps + 8, **cfg_kw)
-    model = RPTCLlama(cfg, rows=1, seed=rank)
-    g = torch.Generator(device="cuda").manual_seed(42 + rank)
+    if tp:
+        model = RPTCLlama(cfg, rows=1, seed=0, tp_world=world, tp_rank=rank)
+    else:
+        model = RPTCLlama(cfg, rows=1, seed=rank)
+    g = torch.Generator(device="cuda").manual_seed(42 + (0 if tp else rank))
     prompt = torch.randint(0, cfg.vocab, (args.prompt,), device="cuda", generator=g, dtype=torch.int32)
     model.reset()
     model.capture(pdl=True)
@@ -255,13 +259,15 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
         cpu_s, cores, sample = cpu_block_seconds(cfg_dims, 3)
         ctx = args.prompt + args.warmup + args.steps // 2
         bt = model.bytes_per_token(ctx)
-        out = {"metric": METRIC, "value": world * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-               "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        seqs = 1 if tp else world
+        out = {"metric": METRIC if not tp else "2-bit Llama-2-70B-shape tensor-parallel decode tok/s (bs1)",
+               "value": seqs * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                "config": {"workload": args.workload, "code": "HASH S=8 K=2 L=16", "layout": "TILED", "incoherence": "RHT both sides",
-                          "prompt": args.prompt, "batch_per_gpu": 1, "parallelism": "replicas" if world > 1 else "single",
+                          "prompt": args.prompt, "batch_per_gpu": 1, "parallelism": (f"tp{world}" if tp else ("replicas" if world > 1 else "single")),
                           "l2": "weights 1.6 GB per token exceed L2", "bytes_per_token": bt},
-               "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 8},
+               "e2e": {"value": seqs * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 8},
                "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks, "roofline": roof,
                "cpu_baseline": {"value": 1.0 / cpu_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
                "token_stream_gbs": (bt["packed"] + bt["head"] + bt["kv"]) / (ms / args.steps * 1e-3) / 1e9}
@@ -272,6 +278,9 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
 
 WORKLOADS = {
     "llama2-7b-decode-bs1": (dict(), dict(hidden=4096, ffn=11008, layers=32, heads=32, kv_heads=32)),
+    # the partitioned shape: tensor-parallel over all ranks (strong scaling), NCCL all-reduce after o and down
+    "llama2-70b-tp": (dict(hidden=8192, layers=80, heads=64, kv_heads=8, ffn=28672),
+                      dict(hidden=8192, ffn=28672, layers=80, heads=64, kv_heads=8)),
 }
 
 
@@ -284,10 +293,6 @@ def main() -> None:
     ap.add_argument("--workload", default="llama2-7b-decode-bs1")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens pushed through the decode step before timing")
     args = ap.parse_args()
-    if args.workload == "llama2-70b-tp":
-        from bench_tp import run_tp          # the partitioned workload lives beside this file
-        run_tp(args)
-        return
     cfg_kw, cfg_dims = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, cfg_dims)

@@ -4,13 +4,15 @@
 //
 // One CTA owns an output tile of 256 tokens x 128 weight rows and walks the reduction dimension in
 // steps of 64 columns through a ring of shared-memory stages.  Warp roles:
-//   warps 0-3  decode producers: thread r owns weight row r of the tile.  Per step it takes the
-//              row's next 128 * K / 2 code bits with 128-bit loads (coalesced per 32-row block of the
-//              TILED layout), rebuilds the shift-register windows with funnel shifts, looks the weights
-//              up, and writes its 128-byte row of the B operand straight into the 128-byte-swizzled
-//              K-major layout the tensor core reads.  After the last step the same warps run the epilogue.
-//   warp 4     one lane issues the 2-D TMA loads of the activation tile (two 128-token halves).
-//   warp 5     owns the TMEM allocation; one lane issues tcgen05.mma (M=128, N=128, K=16, fp32
+//   warps 0-7  decode producers in two groups of four that take alternate steps, so that two stages
+//              are being decoded at any time: thread r of a group owns weight row r of the tile.  Per step
+//              it takes the row's next 128 * K / 2 code bits with 128-bit loads (coalesced per 32-row
+//              block of the TILED layout), rebuilds the shift-register windows with funnel shifts, looks
+//              the weights up, and writes its 128-byte row of the B operand straight into the
+//              128-byte-swizzled K-major layout the tensor core reads.  After the last step the same
+//              warps run the epilogue (group g drains token half g).
+//   warp 8     one lane issues the 2-D TMA loads of the activation tile (two 128-token halves).
+//   warp 9     owns the TMEM allocation; one lane issues tcgen05.mma (M=128, N=128, K=16, fp32
 //              accumulators in TMEM, two token halves) and commits each stage back to the producers.
 // Epilogue: tcgen05.ld 32 lanes x 32 columns at a time -> fp16 -> 128-bit global stores.
 // Every wait on an mbarrier is bounded; a wait that runs out raises the device status word and the
@@ -30,7 +32,8 @@ constexpr uint32_t kXBytes = 2 * kXHalfBytes;                  // 32 KiB
 constexpr uint32_t kWBytes = kTileRows * kStepCols * 2;        // 16 KiB
 constexpr uint32_t kGemmStageBytes = kXBytes + kWBytes;        // 48 KiB
 constexpr int kMaxGemmStages = 3;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;
+constexpr int kProducerWarps = 8, kTmaWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 256;
 
 struct GemmParams {
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
         mbar_init(bar_accum, 1);
         mbar_fence_init();
     }
-    if (warp == 5) {                            // TMEM: 256 columns (two 128-column fp32 accumulators)
+    if (warp == kMmaWarp) {                     // TMEM: 256 columns (two 128-column fp32 accumulators)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -119,26 +122,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
     bool ok = true;
 
-    if (warp < 4) {
+    if (warp < kProducerWarps) {
         // ================= decode producers =================
         const Lut<CODE> lut = lut_view<CODE>(p.lut_addr, p.L, p.S);
-        const int r = tid;                                   // row of the tile
+        const int group = warp >> 2;                         // takes steps it = group, group + 2, ...
+        const int r = tid & 127;                             // row of the tile
         const int64_t row = row0 + r;
         // TILED layout: unit u of row -> ((row >> 5) * n_units + u) * 32 + (row & 31)
         const uint4 *src = p.codes + ((row >> 5) * (int64_t)p.n_units) * 32 + (row & 31);
-        uint32_t prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
+        auto history = [&](int it) -> uint32_t {             // last word before step `it` (decoded by the other group)
+            if (it == 0) return p.carry_in ? __ldg(p.carry_in + row) : 0u;
+            return __ldg(reinterpret_cast<const uint32_t *>(src + ((int64_t)it * UPS - 1) * 32) + 3);
+        };
         uint4 nxt[UPS];
+        uint32_t nxt_prev = 0;
+        if (group < n_steps) {
 #pragma unroll
-        for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + (int64_t)q * 32);
-        for (int it = 0; it < n_steps && ok; ++it) {
+            for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)group * UPS + q) * 32);
+            nxt_prev = history(group);
+        }
+        for (int it = group; it < n_steps && ok; it += 2) {
             const int s = it % p.n_stages;
             const uint32_t par = ((uint32_t)(it / p.n_stages) & 1u) ^ 1u;
             uint4 cur[UPS];
 #pragma unroll
             for (int q = 0; q < UPS; ++q) cur[q] = nxt[q];
-            if (it + 1 < n_steps) {
+            uint32_t prevw = nxt_prev;
+            if (it + 2 < n_steps) {
 #pragma unroll
-                for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + 1) * UPS + q) * 32);
+                for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + 2) * UPS + q) * 32);
+                nxt_prev = history(it + 2);
             }
             ok = mbar_wait(bar_empty + 8 * s, par, p.status);          // the MMA is done with this stage's old contents
             if (!ok) break;
@@ -161,7 +174,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
             fence_proxy_async_smem();               // make the generic-proxy stores visible to the tensor core's reads
             mbar_arrive(bar_full_w + 8 * s);
         }
-    } else if (warp == 4) {
+    } else if (warp == kTmaWarp) {
         // ================= activation loads =================
         pdl_wait_prior_grids();
         if (lane == 0) {
@@ -197,38 +210,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
         }
     }
 
-    // ================= epilogue (warps 0-3): TMEM -> fp16 -> global =================
-    if (warp < 4) {
+    // ================= epilogue (warps 0-7): TMEM -> fp16 -> global =================
+    if (warp < kProducerWarps) {
         if (ok) ok = mbar_wait(bar_accum, 0, p.status);
         tc_fence_after();
         if (ok) {
+            const int h = warp >> 2, quarter = warp & 3;              // a warp may only touch TMEM lanes 32*(warp % 4) ...
+            const int64_t tok = (int64_t)tok0 + h * 128 + quarter * 32 + lane;
 #pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                const int64_t tok = (int64_t)tok0 + h * 128 + warp * 32 + lane;
-#pragma unroll 1
-                for (int c = 0; c < kTileRows / 32; ++c) {
-                    uint32_t v[32];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * 128 + c * 32);
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                        : "r"(taddr));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (tok < p.tokens) {
-                        __half *dst = p.y + tok * p.ld_y + row0 + c * 32;
+            for (int c = 0; c < kTileRows / 32; ++c) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 128 + c * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (tok < p.tokens) {
+                    __half *dst = p.y + tok * p.ld_y + row0 + c * 32;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t o[4];
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t o[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
-                            asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 8 * j), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                         : "memory");
-                        }
+                        for (int e = 0; e < 4; ++e)
+                            o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
+                        asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 8 * j), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                     : "memory");
                     }
                 }
             }
@@ -236,7 +247,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }

@@ -9,6 +9,7 @@ dequant-GEMV overlap the small kernel in front of it.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 
 import torch
@@ -48,16 +49,21 @@ class LlamaConfig:
 
 
 class Block:
-    def __init__(self, cfg: LlamaConfig, fmt: Format, seed: int, device, incoherent: bool):
-        q, kv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+    """One decoder block's weights.  With tensor parallelism (tp > 1) the block holds this rank's
+    shard: qkv and gate-up are split by output rows (heads / FFN channels), o and down by input
+    columns, and the Hadamard blocks are sized so that no block straddles a shard boundary."""
+
+    def __init__(self, cfg: LlamaConfig, fmt: Format, seed: int, device, incoherent: bool, tp: int = 1, norm_seed: int | None = None):
+        q, kv, ffn = cfg.heads * cfg.head_dim // tp, cfg.kv_heads * cfg.head_dim // tp, cfg.ffn // tp
         mk = lambda i, o, s: RPTCLinear.random(i, o, fmt, cfg.weight_scale, seed * 16 + s, device, incoherent)
         self.qkv = mk(cfg.hidden, q + 2 * kv, 0)
+        self.qkv.block_out = hadamard_block(math.gcd(q, kv))
         self.o = mk(q, cfg.hidden, 1)
-        self.gate_up = mk(cfg.hidden, 2 * cfg.ffn, 2)
+        self.gate_up = mk(cfg.hidden, 2 * ffn, 2)
         # gate and up are transformed separately, so that the fused SwiGLU kernel can own matching blocks of both
-        self.gate_up.block_out = hadamard_block(cfg.ffn)
-        self.down = mk(cfg.ffn, cfg.hidden, 3)
-        g = torch.Generator(device=device).manual_seed(seed * 16 + 9)
+        self.gate_up.block_out = hadamard_block(ffn)
+        self.down = mk(ffn, cfg.hidden, 3)
+        g = torch.Generator(device=device).manual_seed((seed if norm_seed is None else norm_seed) * 16 + 9)   # replicated
         self.norm1 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
         self.norm2 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
 
@@ -69,18 +75,26 @@ class RPTCLlama:
     """Random-init Llama-shape model with all block linears RPTC-quantised; batch-`rows` decode."""
 
     def __init__(self, cfg: LlamaConfig, fmt: Format | None = None, rows: int = 1, seed: int = 0, device="cuda",
-                 incoherent: bool = True):
+                 incoherent: bool = True, tp_world: int = 1, tp_rank: int = 0, tp_group=None):
+        """tp_world > 1: this object is rank `tp_rank`'s shard of a tensor-parallel model; the partial
+        outputs of the row-parallel layers (o, down) are summed over `tp_group` with an NCCL all-reduce.
+        Embedding, norms and output head are replicated (same seed on every rank)."""
         self.cfg, self.rows, self.device = cfg, rows, torch.device(device)
+        self.tp_world, self.tp_rank, self.tp_group = tp_world, tp_rank, tp_group
+        if cfg.heads % tp_world or cfg.kv_heads % tp_world or cfg.ffn % (tp_world * 64):
+            raise ValueError("heads, kv_heads and ffn/64 must be divisible by the tensor-parallel degree")
         self.fmt = fmt or Format(CODE_HASH, 2, 16, 8, LAYOUT_TILED)
-        self.blocks = [Block(cfg, self.fmt, seed * 1000 + i + 1, device, incoherent) for i in range(cfg.layers)]
+        self.blocks = [Block(cfg, self.fmt, (seed * 64 + tp_rank) * 1000 + i + 1, device, incoherent, tp_world,
+                             norm_seed=seed * 64000 + i + 1) for i in range(cfg.layers)]
         g = torch.Generator(device=device).manual_seed(seed * 1000 + 999)
         self.embed = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=device) * 0.02).to(torch.float16)
         self.head = (torch.randn(cfg.vocab, cfg.hidden, generator=g, device=device) * 0.02).to(torch.float16)
         self.norm_f = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
-        q, kv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        self.heads_l, self.kv_heads_l, self.ffn_l = cfg.heads // tp_world, cfg.kv_heads // tp_world, cfg.ffn // tp_world
+        q, kv = self.heads_l * cfg.head_dim, self.kv_heads_l * cfg.head_dim
         f16 = dict(dtype=torch.float16, device=device)
-        self.kcache = [torch.zeros((rows, cfg.max_pos, cfg.kv_heads, cfg.head_dim), **f16) for _ in range(cfg.layers)]
-        self.vcache = [torch.zeros((rows, cfg.max_pos, cfg.kv_heads, cfg.head_dim), **f16) for _ in range(cfg.layers)]
+        self.kcache = [torch.zeros((rows, cfg.max_pos, self.kv_heads_l, cfg.head_dim), **f16) for _ in range(cfg.layers)]
+        self.vcache = [torch.zeros((rows, cfg.max_pos, self.kv_heads_l, cfg.head_dim), **f16) for _ in range(cfg.layers)]
         # step workspace (fixed addresses, so that the step can live in a CUDA graph)
         self.ids = torch.zeros(rows, dtype=torch.int32, device=device)
         self.pos = torch.zeros(rows, dtype=torch.int32, device=device)
@@ -89,13 +103,14 @@ class RPTCLlama:
         self.xt = torch.zeros((rows, max(cfg.hidden, q)), **f16)
         self.qkv_out = torch.zeros((rows, q + 2 * kv), **f16)
         self.attn = torch.zeros((rows, q), **f16)
-        self.mlp = torch.zeros((rows, cfg.ffn), **f16)
+        self.mlp = torch.zeros((rows, self.ffn_l), **f16)
+        self.partial = torch.zeros((rows, cfg.hidden), **f16)
         self.logits = torch.zeros((rows, cfg.vocab), **f16)
         self.next_ids = torch.zeros(rows, dtype=torch.int64, device=device)
         f32 = dict(dtype=torch.float32, device=device)
         self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
         self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
-        self.acc_gu = torch.zeros((rows, 2 * cfg.ffn), **f32)
+        self.acc_gu = torch.zeros((rows, 2 * self.ffn_l), **f32)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
 
@@ -110,32 +125,42 @@ class RPTCLlama:
             xt = b.qkv.transform_in(self.xn, out=self.xt[:, : cfg.hidden])
             b.qkv.matvec_acc(xt, self.acc_qkv)
             b.qkv.finish(self.acc_qkv, out=self.qkv_out)
-            ops.rope_cache(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], cfg.heads, cfg.kv_heads, cfg.head_dim,
+            ops.rope_cache(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.heads_l, self.kv_heads_l, cfg.head_dim,
                            cfg.rope_theta)
-            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, cfg.heads, cfg.kv_heads,
+            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
                             cfg.head_dim)
             xt = b.o.transform_in(self.attn, out=self.xt[:, : self.attn.shape[1]])
             b.o.matvec_acc(xt, self.acc_h)
-            b.o.finish(self.acc_h, out=self.h, residual=self.h)
+            self._finish_row_parallel(b.o)
             ops.rmsnorm(self.h, b.norm2, self.xn, cfg.rms_eps)
             xt = b.gate_up.transform_in(self.xn, out=self.xt[:, : cfg.hidden])
             b.gate_up.matvec_acc(xt, self.acc_gu)
             if b.gate_up.incoherent:
-                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, cfg.ffn, b.down.block_in,
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
                                     b.gate_up.scale, 1.0, clear=True)
                 n_launch += 15
             else:
                 gu = b.gate_up.finish(self.acc_gu)
-                torch.mul(torch.nn.functional.silu(gu[:, : cfg.ffn]), gu[:, cfg.ffn:], out=self.mlp)
+                torch.mul(torch.nn.functional.silu(gu[:, : self.ffn_l]), gu[:, self.ffn_l:], out=self.mlp)
                 n_launch += 15
             b.down.matvec_acc(self.mlp, self.acc_h)
-            b.down.finish(self.acc_h, out=self.h, residual=self.h)
+            self._finish_row_parallel(b.down)
         ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         torch.argmax(self.logits, dim=1, out=self.next_ids)
         self.ids.copy_(self.next_ids)
         self.pos.add_(1)
         self.launches_per_step = n_launch + 2
+
+    def _finish_row_parallel(self, lin: RPTCLinear) -> None:
+        """h += (sum over tensor-parallel ranks of) this rank's partial output of a row-parallel layer."""
+        if self.tp_world == 1:
+            lin.finish(self.acc_h, out=self.h, residual=self.h)
+            return
+        import torch.distributed as dist
+        lin.finish(self.acc_h, out=self.partial)
+        dist.all_reduce(self.partial, group=self.tp_group)
+        self.h.add_(self.partial)
 
     def capture(self, pdl: bool = True) -> None:
         """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""
@@ -170,9 +195,9 @@ class RPTCLlama:
 
     def bytes_per_token(self, context: int) -> dict:
         cfg = self.cfg
-        packed = cfg.quantised_weights() * self.fmt.K // 8
+        packed = cfg.quantised_weights() * self.fmt.K // 8 // self.tp_world
         head = cfg.vocab * cfg.hidden * 2
-        kv = 2 * cfg.layers * context * cfg.kv_heads * cfg.head_dim * 2
+        kv = 2 * cfg.layers * context * self.kv_heads_l * cfg.head_dim * 2
         return {"packed": packed, "head": head, "kv": kv}
 
     # -- dense fp32 reference of the same model (decode weights with the GPU's bit-exact decompress) --------
@@ -194,20 +219,27 @@ class RPTCLlama:
             a, b = x[..., :half], x[..., half:]
             return torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1)
 
-        q_dim, kv_dim = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        q_dim, kv_dim = self.heads_l * cfg.head_dim, self.kv_heads_l * cfg.head_dim
         mask = torch.full((T, T), float("-inf"), device=self.device).triu(1)
+
+        def reduce(t):
+            if self.tp_world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(t, group=self.tp_group)
+            return t
+
         for b in self.blocks:
             x = rms(h, b.norm1)
             qkv = x @ b.qkv.effective_weight().t()
-            q = rope(qkv[..., :q_dim].reshape(-1, T, cfg.heads, cfg.head_dim))
-            k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(-1, T, cfg.kv_heads, cfg.head_dim))
-            v = qkv[..., q_dim + kv_dim:].reshape(-1, T, cfg.kv_heads, cfg.head_dim)
-            rep = cfg.heads // cfg.kv_heads
+            q = rope(qkv[..., :q_dim].reshape(-1, T, self.heads_l, cfg.head_dim))
+            k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(-1, T, self.kv_heads_l, cfg.head_dim))
+            v = qkv[..., q_dim + kv_dim:].reshape(-1, T, self.kv_heads_l, cfg.head_dim)
+            rep = self.heads_l // self.kv_heads_l
             k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
             att = torch.einsum("bthd,bshd->bhts", q, k) * cfg.head_dim ** -0.5 + mask
             o = torch.einsum("bhts,bshd->bthd", att.softmax(-1), v).reshape(-1, T, q_dim)
-            h = h + o @ b.o.effective_weight().t()
+            h = h + reduce(o @ b.o.effective_weight().t())
             x = rms(h, b.norm2)
             gu = x @ b.gate_up.effective_weight().t()
-            h = h + (torch.nn.functional.silu(gu[..., : cfg.ffn]) * gu[..., cfg.ffn:]) @ b.down.effective_weight().t()
+            h = h + reduce((torch.nn.functional.silu(gu[..., : self.ffn_l]) * gu[..., self.ffn_l:]) @ b.down.effective_weight().t())
         return rms(h, self.norm_f) @ self.head.float().t()

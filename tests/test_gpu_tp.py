@@ -1,0 +1,22 @@
+"""GPU test of the tensor-parallel decode engine: 2 ranks on 2 GPUs (NCCL all-reduce after each
+row-parallel layer), logits of every rank against a distributed fp32 torch forward of the same
+sharded network; tolerance max-rel 1e-2.  Skipped where fewer than 2 GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_decode_world2():
+    port = 29600 + os.getpid() % 1000
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(port)],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for p, out in zip(procs, outs):
+        assert p.returncode == 0, out[-2000:]

@@ -1,0 +1,48 @@
+"""Child process of tests/test_gpu_tp.py: one tensor-parallel rank on its own GPU (NCCL, NVLS off)."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "let-it-slide_b200"))
+
+
+def main():
+    rank, world, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rptc_b200 import ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=1024, layers=2, heads=8, kv_heads=2, ffn=2048, vocab=512, max_pos=16, weight_scale=0.05)
+    rows, T = 2, 6
+    model = RPTCLlama(cfg, rows=rows, seed=3, tp_world=world, tp_rank=rank)
+    g = torch.Generator(device="cuda").manual_seed(5)                    # same tokens on every rank
+    tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
+    ref = model.reference_logits(tokens)
+    worst = 0.0
+    for use_graph in (False, True):
+        model.reset()
+        if use_graph:
+            model.capture(pdl=True)
+        for t in range(T):
+            model.ids.copy_(tokens[:, t].to(torch.int32))
+            model.step()
+            torch.cuda.synchronize()
+            err = (model.logits.float() - ref[:, t]).abs().max().item() / ref[:, t].abs().max().item()
+            worst = max(worst, err)
+    ops.device_status()
+    same = torch.tensor([model.logits.float().sum().item()], device="cuda", dtype=torch.float64)
+    lo, hi = same.clone(), same.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    dist.destroy_process_group()
+    assert worst <= 1e-2, f"rank {rank}: logits off by {worst}"
+    assert abs(hi.item() - lo.item()) <= 1e-3 * abs(hi.item()) + 1e-3, "ranks disagree on the logits"
+    print(f"rank {rank} ok worst {worst:.2e}")
+
+
+if __name__ == "__main__":
+    main()
