@@ -273,6 +273,9 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
                "token_stream_gbs": (bt["packed"] + bt["head"] + bt["kv"]) / (ms / args.steps * 1e-3) / 1e9}
         print(json.dumps(out))
     if world > 1:
+        model.graph = None          # graphs that captured collectives must be gone before their communicator is torn down
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
 
 

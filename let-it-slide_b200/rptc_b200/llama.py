@@ -164,7 +164,8 @@ class RPTCLlama:
 
     def capture(self, pdl: bool = True) -> None:
         """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""
-        lib().rptc_set_pdl(1 if pdl else 0)
+        # Programmatic dependent launch is kept off when NCCL kernels sit in the same graph.
+        lib().rptc_set_pdl(1 if (pdl and self.tp_world == 1) else 0)
         ids0, pos0 = self.ids.clone(), self.pos.clone()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())

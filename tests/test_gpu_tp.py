@@ -17,6 +17,12 @@ def test_tensor_parallel_decode_world2():
     port = 29600 + os.getpid() % 1000
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(port)],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=240)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append("timed out\n" + p.communicate()[0])
     for p, out in zip(procs, outs):
         assert p.returncode == 0, out[-2000:]

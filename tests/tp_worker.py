@@ -12,7 +12,10 @@ def main():
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    # a short collective timeout: if the peer rank dies, this rank's next collective errors out instead of waiting
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
     cfg = LlamaConfig(hidden=1024, layers=2, heads=8, kv_heads=2, ffn=2048, vocab=512, max_pos=16, weight_scale=0.05)
@@ -21,11 +24,13 @@ def main():
     g = torch.Generator(device="cuda").manual_seed(5)                    # same tokens on every rank
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
+    print(f"rank {rank}: reference done", flush=True)
     worst = 0.0
     for use_graph in (False, True):
         model.reset()
         if use_graph:
             model.capture(pdl=True)
+        print(f"rank {rank}: graph={use_graph} ready", flush=True)
         for t in range(T):
             model.ids.copy_(tokens[:, t].to(torch.int32))
             model.step()
@@ -37,6 +42,10 @@ def main():
     lo, hi = same.clone(), same.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    # graphs that captured collectives must be gone before their communicator is torn down
+    model.graph = None
+    torch.cuda.synchronize()
+    print(f"rank {rank}: worst {worst:.2e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     assert worst <= 1e-2, f"rank {rank}: logits off by {worst}"
