@@ -118,6 +118,18 @@ int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, cons
 int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t m, int batch, float scale,
                      int accumulate, int clear, rptc_stream_t stream);
 
+/* The fused matvec for callers that cannot allocate device memory where they call this library (a server whose
+ * memory pool owns the whole device, a plugin that must not go around its host's allocator, a process with a
+ * frozen footprint).  Same product as rptc_gemv + rptc_gemv_finish, y[b][row] = fp16(sum_c W[row][c] x[b][c]),
+ * but the fp32 accumulator is a fixed 1 MiB array inside the library instead of caller scratch:
+ * batch * m <= 262144 or the call returns RPTC_ERR_TOO_LARGE.  It calls no allocating routine.  The first call
+ * on each device looks up the array's device address (make that call before any stream capture).  All calls
+ * on a device share the one array: calls that may overlap on the GPU (different streams) race and must be
+ * serialised by the caller.  It has no counterpart in the reference. */
+int rptc_gemv_f16_static(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x, void *y,
+                         int64_t ld_y, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
+                         rptc_stream_t stream);
+
 /* Fused decode + GEMM for prefill (tcgen05 tensor cores, TMEM accumulators):
  * y[t][row] = fp16( sum_c x[t][c] * W[row][c] ),  x fp16 [tokens][ld_x], y fp16 [tokens][ld_y].
  * No reference counterpart (the reference has batch-1 kernels only); the equivalent reference

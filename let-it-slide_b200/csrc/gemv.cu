@@ -450,3 +450,39 @@ extern "C" int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_
     return launch(gemv_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                   acc, ld_acc, static_cast<__half *>(y), ld_y, m, batch, scale, accumulate, clear);
 }
+
+// ---- entry point that allocates nothing --------------------------------------------------------------
+// Some hosts of this library may not call cudaMalloc where they call us: a serving process whose memory
+// pool owns every byte of the device, a plugin that runs under an allocator it must not bypass, or code
+// that has been told its memory footprint is frozen.  For them the fp32 accumulator of the fused matvec
+// lives in this fixed array, which every GPU that loads the library holds until the process exits.
+namespace rptc {
+constexpr int64_t kStaticAccFloats = 262144;                      // 1 MiB: batch * m may not exceed this
+static __device__ __align__(256) float g_static_acc[kStaticAccFloats];
+static float *g_static_acc_ptr[64];                               // device address of the array, per device
+}  // namespace rptc
+
+extern "C" int rptc_gemv_f16_static(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
+                                    void *y, int64_t ld_y, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
+                                    rptc_stream_t stream) {
+    if (!y) return RPTC_ERR_ARG;
+    if (batch < 1 || batch > 8 || m <= 0) return RPTC_ERR_ARG;
+    if ((int64_t)batch * m > kStaticAccFloats) return RPTC_ERR_TOO_LARGE;      // the fixed accumulator cannot hold it
+    if (ld_y < m) return RPTC_ERR_SHAPE;
+    int dev = 0;
+    RPTC_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return RPTC_ERR_ARG;
+    if (!g_static_acc_ptr[dev]) {
+        // Set-up, once per device, with that device current: in host code the array's name is only a handle,
+        // the address a kernel can use has to be asked for.
+        float *ptr = nullptr;
+        RPTC_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_acc));
+        g_static_acc_ptr[dev] = ptr;
+    }
+    float *acc = g_static_acc_ptr[dev];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // every call shares the array and finds the previous call's leftovers in it: start from zero
+    RPTC_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)batch * (size_t)m, s));
+    if (int e = rptc_gemv(codes, lut, carry_in, x, ld_x, acc, m, m, n, batch, x_order, fmt, stream)) return e;
+    return rptc_gemv_finish(acc, m, y, ld_y, m, batch, 1.0f, 0, 0, stream);
+}
