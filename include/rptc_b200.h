@@ -167,9 +167,23 @@ int rptc_rmsnorm(const void *x, int64_t ld_x, const void *w, void *out, int64_t 
  * q in place, rotated k and v appended to caches [rows][max_pos][hkv][d] at pos[row]. */
 int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, void *kcache, void *vcache, int64_t rows, int hq, int hkv,
                     int d, int max_pos, float theta, rptc_stream_t stream);
-/* Single-query attention of each row's q heads over cache positions [0, pos[row]]; d must be 128. */
+/* Single-query attention of each row's q heads over cache positions [0, pos[row]]; d must be 128.
+ * signs_in (fp16 [hq*128] or NULL): when given, each head's output is also put through the input-side
+ * transform of the output projection with one 128-wide Hadamard block per head, H(s * o) / sqrt(128). */
 int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
-                     int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, rptc_stream_t stream);
+                     int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, const void *signs_in,
+                     rptc_stream_t stream);
+/* Glue between two quantised layers of a decoder block in one launch (rows that are a single Hadamard
+ * block, n = 256..4096):  if acc: h += s_out * H(acc) * scale_out (acc cleared);  xn = rmsnorm(h) * w_norm;
+ * out = transform_in ? H(s_in * xn) / sqrt(n) : xn. */
+int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, void *h, int64_t ld_h,
+                              const void *w_norm, float eps, const void *signs_in, int transform_in, void *out, int64_t ld_out,
+                              int64_t rows, int64_t n, rptc_stream_t stream);
+/* Output side of a fused qkv layer + rotary embedding + KV-cache append: y = s_out * H(acc) * scale in blocks of
+ * `block` >= 128 columns of [q | k | v] (128 per head); rotated q -> q_out, rotated k and v -> caches at pos[row]. */
+int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *q_out, int64_t ld_q, void *kcache,
+                    void *vcache, const int32_t *pos, int64_t rows, int hq, int hkv, int max_pos, int block, float theta,
+                    rptc_stream_t stream);
 /* Dense fp16 matvec y[b] = W x[b] (fp32 accumulation), batch 1..8: the output head, and the dense-bandwidth
  * probe the reference's tests call `matvec` (rptc_kernels/tests/test_matvec.py:18, not exported by wrapper.cpp). */
 int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,

@@ -31,6 +31,18 @@ __device__ __forceinline__ void load8_f16(const __half *p, float (&v)[8]) {
         v[2 * i] = f.x, v[2 * i + 1] = f.y;
     }
 }
+__device__ __forceinline__ void unpack8(const uint4 a, float (&v)[8]) {
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(u32_as_half2(w[i]));
+        v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+}
+// eight fp16 values as raw bits; a null pointer reads as eight ones (0x3C00)
+__device__ __forceinline__ uint4 raw8_or_ones(const __half *p) {
+    return p ? *reinterpret_cast<const uint4 *>(p) : make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
+}
 __device__ __forceinline__ void load8_f32(float *p, float (&v)[8], bool clear) {
     const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
@@ -70,25 +82,45 @@ __device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
         }
     }
     if (block > 256) {
+        // Strides 256 .. block/2 mix the 256-element groups: element 256*g + r with element 256*g' + r.  Through
+        // shared memory each of the first chunk/16 threads takes the G = block/256 group values of one r,
+        // transforms them in registers, and puts them back (two barriers instead of one per stride).
+        const int G = block >> 8;                      // 2, 4, 8 or 16
         __syncthreads();          // the buffer may still be read from an earlier transform
 #pragma unroll
         for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
         __syncthreads();
-        for (int h = 256; h < block; h <<= 1) {
+        const int n_items = (int)blockDim.x * 8 / G;       // (block index, r) pairs in the chunk
+        for (int item = t; item < n_items; item += blockDim.x) {
+            const int blk = item >> 8, r = item & 255;
+            float *base = ex + blk * block + r;
+            float z[16];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {          // chunk / 2 pairs over chunk / 8 threads
-                const int q = t + k * (int)blockDim.x;
-                const int i = ((q / h) * 2 * h) + (q % h);
-                const float a = ex[i], b = ex[i + h];
-                ex[i] = a + b;
-                ex[i + h] = a - b;
+            for (int g = 0; g < 16; ++g) z[g] = g < G ? base[256 * g] : 0.f;
+#pragma unroll
+            for (int h = 1; h < 16; h <<= 1) {
+                if (h < G) {
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) {
+                        if ((g & h) == 0) {
+                            const float a = z[g], b = z[g + h];
+                            z[g] = a + b;
+                            z[g + h] = a - b;
+                        }
+                    }
+                }
             }
-            __syncthreads();
+#pragma unroll
+            for (int g = 0; g < 16; ++g)
+                if (g < G) base[256 * g] = z[g];
         }
+        __syncthreads();
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
     }
 }
+
+__device__ __forceinline__ float hadamard_norm_dev(int block) { return rsqrtf((float)block); }
 
 __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
     __shared__ float ex[4096];
@@ -144,16 +176,17 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
     const int64_t row = blockIdx.y;
     const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
     float g[8], u[8], sg[8];
+    const uint4 raw_sg = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
+    const uint4 raw_su = raw8_or_ones(p.signs_out ? p.signs_out + p.n + col : nullptr);
+    const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
     load8_f32(p.acc + row * p.ld_acc + col, g, p.clear != 0);
     load8_f32(p.acc + row * p.ld_acc + p.n + col, u, p.clear != 0);
     fwht8(g, p.block, ex);
     fwht8(u, p.block, ex);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
-    if (p.signs_out) load8_f16(p.signs_out + col, sg);
+    unpack8(raw_sg, sg);
 #pragma unroll
     for (int i = 0; i < 8; ++i) g[i] *= p.scale_out * sg[i];
-    if (p.signs_out) load8_f16(p.signs_out + p.n + col, sg);
+    unpack8(raw_su, sg);
 #pragma unroll
     for (int i = 0; i < 8; ++i) u[i] *= p.scale_out * sg[i];
     // the layer's own output is fp16; round there as the unfused path would
@@ -162,15 +195,150 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
         const float gg = __half2float(__float2half_rn(g[i])), uu = __half2float(__float2half_rn(u[i]));
         g[i] = __half2float(__float2half_rn(gg / (1.f + __expf(-gg)) * uu));
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sg[i] = 1.f;
-    if (p.signs_in) load8_f16(p.signs_in + col, sg);
+    unpack8(raw_si, sg);
 #pragma unroll
     for (int i = 0; i < 8; ++i) g[i] *= sg[i];
     fwht8(g, p.block, ex);
 #pragma unroll
     for (int i = 0; i < 8; ++i) g[i] *= p.scale_in;
     store8_f16(p.out + row * p.ld_out + col, g);
+}
+
+// ---- fused glue kernels of the decode step ------------------------------------------------------------
+// They exist to shorten the chain of small dependent launches between two fused dequant-GEMVs.
+
+__device__ __forceinline__ float block_sum(float v, float *red) {      // red: >= 17 floats; all threads call
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    __syncthreads();
+    if ((t & 31) == 0) red[t >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    return tot;
+}
+
+// (1) optional: h = residual + s_out * H(acc) * scale   (the output side of a row's previous layer; acc cleared)
+// (2) xn = rmsnorm(h) * w_norm
+// (3) out = H(s_in * xn) * norm   (the input side of the next layer), or out = xn when no transform is wanted.
+// One CTA per row; the row must be a single Hadamard block (n == block <= 4096).
+struct FinishNormParams {
+    float *acc;                  // fp32 [rows][ld_acc] or NULL (then h is read as it is)
+    int64_t ld_acc;
+    const __half *signs_out;     // [n] or NULL
+    float scale_out;
+    __half *h;                   // fp16 [rows][ld_h]: residual in, updated residual out
+    int64_t ld_h;
+    const __half *w_norm;        // [n]
+    float eps;
+    const __half *signs_in;      // [n] or NULL
+    int transform_in;            // apply the input-side Hadamard transform to the normalised row
+    __half *out;                 // fp16 [rows][ld_out]
+    int64_t ld_out;
+    int32_t n;
+};
+
+__global__ void __launch_bounds__(512) finish_norm_hadamard_kernel(const FinishNormParams p) {
+    __shared__ float ex[4096];
+    __shared__ float red[20];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    const int col = 8 * t;
+    const float hn = hadamard_norm_dev(p.n);
+    // every global load is issued before the first dependent use: one memory round trip for the kernel
+    const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
+    const uint4 raw_h = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
+    const uint4 raw_w = *reinterpret_cast<const uint4 *>(p.w_norm + col);
+    const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
+    float v[8], sg[8];
+    if (p.acc) {
+        load8_f32(p.acc + row * p.ld_acc + col, v, true);
+        fwht8(v, p.n, ex);
+        unpack8(raw_so, sg);
+        float r[8];
+        unpack8(raw_h, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = r[i] + v[i] * (p.scale_out * hn) * sg[i];
+        store8_f16(p.h + row * p.ld_h + col, v);
+        // continue from the rounded residual stream, as an unfused reader of h would
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i]));
+    } else {
+        unpack8(raw_h, v);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    const float inv = rsqrtf(block_sum(ss, red) / p.n + p.eps);
+    float w[8];
+    unpack8(raw_w, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i] * inv * w[i]));
+    if (p.transform_in) {
+        unpack8(raw_si, sg);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= sg[i];
+        fwht8(v, p.n, ex);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= hn;
+    }
+    store8_f16(p.out + row * p.ld_out + col, v);
+}
+
+// Output side of the fused qkv layer, rotary embedding and KV-cache append in one pass:
+// y = s_out * H(acc) * scale over blocks of `block` (>= 128) columns of [q heads | k heads | v heads];
+// q is rotated and written to `q_out`, rotated k and v go to the caches at pos[row].  Head size 128,
+// rotate-half pairing (i, i + 64): the partner of a thread's eight columns sits eight threads away.
+struct QkvFinishParams {
+    float *acc;
+    int64_t ld_acc;
+    const __half *signs_out;
+    float scale;
+    __half *q_out;               // fp16 [rows][ld_q], hq * 128 columns
+    int64_t ld_q;
+    __half *kcache, *vcache;     // [rows][max_pos][hkv][128]
+    const int32_t *pos;
+    int32_t hq, hkv, max_pos, block, chunk;
+    float theta;
+};
+
+__global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p) {
+    __shared__ float ex[4096];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.y;
+    const int col = blockIdx.x * p.chunk + 8 * t;
+    float v[8], sg[8];
+    const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
+    const int ps = p.pos[row];
+    load8_f32(p.acc + row * p.ld_acc + col, v, true);
+    fwht8(v, p.block, ex);
+    unpack8(raw_so, sg);
+    const float sc = p.scale * hadamard_norm_dev(p.block);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i] * sc * sg[i]));     // the layer's fp16 output
+    const int head = col >> 7, idx = col & 127;
+    if (head < p.hq + p.hkv) {
+        const bool upper = idx >= 64;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
+            const int j = (idx & 63) + i;                       // frequency index
+            float sn, cs;
+            sincosf(ps * __powf(p.theta, -2.f * j / 128.f), &sn, &cs);
+            o[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
+        }
+        __half *dst = head < p.hq ? p.q_out + row * p.ld_q + col
+                                  : p.kcache + ((row * p.max_pos + ps) * p.hkv + (head - p.hq)) * 128 + idx;
+        store8_f16(dst, o);
+    } else {
+        store8_f16(p.vcache + ((row * p.max_pos + ps) * p.hkv + (head - p.hq - p.hkv)) * 128 + idx, v);
+    }
 }
 
 static float hadamard_norm(int block) {
@@ -245,4 +413,63 @@ extern "C" int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64
     p.scale_in = scale_in * hadamard_norm(block);
     return launch(swiglu_hadamard_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0,
                   static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, void *h, int64_t ld_h,
+                                         const void *w_norm, float eps, const void *signs_in, int transform_in, void *out,
+                                         int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream) {
+    if (!h || !w_norm || !out) return RPTC_ERR_ARG;
+    if (n < 256 || n > 4096 || (n & (n - 1))) return RPTC_ERR_UNSUPPORTED;      // one Hadamard block per row
+    if (rows <= 0 || ld_h < n || ld_out < n || (acc && ld_acc < n)) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(w_norm) & 15) ||
+        (acc && (reinterpret_cast<uintptr_t>(acc) & 15)) || (ld_h % 8) || (ld_out % 8) || (ld_acc % 4))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    FinishNormParams p;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.signs_out = static_cast<const __half *>(signs_out);
+    p.scale_out = scale_out;
+    p.h = static_cast<__half *>(h);
+    p.ld_h = ld_h;
+    p.w_norm = static_cast<const __half *>(w_norm);
+    p.eps = eps;
+    p.signs_in = static_cast<const __half *>(signs_in);
+    p.transform_in = transform_in;
+    p.out = static_cast<__half *>(out);
+    p.ld_out = ld_out;
+    p.n = (int32_t)n;
+    return launch(finish_norm_hadamard_kernel, dim3((unsigned)rows), dim3((unsigned)(n / 8)), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *q_out, int64_t ld_q,
+                               void *kcache, void *vcache, const int32_t *pos, int64_t rows, int hq, int hkv, int max_pos, int block,
+                               float theta, rptc_stream_t stream) {
+    if (!acc || !q_out || !kcache || !vcache || !pos) return RPTC_ERR_ARG;
+    if (block < 128 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
+    const int64_t n = (int64_t)(hq + 2 * hkv) * 128;
+    const int chunk = block < 256 ? 256 : block;
+    if (rows <= 0 || rows > 65535 || hq <= 0 || hkv <= 0 || (n % chunk) || ld_acc < n || ld_q < (int64_t)hq * 128 || max_pos <= 0)
+        return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(q_out) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15) ||
+        (reinterpret_cast<uintptr_t>(vcache) & 15) || (ld_acc % 4) || (ld_q % 8))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    QkvFinishParams p;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.signs_out = static_cast<const __half *>(signs_out);
+    p.scale = scale;
+    p.q_out = static_cast<__half *>(q_out);
+    p.ld_q = ld_q;
+    p.kcache = static_cast<__half *>(kcache);
+    p.vcache = static_cast<__half *>(vcache);
+    p.pos = pos;
+    p.hq = hq;
+    p.hkv = hkv;
+    p.max_pos = max_pos;
+    p.block = block;
+    p.chunk = chunk;
+    p.theta = theta;
+    return launch(qkv_finish_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0, static_cast<cudaStream_t>(stream), p);
 }

@@ -85,14 +85,18 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     }
 }
 
-// Single-query attention over the cache: one CTA of 128 threads per (row, q head); d == 128.
-// scores -> shared memory, softmax, then thread c accumulates output column c.
-__global__ void __launch_bounds__(128) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv, const int32_t *__restrict__ pos,
-                                                          const __half *__restrict__ kcache, const __half *__restrict__ vcache,
-                                                          __half *__restrict__ out, int64_t ld_out, int hq, int hkv, int max_pos,
-                                                          float scale) {
-    extern __shared__ float sc[];       // [ctx]
-    __shared__ float red[4];
+// Single-query attention over the cache: one CTA of 256 threads per (row, q head); d == 128.
+// Both passes are spread over the 8 warps by position (a warp reads one 256-byte K or V row per step,
+// four steps in flight), partial outputs meet in shared memory.
+constexpr int kAttnThreads = 256, kAttnWarps = 8;
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv,
+                                                                  const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
+                                                                  const __half *__restrict__ vcache, __half *__restrict__ out,
+                                                                  int64_t ld_out, int hq, int hkv, int max_pos, float scale,
+                                                                  const __half *__restrict__ signs_in) {
+    extern __shared__ float sc[];       // [max(ctx, 128)] scores, later the 128 outputs
+    __shared__ float red[kAttnWarps];
+    __shared__ float part[kAttnWarps][128];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     constexpr int D = 128;
@@ -102,23 +106,38 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half *__restri
     const __half *q = qkv + (int64_t)row * ld_qkv + (int64_t)head * D;
     const float2 q01 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane]);
     const float2 q23 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane + 1]);
-    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D;
-    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D;
+    const int64_t stride = (int64_t)hkv * D;
+    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
+    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
+    // ---- scores ----
     float mx = -1e30f;
-    for (int j = warp; j < ctx; j += 4) {
-        const uint2 kk = *reinterpret_cast<const uint2 *>(kb + (int64_t)j * hkv * D + 4 * lane);
-        const float2 k01 = __half22float2(u32_as_half2(kk.x)), k23 = __half22float2(u32_as_half2(kk.y));
-        float s = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
-        s = warp_sum(s) * scale;
-        if (lane == 0) sc[j] = s;
-        mx = fmaxf(mx, s);
+    for (int j0 = warp; j0 < ctx; j0 += 4 * kAttnWarps) {
+        uint2 kk[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * kAttnWarps;
+            kk[u] = j < ctx ? *reinterpret_cast<const uint2 *>(kb + j * stride) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * kAttnWarps;
+            const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
+            float s = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+            s = warp_sum(s) * scale;
+            if (j < ctx) {
+                if (lane == 0) sc[j] = s;
+                mx = fmaxf(mx, s);
+            }
+        }
     }
     if (lane == 0) red[warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) mx = fmaxf(mx, red[w]);
     __syncthreads();
     float sum = 0.f;
-    for (int j = t; j < ctx; j += 128) {
+    for (int j = t; j < ctx; j += kAttnThreads) {
         const float e = __expf(sc[j] - mx);
         sc[j] = e;
         sum += e;
@@ -126,10 +145,54 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __half *__restri
     sum = warp_sum(sum);
     if (lane == 0) red[warp] = sum;
     __syncthreads();
-    const float inv = 1.f / (red[0] + red[1] + red[2] + red[3]);
-    float acc = 0.f;
-    for (int j = 0; j < ctx; ++j) acc += sc[j] * __half2float(vb[(int64_t)j * hkv * D + t]);
-    out[(int64_t)row * ld_out + (int64_t)head * D + t] = __float2half_rn(acc * inv);
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) tot += red[w];
+    const float inv = 1.f / tot;
+    // ---- weighted sum of V: lane owns dims 4*lane .. 4*lane+3 of its warp's positions ----
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int j0 = warp; j0 < ctx; j0 += 4 * kAttnWarps) {
+        uint2 vv[4];
+        float pw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * kAttnWarps;
+            vv[u] = j < ctx ? *reinterpret_cast<const uint2 *>(vb + j * stride) : make_uint2(0u, 0u);
+            pw[u] = j < ctx ? sc[j] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float2 v01 = __half22float2(u32_as_half2(vv[u].x)), v23 = __half22float2(u32_as_half2(vv[u].y));
+            a0 += pw[u] * v01.x, a1 += pw[u] * v01.y, a2 += pw[u] * v23.x, a3 += pw[u] * v23.y;
+        }
+    }
+    *reinterpret_cast<float4 *>(&part[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+    __syncthreads();
+    if (t < D) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) acc += part[w][t];
+        float o = __half2float(__float2half_rn(acc * inv));            // the attention output in fp16
+        if (signs_in) {
+            // input-side transform of the output projection, one 128-wide Hadamard block per head:
+            // o <- H_128(s * o) / sqrt(128); thread t holds element t (threads 0..127 = warps 0..3)
+            o *= __half2float(signs_in[head * D + t]);
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, o, m);
+                o = (lane & m) ? other - o : o + other;
+            }
+            sc[t] = o;                                                   // scores are no longer needed
+        }
+        if (signs_in) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");             // only the four warps that hold outputs
+            const float e0 = sc[lane], e1 = sc[32 + lane], e2 = sc[64 + lane], e3 = sc[96 + lane];
+            const float b0 = e0 + e1, b1 = e0 - e1, b2 = e2 + e3, b3 = e2 - e3;
+            const float c = warp == 0 ? b0 + b2 : warp == 1 ? b1 + b3 : warp == 2 ? b0 - b2 : b1 - b3;
+            o = c * 0.08838834764831845f;
+        }
+        out[(int64_t)row * ld_out + (int64_t)head * D + t] = __float2half_rn(o);
+    }
 }
 
 // Dense fp16 matvec  y[b][r] = sum_c W[r][c] x[b][c]  (fp32 accumulation), one warp per row of W, the
@@ -204,7 +267,8 @@ extern "C" int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, vo
 }
 
 extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
-                                int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, rptc_stream_t stream) {
+                                int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, const void *signs_in,
+                                rptc_stream_t stream) {
     if (!qkv || !pos || !kcache || !vcache || !out) return RPTC_ERR_ARG;
     if (d != 128) return RPTC_ERR_UNSUPPORTED;
     if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || max_pos <= 0 || max_pos > 32768) return RPTC_ERR_SHAPE;
@@ -215,9 +279,10 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
         RPTC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
         configured = true;
     }
-    return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(128), (size_t)max_pos * 4, static_cast<cudaStream_t>(stream),
+    const size_t smem = (size_t)(max_pos < 128 ? 128 : max_pos) * 4;
+    return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), smem, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
-                  static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale);
+                  static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in));
 }
 
 extern "C" int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,

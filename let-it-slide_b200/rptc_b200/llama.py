@@ -59,6 +59,7 @@ class Block:
         self.qkv = mk(cfg.hidden, q + 2 * kv, 0)
         self.qkv.block_out = hadamard_block(math.gcd(q, kv))
         self.o = mk(q, cfg.hidden, 1)
+        self.o.block_in = min(self.o.block_in, cfg.head_dim)      # one Hadamard block per head: fuses into the attention kernel
         self.gate_up = mk(cfg.hidden, 2 * ffn, 2)
         # gate and up are transformed separately, so that the fused SwiGLU kernel can own matching blocks of both
         self.gate_up.block_out = hadamard_block(ffn)
@@ -115,7 +116,54 @@ class RPTCLlama:
         self.launches_per_step = 0
 
     # -- one token for every row ---------------------------------------------------------------------
+    def _fusable(self) -> bool:
+        """The short chain (9 launches per block) needs incoherent layers, no tensor parallelism, and a
+        hidden size that is a single Hadamard block."""
+        n = self.cfg.hidden
+        return (self.tp_world == 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 4096
+                and self.cfg.head_dim == 128)
+
     def step_eager(self) -> None:
+        if self._fusable():
+            self._step_fused()
+        else:
+            self._step_unfused()
+
+    def _step_fused(self) -> None:
+        cfg = self.cfg
+        q_dim = self.heads_l * cfg.head_dim
+        ops.embed(self.embed, self.ids, self.h)
+        b0 = self.blocks[0]
+        xt = self.xt[:, : cfg.hidden]
+        ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
+        n_launch = 2
+        for i, b in enumerate(self.blocks):
+            b.qkv.matvec_acc(xt, self.acc_qkv)
+            ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                           self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                            cfg.head_dim, signs_in=b.o.signs_in)
+            b.o.matvec_acc(self.attn, self.acc_h)
+            ops.finish_norm_hadamard(self.acc_h, b.o.signs_out, b.o.scale, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in, True, xt)
+            b.gate_up.matvec_acc(xt, self.acc_gu)
+            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                b.gate_up.scale, 1.0, clear=True)
+            b.down.matvec_acc(self.mlp, self.acc_h)
+            if i + 1 < len(self.blocks):
+                nb = self.blocks[i + 1]
+                ops.finish_norm_hadamard(self.acc_h, b.down.signs_out, b.down.scale, self.h, nb.norm1, cfg.rms_eps,
+                                         nb.qkv.signs_in, True, xt)
+            else:
+                ops.finish_norm_hadamard(self.acc_h, b.down.signs_out, b.down.scale, self.h, self.norm_f, cfg.rms_eps, None, False,
+                                         self.xn)
+            n_launch += 9
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        torch.argmax(self.logits, dim=1, out=self.next_ids)
+        self.ids.copy_(self.next_ids)
+        self.pos.add_(1)
+        self.launches_per_step = n_launch + 1
+
+    def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
         n_launch = 0
         ops.embed(self.embed, self.ids, self.h)
@@ -138,11 +186,10 @@ class RPTCLlama:
             if b.gate_up.incoherent:
                 ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
                                     b.gate_up.scale, 1.0, clear=True)
-                n_launch += 15
             else:
                 gu = b.gate_up.finish(self.acc_gu)
                 torch.mul(torch.nn.functional.silu(gu[:, : self.ffn_l]), gu[:, self.ffn_l:], out=self.mlp)
-                n_launch += 15
+            n_launch += 15
             b.down.matvec_acc(self.mlp, self.acc_h)
             self._finish_row_parallel(b.down)
         ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)

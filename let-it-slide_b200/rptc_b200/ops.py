@@ -193,13 +193,35 @@ def rope_cache(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcach
 
 
 def attn_decode(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, out: torch.Tensor, hq: int,
-                hkv: int, d: int) -> torch.Tensor:
+                hkv: int, d: int, signs_in: torch.Tensor | None = None) -> torch.Tensor:
     rows = qkv.shape[0]
     with torch.cuda.device(qkv.device):
         check(lib().rptc_attn_decode(ptr(qkv), _ld(qkv, qkv.shape[1]), ptr(pos), ptr(kcache), ptr(vcache), ptr(out),
-                                     _ld(out, out.shape[1]), rows, hq, hkv, d, kcache.shape[1], d ** -0.5, stream_ptr()),
-              "rptc_attn_decode")
+                                     _ld(out, out.shape[1]), rows, hq, hkv, d, kcache.shape[1], d ** -0.5, ptr(signs_in),
+                                     stream_ptr()), "rptc_attn_decode")
     return out
+
+
+def finish_norm_hadamard(acc: torch.Tensor | None, signs_out: torch.Tensor | None, scale_out: float, h: torch.Tensor,
+                         w_norm: torch.Tensor, eps: float, signs_in: torch.Tensor | None, transform_in: bool,
+                         out: torch.Tensor) -> torch.Tensor:
+    """h += output transform of acc; out = input transform of rmsnorm(h) (rptc_finish_norm_hadamard)."""
+    rows, n = h.shape
+    with torch.cuda.device(h.device):
+        check(lib().rptc_finish_norm_hadamard(ptr(acc), 0 if acc is None else _ld(acc, n), ptr(signs_out), scale_out, ptr(h),
+                                              _ld(h, n), ptr(w_norm), eps, ptr(signs_in), int(transform_in), ptr(out),
+                                              _ld(out, n), rows, n, stream_ptr()), "rptc_finish_norm_hadamard")
+    return out
+
+
+def qkv_finish(acc: torch.Tensor, signs_out: torch.Tensor | None, scale: float, q_out: torch.Tensor, kcache: torch.Tensor,
+               vcache: torch.Tensor, pos: torch.Tensor, hq: int, hkv: int, block: int, theta: float) -> None:
+    """Output transform of the fused qkv layer + RoPE + KV-cache append (rptc_qkv_finish)."""
+    rows = acc.shape[0]
+    with torch.cuda.device(acc.device):
+        check(lib().rptc_qkv_finish(ptr(acc), _ld(acc, acc.shape[1]), ptr(signs_out), scale, ptr(q_out), _ld(q_out, q_out.shape[1]),
+                                    ptr(kcache), ptr(vcache), ptr(pos), rows, hq, hkv, kcache.shape[1], block, theta,
+                                    stream_ptr()), "rptc_qkv_finish")
 
 
 def dense_gemv(W: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
