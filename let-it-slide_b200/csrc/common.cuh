@@ -247,50 +247,58 @@ struct GroupShape {
     static constexpr int kPairs = kWeights / 2;
 };
 
-template <int CODE, int K, typename Emit>
-__device__ __forceinline__ void decode_group(const uint32_t (&w)[GroupShape<K>::kWords], uint32_t halo,
-                                             const Lut<CODE> &lut, Emit &&emit) {
+// Window registers of a group: R[o] covers stream bits [16o-16, 16o+16) of the group.
+template <int K>
+__device__ __forceinline__ void make_windows(const uint32_t (&w)[GroupShape<K>::kWords], uint32_t halo,
+                                             uint32_t (&R)[2 * GroupShape<K>::kWords]) {
     constexpr int NW = GroupShape<K>::kWords;
-    uint32_t R[2 * NW];
 #pragma unroll
     for (int i = 0; i < NW; ++i) {
         R[2 * i] = __funnelshift_l(w[i], i == 0 ? halo : w[i - 1], 16);
         R[2 * i + 1] = w[i];
     }
+}
+
+// Weight pair p (columns 2p, 2p+1) of a group from its window registers.  `p` must be a constant after unrolling.
+template <int CODE, int K>
+__device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[2 * GroupShape<K>::kWords], const Lut<CODE> &lut, int p) {
     if (CODE == RPTC_CODE_LUT) {
+        uint32_t h[2];
 #pragma unroll
-        for (int p = 0; p < GroupShape<K>::kPairs; ++p) {
-            uint32_t h[2];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int e = K * (2 * p + q + 1);
-                const int o = (e - 1) >> 4;
-                const int sh = 16 * (o + 1) - e;
-                const uint32_t state = (R[o] >> sh) & lut.mask;
-                h[q] = lds16(lut.base + 2u * state);
-            }
-            emit(p, u32_as_half2(h[0] | (h[1] << 16)));
-        }
-    } else {
-        constexpr int BPS = 2 * K;   // bits per step
-#pragma unroll
-        for (int p = 0; p < GroupShape<K>::kPairs; ++p) {
-            const int e = BPS * (p + 1);
+        for (int q = 0; q < 2; ++q) {
+            const int e = K * (2 * p + q + 1);
             const int o = (e - 1) >> 4;
             const int sh = 16 * (o + 1) - e;
-            const uint32_t t = R[o] >> sh;
-            if (CODE == RPTC_CODE_HASH) {
-                const uint32_t h = t * t + t;
-                emit(p, u32_as_half2(lds32_hash((h & 0xFF00u) | lut.base)));
-            } else {
-                // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
-                // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.
-                uint32_t h = t * (2u * t + 1u);
-                h ^= h >> lut.shift;
-                emit(p, u32_as_half2(lds32(lut.base + ((h & lut.mask) << 7))));
-            }
+            const uint32_t state = (R[o] >> sh) & lut.mask;
+            h[q] = lds16(lut.base + 2u * state);
+        }
+        return u32_as_half2(h[0] | (h[1] << 16));
+    } else {
+        constexpr int BPS = 2 * K;   // bits per step
+        const int e = BPS * (p + 1);
+        const int o = (e - 1) >> 4;
+        const int sh = 16 * (o + 1) - e;
+        const uint32_t t = R[o] >> sh;
+        if (CODE == RPTC_CODE_HASH) {
+            const uint32_t h = t * t + t;
+            return u32_as_half2(lds32_hash((h & 0xFF00u) | lut.base));
+        } else {
+            // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
+            // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.
+            uint32_t h = t * (2u * t + 1u);
+            h ^= h >> lut.shift;
+            return u32_as_half2(lds32(lut.base + ((h & lut.mask) << 7)));
         }
     }
+}
+
+template <int CODE, int K, typename Emit>
+__device__ __forceinline__ void decode_group(const uint32_t (&w)[GroupShape<K>::kWords], uint32_t halo,
+                                             const Lut<CODE> &lut, Emit &&emit) {
+    uint32_t R[2 * GroupShape<K>::kWords];
+    make_windows<K>(w, halo, R);
+#pragma unroll
+    for (int p = 0; p < GroupShape<K>::kPairs; ++p) emit(p, decode_pair<CODE, K>(R, lut, p));
 }
 
 #endif  // __CUDACC__

@@ -20,16 +20,22 @@
 
 namespace rptc {
 
-constexpr int kGemvThreads = 512;
+#ifndef RPTC_GEMV_THREADS
+#define RPTC_GEMV_THREADS 512
+#endif
+#ifndef RPTC_GEMV_STAGES
+#define RPTC_GEMV_STAGES 3
+#endif
+constexpr int kGemvThreads = RPTC_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kStages = 3;                       // ring depth per warp
+constexpr int kStages = RPTC_GEMV_STAGES;        // ring depth per warp
 constexpr int kStageUnits = 2;                   // units per bulk copy
 constexpr uint32_t kUnitBytes = 512;             // 32 rows x 128 bits
 constexpr uint32_t kStageBytes = kStageUnits * kUnitBytes;
 constexpr uint32_t kBarBytes = 1024;             // kGemvWarps * kStages * 8 <= 1024
 constexpr uint32_t kRingBytes = kGemvWarps * kStages * kStageBytes;
 static_assert(kGemvWarps * kStages * 8 <= kBarBytes, "barrier area too small");
-static_assert(kBarBytes + kRingBytes + 2048 <= kHashLutWindow, "ring must fit below the HASH table window");
+static_assert(kBarBytes + kRingBytes + 1024 <= kHashLutWindow, "ring must fit below the HASH table window");
 
 struct GemvParams {
     const uint4 *codes;
@@ -220,46 +226,52 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
             const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
             const uint32_t xg = xs + (uint32_t)(gi * GU) * (WPU * 2u);
+            // Both units of the granule are decoded in one straight-line block so that their lookups overlap.
+            // A short granule (last of a block with an odd unit count) decodes zero words against the first
+            // unit's activations and its sum is dropped.
+            uint4 vq[GU];
 #pragma unroll
             for (int q = 0; q < GU; ++q) {
-                if (q < units) {
-                    uint4 v;
-                    if (TMA) {
-                        v = lds128(stage_base + q * kUnitBytes);
-                    } else {
-                        v = nextv;
-                        if (k + 1 < count) nextv = ldg128_stream(next_unit_ptr());
-                    }
-                    uint32_t halo = prevw;
-                    if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
-                        const int32_t u = useg0 + gi;
-                        if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
-                            if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
-                            else if (u > 0) halo = prevw >> 16;
-                        }
-                    }
-                    prevw = v.w;
-                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                    const uint32_t xu = xg + q * (WPU * 2u);
-                    __half2 hacc[BATCH][4];
-                    uint4 xv[BATCH];
-                    decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
-                        if ((pi & 3) == 0) {
+                if (TMA) {
+                    vq[q] = q < units ? lds128(stage_base + q * kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
+                } else {
+                    vq[q] = nextv;
+                    if (k + 1 < count) nextv = ldg128_stream(next_unit_ptr());
+                }
+            }
 #pragma unroll
-                            for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
-                        }
+            for (int q = 0; q < GU; ++q) {
+                const uint4 v = vq[q];
+                const bool valid = q < units;
+                uint32_t halo = prevw;
+                if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
+                    const int32_t u = useg0 + gi;
+                    if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
+                        if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
+                        else if (u > 0) halo = prevw >> 16;
+                    }
+                }
+                if (valid) prevw = v.w;
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                const uint32_t xu = xg + (valid ? q : 0) * (WPU * 2u);
+                __half2 hacc[BATCH][4];
+                uint4 xv[BATCH];
+                decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                    if ((pi & 3) == 0) {
 #pragma unroll
-                        for (int b = 0; b < BATCH; ++b) {
-                            const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                            hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
-                        }
-                    });
+                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                    }
 #pragma unroll
                     for (int b = 0; b < BATCH; ++b) {
-                        const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
-                        const float2 f2 = __half22float2(s);
-                        facc[b] += f2.x + f2.y;
+                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                        hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
                     }
+                });
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
+                    const float2 f2 = __half22float2(s);
+                    facc[b] += valid ? f2.x + f2.y : 0.f;
                 }
             }
             if (TMA) {
@@ -286,6 +298,235 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
         }
         if (TMA && !ok) {
+            // After a failed wait: give the copies still in flight a bounded chance to land before
+            // the shared memory they target is released, then stop.
+            for (int s = 0; s < kStages; ++s) {
+                mbar_wait(bars + 8u * slot, phase, p.status);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            break;
+        }
+    }
+    if (!waited_prior) pdl_wait_prior_grids();
+}
+
+// ---- the batch 1-2 fast path: two row blocks per warp ----------------------------------------------------
+// Same decomposition as gemv_kernel, but a granule is one unit of TWO adjacent row blocks (lane l owns rows
+// 64*p + l and 64*p + 32 + l).  The two 512-byte pieces arrive in one ring stage on one mbarrier, and the
+// activation quads read from shared memory serve both rows: the broadcast x loads, which cost more
+// shared-memory wavefronts than their count suggests, are halved per weight.  TILED layout only.
+template <int CODE, int K, int BATCH>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvParams p) {
+    constexpr int WPU = 128 / K;
+    constexpr int PAIRS = WPU / 2;
+    constexpr int NW2 = 2 * GroupShape<K>::kWords;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t s0 = smem_addr(smem_raw);
+    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
+    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
+    uint32_t lut_tab, xs;
+    if (CODE == RPTC_CODE_HASH) {
+        lut_tab = kHashLutWindow;
+        xs = kHashLutWindow + kHashLutBytes;
+    } else {
+        lut_tab = s0 + kBarBytes + kRingBytes;
+        xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
+    }
+    if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
+        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        return;
+    }
+    // ---- prologue: nothing here depends on the kernels before this one ----
+    lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
+    pdl_allow_next_grid();
+
+    const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
+    const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
+    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;
+    const int64_t rb_stride = (int64_t)p.n_units << 5;        // 128-bit units between row blocks of the TILED layout
+    uint32_t slot = 0, phase = 0;
+    bool ok = true, waited_prior = false;
+
+    for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
+        const int32_t nu = min(p.seg_units, p.n_units - useg0);
+        const uint32_t T = n_rbp * (uint32_t)nu;
+        const uint32_t per = T / GW, extra = T - per * GW;
+        const uint32_t g0 = gw * per + min(gw, extra);
+        const uint32_t count = per + (gw < extra ? 1u : 0u);
+        const uint32_t rbp0 = count ? g0 / (uint32_t)nu : 0u;
+        const int32_t u0 = count ? (int32_t)(g0 - rbp0 * (uint32_t)nu) : 0;
+
+        // fetch cursor (lane 0)
+        uint32_t frbp = rbp0;
+        int32_t fu = u0;
+        const uint4 *fptr = p.codes + (int64_t)(2 * rbp0) * rb_stride + ((int64_t)(useg0 + u0) << 5);
+        auto issue_stage = [&](uint32_t at_slot) {
+            const bool has_b = 2 * frbp + 1 < n_rb;
+            const uint32_t bar = bars + 8u * at_slot, dst = ring + at_slot * kStageBytes;
+            mbar_expect_tx(bar, has_b ? 2 * kUnitBytes : kUnitBytes);
+            bulk_g2s(dst, fptr, kUnitBytes, bar);
+            if (has_b) bulk_g2s(dst + kUnitBytes, fptr + rb_stride, kUnitBytes, bar);
+            fptr += 32;
+            if (++fu == nu) {
+                fu = 0;
+                ++frbp;
+                fptr = p.codes + (int64_t)(2 * frbp) * rb_stride + ((int64_t)useg0 << 5);
+            }
+        };
+        uint32_t to_issue = count;
+        {
+            const uint32_t ahead = min(count, (uint32_t)kStages);
+            if (lane == 0) {
+                uint32_t sl = slot;
+                for (uint32_t k = 0; k < ahead; ++k) {
+                    issue_stage(sl);
+                    if (++sl == kStages) sl = 0;
+                }
+            }
+            to_issue -= ahead;
+        }
+
+        // ---- activations of this column segment -> shared memory ----
+        if (!waited_prior) {
+            pdl_wait_prior_grids();
+            waited_prior = true;
+        }
+        if (useg0 > 0) __syncthreads();
+        {
+            const int64_t col0 = (int64_t)useg0 * WPU;
+            const int pairs = nu * PAIRS;
+            if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+                const int vecs = pairs >> 2;
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
+                    const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
+                    for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
+                        uint4 v[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs)
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
+                                             "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                             : "memory");
+                    }
+                }
+            } else {
+                for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
+                    const int b = i / pairs, s = i - b * pairs;
+                    int64_t src = (col0 >> 1) + s;
+                    if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- main loop over this warp's granules ----
+        uint32_t rbp = rbp0;
+        int32_t u = u0;
+        bool fresh = true;
+        uint32_t prev_a = 0, prev_b = 0;
+        float facc_a[BATCH], facc_b[BATCH];
+#pragma unroll 1
+        for (uint32_t k = 0; k < count; ++k) {
+            const int64_t row_a = ((int64_t)rbp << 6) + lane;
+            const bool has_b = 2 * rbp + 1 < n_rb;
+            if (fresh) {
+                fresh = false;
+                const int32_t ug = useg0 + u;
+                if (ug == 0) {
+                    prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
+                    prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
+                } else {
+                    const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride +
+                                                                               ((int64_t)(ug - 1) << 5) + lane) + 3;
+                    prev_a = __ldg(last);
+                    prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+                }
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
+            }
+            ok = mbar_wait(bars + 8u * slot, phase, p.status);
+            if (!ok) break;
+            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
+            const uint4 va = lds128(stage_base);
+            const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
+            uint32_t Ra[NW2], Rb[NW2];
+            {
+                const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+                make_windows<K>(wa, prev_a, Ra);
+                make_windows<K>(wb, prev_b, Rb);
+            }
+            prev_a = va.w;
+            prev_b = vb.w;
+            const uint32_t xu = xs + (uint32_t)u * (WPU * 2u);
+            __half2 ha[BATCH][4], hb[BATCH][4];
+            uint4 xv[BATCH];
+#pragma unroll
+            for (int pi = 0; pi < PAIRS; ++pi) {
+                if ((pi & 3) == 0) {
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                }
+                const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
+                const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                    const __half2 x2 = u32_as_half2(xq);
+                    ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
+                    hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+                const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
+                const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
+                facc_a[b] += fa.x + fa.y;
+                facc_b[b] += fb.x + fb.y;
+            }
+            __syncwarp();                     // every lane has taken its words: the slot can be refilled
+            if (to_issue) {
+                if (lane == 0) issue_stage(slot);
+                --to_issue;
+            }
+            if (++slot == kStages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+            const bool last_of_block = u == nu - 1;
+            if (last_of_block || k + 1 == count) {
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
+                    if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
+                }
+                fresh = true;
+            }
+            if (last_of_block) {
+                u = 0;
+                ++rbp;
+            } else {
+                ++u;
+            }
+        }
+        if (!ok) {
             // After a failed wait: give the copies still in flight a bounded chance to land before
             // the shared memory they target is released, then stop.
             for (int s = 0; s < kStages; ++s) {
@@ -329,11 +570,22 @@ static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
+template <int CODE, int K, int BATCH>
+static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t stream) {
+    static bool configured = false;
+    auto kern = gemv_pair_kernel<CODE, K, BATCH>;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
+}
+
 template <int CODE, int K, bool TMA>
 static int dispatch_batch(const GemvParams &p, int batch, size_t smem, cudaStream_t stream) {
     switch (batch) {
-        case 1: return launch_gemv<CODE, K, 1, TMA>(p, smem, stream);
-        case 2: return launch_gemv<CODE, K, 2, TMA>(p, smem, stream);
+        case 1: return TMA ? launch_gemv_pair<CODE, K, 1>(p, smem, stream) : launch_gemv<CODE, K, 1, TMA>(p, smem, stream);
+        case 2: return TMA ? launch_gemv_pair<CODE, K, 2>(p, smem, stream) : launch_gemv<CODE, K, 2, TMA>(p, smem, stream);
         case 4: return launch_gemv<CODE, K, 4, TMA>(p, smem, stream);
         case 8: return launch_gemv<CODE, K, 8, TMA>(p, smem, stream);
     }

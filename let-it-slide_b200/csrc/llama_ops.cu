@@ -85,10 +85,10 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     }
 }
 
-// Single-query attention over the cache: one CTA of 256 threads per (row, q head); d == 128.
-// Both passes are spread over the 8 warps by position (a warp reads one 256-byte K or V row per step,
+// Single-query attention over the cache: one CTA of 1024 threads per (row, q head); d == 128.
+// Both passes are spread over the 32 warps by position (a warp reads one 256-byte K or V row per step,
 // four steps in flight), partial outputs meet in shared memory.
-constexpr int kAttnThreads = 256, kAttnWarps = 8;
+constexpr int kAttnThreads = 1024, kAttnWarps = 32;
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv,
                                                                   const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
                                                                   const __half *__restrict__ vcache, __half *__restrict__ out,

@@ -11,7 +11,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG, "librptc_b200.so")
+LIB_PATH = os.environ.get("RPTC_B200_LIB") or os.path.join(_PKG, "librptc_b200.so")
 
 CODE_LUT, CODE_HASH, CODE_LITE = 0, 1, 2
 LAYOUT_ROWMAJOR, LAYOUT_CHUNKED, LAYOUT_UNITMAJOR, LAYOUT_TILED = 0, 1, 2, 3
