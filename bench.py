@@ -154,7 +154,7 @@ def gemv_roofline(model, torch, reps: int = 5) -> dict:
         for l in linears:
             l.matvec_acc(xs[l.in_features], accs[l.out_features])
 
-    lib().rptc_set_pdl(0)
+    lib().rptc_set_pdl(1)      # launched the way the decode step launches it
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s):
@@ -173,6 +173,7 @@ def gemv_roofline(model, torch, reps: int = 5) -> dict:
         b.record(s)
         b.synchronize()
     torch.cuda.current_stream().wait_stream(s)
+    lib().rptc_set_pdl(0)
     sec = a.elapsed_time(b) * 1e-3 / reps
     K = model.fmt.K
     alg = sum(l.in_features * l.out_features * K // 8 + 2 * l.in_features + 4 * l.out_features + 2 * l.lut.numel() for l in linears)
@@ -180,7 +181,7 @@ def gemv_roofline(model, torch, reps: int = 5) -> dict:
     peak, src = measured_hbm_peak()
     n = len(linears)
     achieved = alg / sec / 1e9
-    return {"bound": "hbm", "kernel": "gemv_kernel<HASH,K=2,batch=1,TMA>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    return {"bound": "hbm", "kernel": "gemv_pair_kernel<HASH,K=2,batch=1>", "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "peak_source": f"{src} copy bandwidth", "traffic": alg / n * GEMV_TRAFFIC_RATIO,
             "algorithmic_bytes_per_launch": alg / n, "launch_us": sec / n * 1e6, "launches_timed": n * reps,
             "packed_stream_gbs": packed / sec / 1e9, "frac_of_8000": packed / sec / 1e9 / 8000.0}

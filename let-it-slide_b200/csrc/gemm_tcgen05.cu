@@ -2,8 +2,11 @@
 //
 //   y[t][row] = sum_c x[t][c] * W[row][c]        x: [tokens][n] fp16,  W decoded on the fly
 //
-// One CTA owns an output tile of 256 tokens x 128 weight rows and walks the reduction dimension in
-// steps of 64 columns through a ring of shared-memory stages.  Warp roles:
+// One CTA owns an output tile of 256 tokens x NROWS weight rows (256 when m allows, else 128) and walks
+// the reduction dimension in steps of 64 columns through a ring of shared-memory stages.  With both
+// operands read from shared memory a 128 x 128 x 16 MMA needs 8 KiB of operand reads per 64 tensor-core
+// cycles -- exactly the 128 B/clk a SM's shared memory delivers -- so the wide tile (N = 256, 12 KiB per
+// 128 cycles) is what lets the tensor pipe run ahead of shared memory.  Warp roles:
 //   warps 0-7  decode producers in two groups of four that take alternate steps, so that two stages
 //              are being decoded at any time: thread r of a group owns weight row r of the tile.  Per step
 //              it takes the row's next 128 * K / 2 code bits with 128-bit loads (coalesced per 32-row
@@ -25,16 +28,12 @@
 namespace rptc {
 
 constexpr int kTileTokens = 256;       // two M = 128 halves
-constexpr int kTileRows = 128;         // N of the MMA
 constexpr int kStepCols = 64;          // one 128-byte swizzle atom of fp16
 constexpr uint32_t kXHalfBytes = 128 * kStepCols * 2;          // 16 KiB
 constexpr uint32_t kXBytes = 2 * kXHalfBytes;                  // 32 KiB
-constexpr uint32_t kWBytes = kTileRows * kStepCols * 2;        // 16 KiB
-constexpr uint32_t kGemmStageBytes = kXBytes + kWBytes;        // 48 KiB
 constexpr int kMaxGemmStages = 3;
 constexpr int kGemmThreads = 320;
 constexpr int kProducerWarps = 8, kTmaWarp = 8, kMmaWarp = 9;
-constexpr uint32_t kTmemCols = 256;
 
 struct GemmParams {
     const uint4 *codes;
@@ -47,7 +46,7 @@ struct GemmParams {
     int32_t L, S;
     int32_t n_stages;
     uint32_t bar_addr, lut_addr;      // absolute addresses in the shared window
-    uint32_t stage_addr[kMaxGemmStages];
+    uint32_t xa_addr[kMaxGemmStages], xb_addr[kMaxGemmStages], w_addr[kMaxGemmStages];   // the three pieces of a stage
     unsigned int *status;
 };
 
@@ -76,12 +75,17 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
-// fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
-constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(kTileRows >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// fp32 accumulate, fp16 A and B, both K-major, M = 128
+constexpr uint32_t instr_desc(int n_rows) { return (1u << 4) | ((uint32_t)(n_rows >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); }
 
-template <int CODE, int K>
+template <int CODE, int K, int NROWS>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
     constexpr int UPS = K / 2;                 // 128-bit units per 64-column step
+    constexpr int kTileRows = NROWS;
+    constexpr uint32_t kTmemCols = 2 * NROWS;  // two token halves of NROWS fp32 columns
+    constexpr uint32_t kInstrDesc = instr_desc(NROWS);
+    constexpr int kGroups = NROWS == 256 ? 1 : 2;        // producer groups taking alternate steps
+    constexpr uint32_t kProducersPerStage = 256 / kGroups;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s0 = smem_addr(smem_raw);
@@ -98,14 +102,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
 
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; ++s) {
-            mbar_init(bar_full_w + 8 * s, 128);
+            mbar_init(bar_full_w + 8 * s, kProducersPerStage);
             mbar_init(bar_full_x + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_accum, 1);
         mbar_fence_init();
     }
-    if (warp == kMmaWarp) {                     // TMEM: 256 columns (two 128-column fp32 accumulators)
+    if (warp == kMmaWarp) {                     // TMEM: two fp32 accumulators of NROWS columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -125,8 +129,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     if (warp < kProducerWarps) {
         // ================= decode producers =================
         const Lut<CODE> lut = lut_view<CODE>(p.lut_addr, p.L, p.S);
-        const int group = warp >> 2;                         // takes steps it = group, group + 2, ...
-        const int r = tid & 127;                             // row of the tile
+        const int group = kGroups == 2 ? warp >> 2 : 0;      // takes steps it = group, group + kGroups, ...
+        const int r = kGroups == 2 ? (tid & 127) : tid;      // row of the tile
         const int64_t row = row0 + r;
         // TILED layout: unit u of row -> ((row >> 5) * n_units + u) * 32 + (row & 31)
         const uint4 *src = p.codes + ((row >> 5) * (int64_t)p.n_units) * 32 + (row & 31);
@@ -135,27 +139,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
             return __ldg(reinterpret_cast<const uint32_t *>(src + ((int64_t)it * UPS - 1) * 32) + 3);
         };
         uint4 nxt[UPS];
-        uint32_t nxt_prev = 0;
+        uint32_t nxt_prev = 0, carry = 0;                    // carry: last word of the previous step when this thread decoded it
         if (group < n_steps) {
 #pragma unroll
             for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)group * UPS + q) * 32);
             nxt_prev = history(group);
         }
-        for (int it = group; it < n_steps && ok; it += 2) {
+        for (int it = group; it < n_steps && ok; it += kGroups) {
             const int s = it % p.n_stages;
             const uint32_t par = ((uint32_t)(it / p.n_stages) & 1u) ^ 1u;
             uint4 cur[UPS];
 #pragma unroll
             for (int q = 0; q < UPS; ++q) cur[q] = nxt[q];
-            uint32_t prevw = nxt_prev;
-            if (it + 2 < n_steps) {
+            uint32_t prevw = (kGroups == 2 || it == 0) ? nxt_prev : carry;
+            if (it + kGroups < n_steps) {
 #pragma unroll
-                for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + 2) * UPS + q) * 32);
-                nxt_prev = history(it + 2);
+                for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + kGroups) * UPS + q) * 32);
+                nxt_prev = kGroups == 2 ? history(it + kGroups) : 0u;
             }
             ok = mbar_wait(bar_empty + 8 * s, par, p.status);          // the MMA is done with this stage's old contents
             if (!ok) break;
-            const uint32_t wrow = p.stage_addr[s] + kXBytes + (uint32_t)r * 128u;
+            const uint32_t wrow = p.w_addr[s] + (uint32_t)r * 128u;
 #pragma unroll
             for (int q = 0; q < UPS; ++q) {
                 const uint32_t w[4] = {cur[q].x, cur[q].y, cur[q].z, cur[q].w};
@@ -171,6 +175,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
                 });
                 prevw = cur[q].w;
             }
+            carry = prevw;
             fence_proxy_async_smem();               // make the generic-proxy stores visible to the tensor core's reads
             mbar_arrive(bar_full_w + 8 * s);
         }
@@ -184,8 +189,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
                 ok = mbar_wait(bar_empty + 8 * s, par, p.status);
                 if (!ok) break;
                 mbar_expect_tx(bar_full_x + 8 * s, kXBytes);
-                tma_load_2d(p.stage_addr[s], &x_map, it * kStepCols, tok0, bar_full_x + 8 * s);
-                tma_load_2d(p.stage_addr[s] + kXHalfBytes, &x_map, it * kStepCols, tok0 + 128, bar_full_x + 8 * s);
+                tma_load_2d(p.xa_addr[s], &x_map, it * kStepCols, tok0, bar_full_x + 8 * s);
+                tma_load_2d(p.xb_addr[s], &x_map, it * kStepCols, tok0 + 128, bar_full_x + 8 * s);
             }
         }
     } else {
@@ -197,12 +202,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
                 ok = mbar_wait(bar_full_x + 8 * s, par, p.status) && mbar_wait(bar_full_w + 8 * s, par, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t xa = p.stage_addr[s], wa = xa + kXBytes;
+                const uint32_t xa = p.xa_addr[s], xb = p.xb_addr[s], wa = p.w_addr[s];
 #pragma unroll
                 for (int k = 0; k < kStepCols / 16; ++k) {
                     const uint64_t bdesc = umma_desc_sw128(wa + 32u * k);
                     tc_mma_f16(tmem_base, umma_desc_sw128(xa + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
-                    tc_mma_f16(tmem_base + 128u, umma_desc_sw128(xa + kXHalfBytes + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
+                    tc_mma_f16(tmem_base + (uint32_t)NROWS, umma_desc_sw128(xb + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
                 }
                 tc_commit(bar_empty + 8 * s);       // arrives when the MMAs above have read this stage
             }
@@ -220,7 +225,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
 #pragma unroll 1
             for (int c = 0; c < kTileRows / 32; ++c) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 128 + c * 32);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * NROWS + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -266,15 +271,20 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_tiled_fn() {
     return fn;
 }
 
-template <int CODE, int K>
+template <int CODE, int K, int NROWS>
 static int launch_gemm(const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemm_kernel<CODE, K>;
+    auto kern = gemm_kernel<CODE, K, NROWS>;
     if (!configured) {
         RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
     return launch(kern, grid, dim3(kGemmThreads), smem, stream, p, map);
+}
+
+template <int CODE, int K>
+static int launch_gemm_rows(int n_rows, const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
+    return n_rows == 256 ? launch_gemm<CODE, K, 256>(p, map, smem, grid, stream) : launch_gemm<CODE, K, 128>(p, map, smem, grid, stream);
 }
 
 int check_format(const rptc_format *f);   // api.cu
@@ -289,7 +299,7 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
     if (int e = check_format(fmt)) return e;
     if (fmt->layout != RPTC_LAYOUT_TILED || fmt->quirk != RPTC_QUIRK_NONE) return RPTC_ERR_UNSUPPORTED;
     if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
-    if (m <= 0 || n <= 0 || tokens <= 0 || (m % kTileRows) || (n % kStepCols) || ld_x < n || ld_y < m) return RPTC_ERR_SHAPE;
+    if (m <= 0 || n <= 0 || tokens <= 0 || (m % 128) || (n % kStepCols) || ld_x < n || ld_y < m) return RPTC_ERR_SHAPE;
     if (m > (int64_t(1) << 30) || n > (int64_t(1) << 30) || tokens > (int64_t(1) << 24)) return RPTC_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(lut) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
         (reinterpret_cast<uintptr_t>(y) & 15) || (ld_x % 8) || (ld_y % 8))
@@ -325,37 +335,80 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
     p.S = fmt->S;
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
-    // shared-window plan (absolute addresses; the dynamic area is expected to start at or below 0x400)
+    // shared-window plan (absolute addresses; the dynamic area is expected to start at or below 0x400): the
+    // pieces of each stage (two activation halves, one weight tile) go first-fit into the space around the table
     const uint32_t kTop = 0x38800;       // 226 KiB: the last byte any plan may touch (dynamic limit is 227 KiB)
     p.bar_addr = 0x400;
-    uint32_t next = 0x800;
-    int stages = 0;
+    uint32_t free_lo[2], free_hi[2];
+    int n_free;
     if (fmt->code == RPTC_CODE_HASH) {
         p.lut_addr = kHashLutWindow;
-        p.stage_addr[stages++] = next;                               // 0x800 .. 0xC800, below the table
-        next = kHashLutWindow + kHashLutBytes;
+        free_lo[0] = 0x800, free_hi[0] = kHashLutWindow;
+        free_lo[1] = kHashLutWindow + kHashLutBytes, free_hi[1] = kTop;
+        n_free = 2;
     } else {
-        p.lut_addr = next;
+        p.lut_addr = 0x800;
         const uint32_t lb = fmt->code == RPTC_CODE_LUT ? (2u << fmt->L) : (128u << fmt->S);
-        next = (next + lb + 1023u) & ~1023u;
+        free_lo[0] = (0x800 + lb + 1023u) & ~1023u, free_hi[0] = kTop;
+        n_free = 1;
     }
-    while (stages < kMaxGemmStages && next + kGemmStageBytes <= kTop) {
-        p.stage_addr[stages++] = next;
-        next += kGemmStageBytes;
+    auto take = [&](uint32_t bytes) -> uint32_t {
+        for (int i = 0; i < n_free; ++i)
+            if (free_lo[i] + bytes <= free_hi[i]) {
+                const uint32_t a = free_lo[i];
+                free_lo[i] += bytes;
+                return a;
+            }
+        return 0;
+    };
+    // Tile height: 256 rows feed the tensor pipe about 1.35x faster per CTA-step than 128 rows, but need twice
+    // the time per CTA; with few tiles the shorter ones fill more SMs.  Compare whole waves of CTAs.
+    int n_rows = 128;
+    if (m % 256 == 0) {
+        const int64_t tt = (tokens + kTileTokens - 1) / kTileTokens, sms = num_sms();
+        const int64_t waves256 = ((m / 256) * tt + sms - 1) / sms, waves128 = ((m / 128) * tt + sms - 1) / sms;
+        if (waves256 * 148 <= waves128 * 100) n_rows = 256;          // 2 / 1.35 = 1.48
+    }
+    int stages = 0;
+    for (int attempt = 0; attempt < 2 && stages < 2; ++attempt) {
+        if (attempt == 1) {              // the wide tile does not fit beside this table: fall back to 128 rows
+            if (n_rows == 128) break;
+            n_rows = 128;
+            if (fmt->code == RPTC_CODE_HASH) {
+                free_lo[0] = 0x800, free_lo[1] = kHashLutWindow + kHashLutBytes;
+            } else {
+                const uint32_t lb = fmt->code == RPTC_CODE_LUT ? (2u << fmt->L) : (128u << fmt->S);
+                free_lo[0] = (0x800 + lb + 1023u) & ~1023u;
+            }
+        }
+        stages = 0;
+        const int want = n_rows == 256 ? 2 : kMaxGemmStages;
+        while (stages < want) {
+            const uint32_t save0 = free_lo[0], save1 = free_lo[1];
+            const uint32_t w = take((uint32_t)n_rows * 128u), xa = take(kXHalfBytes), xb = take(kXHalfBytes);
+            if (!w || !xa || !xb) {
+                free_lo[0] = save0, free_lo[1] = save1;
+                break;
+            }
+            p.w_addr[stages] = w, p.xa_addr[stages] = xa, p.xb_addr[stages] = xb;
+            ++stages;
+        }
     }
     if (stages < 2) return RPTC_ERR_UNSUPPORTED;
-    for (int s = stages; s < kMaxGemmStages; ++s) p.stage_addr[s] = 0;
+    for (int s = stages; s < kMaxGemmStages; ++s) p.w_addr[s] = p.xa_addr[s] = p.xb_addr[s] = 0;
     p.n_stages = stages;
     const size_t smem = kTop;            // covers every planned address whatever the start of the dynamic area
-    const dim3 grid((unsigned)(m / kTileRows), (unsigned)((tokens + kTileTokens - 1) / kTileTokens));
+    const dim3 grid((unsigned)(m / n_rows), (unsigned)((tokens + kTileTokens - 1) / kTileTokens));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (fmt->code) {
         case RPTC_CODE_LUT:
-            return fmt->K == 2 ? launch_gemm<RPTC_CODE_LUT, 2>(p, map, smem, grid, s) : launch_gemm<RPTC_CODE_LUT, 4>(p, map, smem, grid, s);
+            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LUT, 2>(n_rows, p, map, smem, grid, s)
+                               : launch_gemm_rows<RPTC_CODE_LUT, 4>(n_rows, p, map, smem, grid, s);
         case RPTC_CODE_HASH:
-            return launch_gemm<RPTC_CODE_HASH, 2>(p, map, smem, grid, s);
+            return launch_gemm_rows<RPTC_CODE_HASH, 2>(n_rows, p, map, smem, grid, s);
         case RPTC_CODE_LITE:
-            return fmt->K == 2 ? launch_gemm<RPTC_CODE_LITE, 2>(p, map, smem, grid, s) : launch_gemm<RPTC_CODE_LITE, 4>(p, map, smem, grid, s);
+            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LITE, 2>(n_rows, p, map, smem, grid, s)
+                               : launch_gemm_rows<RPTC_CODE_LITE, 4>(n_rows, p, map, smem, grid, s);
     }
     return RPTC_ERR_UNSUPPORTED;
 }

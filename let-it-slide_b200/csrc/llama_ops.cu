@@ -87,8 +87,8 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
 
 // Single-query attention over the cache: one CTA of 1024 threads per (row, q head); d == 128.
 // Both passes are spread over the 32 warps by position (a warp reads one 256-byte K or V row per step,
-// four steps in flight), partial outputs meet in shared memory.
-constexpr int kAttnThreads = 1024, kAttnWarps = 32;
+// eight steps in flight), partial outputs meet in shared memory.
+constexpr int kAttnThreads = 1024, kAttnWarps = 32, kAttnUnroll = 8;     // 256 positions in flight per pass
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv,
                                                                   const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
                                                                   const __half *__restrict__ vcache, __half *__restrict__ out,
@@ -111,15 +111,15 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
     // ---- scores ----
     float mx = -1e30f;
-    for (int j0 = warp; j0 < ctx; j0 += 4 * kAttnWarps) {
-        uint2 kk[4];
+    for (int j0 = warp; j0 < ctx; j0 += kAttnUnroll * kAttnWarps) {
+        uint2 kk[kAttnUnroll];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kAttnUnroll; ++u) {
             const int j = j0 + u * kAttnWarps;
             kk[u] = j < ctx ? *reinterpret_cast<const uint2 *>(kb + j * stride) : make_uint2(0u, 0u);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kAttnUnroll; ++u) {
             const int j = j0 + u * kAttnWarps;
             const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
             float s = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
@@ -151,17 +151,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     const float inv = 1.f / tot;
     // ---- weighted sum of V: lane owns dims 4*lane .. 4*lane+3 of its warp's positions ----
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    for (int j0 = warp; j0 < ctx; j0 += 4 * kAttnWarps) {
-        uint2 vv[4];
-        float pw[4];
+    for (int j0 = warp; j0 < ctx; j0 += kAttnUnroll * kAttnWarps) {
+        uint2 vv[kAttnUnroll];
+        float pw[kAttnUnroll];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kAttnUnroll; ++u) {
             const int j = j0 + u * kAttnWarps;
             vv[u] = j < ctx ? *reinterpret_cast<const uint2 *>(vb + j * stride) : make_uint2(0u, 0u);
             pw[u] = j < ctx ? sc[j] : 0.f;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kAttnUnroll; ++u) {
             const float2 v01 = __half22float2(u32_as_half2(vv[u].x)), v23 = __half22float2(u32_as_half2(vv[u].y));
             a0 += pw[u] * v01.x, a1 += pw[u] * v01.y, a2 += pw[u] * v23.x, a3 += pw[u] * v23.y;
         }
