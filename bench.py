@@ -202,7 +202,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     tp = args.workload.endswith("-tp")
     cfg = LlamaConfig(max_pos=args.prompt + max(3, args.warmup) + 2 * args.steps + 8, **cfg_kw)
     if tp:
-        model = RPTCLlama(cfg, rows=1, seed=0, tp_world=world, tp_rank=rank)
+        model = RPTCLlama(cfg, rows=1, seed=0, tp_world=world, tp_rank=rank, peer_allreduce=args.allreduce == "peer")
     else:
         model = RPTCLlama(cfg, rows=1, seed=rank)
     g = torch.Generator(device="cuda").manual_seed(42 + (0 if tp else rank))
@@ -266,7 +266,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                "config": {"workload": args.workload, "code": "HASH S=8 K=2 L=16", "layout": "TILED", "incoherence": "RHT both sides",
-                          "prompt": args.prompt, "batch_per_gpu": 1, "parallelism": (f"tp{world}" if tp else ("replicas" if world > 1 else "single")),
+                          "prompt": args.prompt, "batch_per_gpu": 1, "allreduce": (args.allreduce if tp else None), "parallelism": (f"tp{world}" if tp else ("replicas" if world > 1 else "single")),
                           "l2": "weights 1.6 GB per token exceed L2", "bytes_per_token": bt},
                "e2e": {"value": seqs * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 8},
                "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks, "roofline": roof,
@@ -276,6 +276,8 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     if world > 1:
         model.graph = None          # graphs that captured collectives must be gone before their communicator is torn down
         torch.cuda.synchronize()
+        if getattr(model, "peer", None) is not None:
+            model.peer.close()
         dist.barrier()
         dist.destroy_process_group()
 
@@ -295,6 +297,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama2-7b-decode-bs1")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="tensor-parallel workloads: fused peer-memory all-reduce kernel, or NCCL")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens pushed through the decode step before timing")
     args = ap.parse_args()
     cfg_kw, cfg_dims = WORKLOADS[args.workload]

@@ -191,6 +191,25 @@ int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, vo
 /* out[r] = table[ids[r]], fp16 rows of length n. */
 int rptc_embed(const void *table, const int32_t *ids, void *out, int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream);
 
+/* --- tensor-parallel decode: output transform + all-reduce + residual add in one kernel over NVLink peer
+ * memory (no reference counterpart; the reference has no distributed code) ---
+ * rptc_peer_alloc / export / import / close / free: an exchange buffer of this process (cudaMalloc, zeroed),
+ * its 64-byte CUDA IPC handle, and the mapping of a peer's handle; the caller passes handles between ranks. */
+int rptc_peer_alloc(int64_t bytes, void **ptr);
+int rptc_peer_free(void *ptr);
+int rptc_peer_export(void *ptr, unsigned char *handle64);
+int rptc_peer_import(const unsigned char *handle64, void **ptr);
+int rptc_peer_close(void *ptr);
+/* h[rows][n] += sum over ranks of fp16( s_out * H(acc_rank) * scale );  acc is cleared.
+ * data_ptrs[r]: rank r's exchange buffer, fp16 [2][world][rows*n];  flag_ptrs[r]: rank r's flags, uint32
+ * [world][ctas] with ctas = rows * n / max(block,256);  epochs: local uint32 [ctas]; all zero-initialised.
+ * Every rank must call it the same number of times with the same shapes.  A rank that waits longer than
+ * timeout_ms (0 = 2000) for a peer gives up: the device status word is raised (rptc_device_status) and h is
+ * left untouched for the rows it could not finish. */
+int rptc_peer_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *h, int64_t ld_h,
+                     void *const *data_ptrs, void *const *flag_ptrs, void *epochs, int rank, int world, int64_t rows,
+                     int64_t n, int block, int64_t timeout_ms, rptc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

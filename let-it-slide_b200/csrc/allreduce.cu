@@ -1,0 +1,263 @@
+// Output side of a row-parallel (tensor-parallel) quantised layer fused with its all-reduce and the
+// residual add, as ONE kernel over NVLink peer memory:
+//     h += sum over ranks r of ( s_out * H(acc_r) * scale )
+// Every rank transforms its fp32 partial accumulator, stores the fp16 result straight into a slot of
+// EVERY rank's exchange buffer with plain peer stores (no multimem, no NCCL), raises a per-CTA epoch
+// flag on each peer, waits -- with a time limit -- until all ranks' flags show the same epoch, and adds
+// the partials from its own buffer in rank order (so all ranks compute bit-identical sums) onto the
+// residual stream.  Decode messages are tiny (16 KiB at hidden 8192), so the cost is one NVLink round
+// trip instead of a collective launch.  Buffers are double-buffered by epoch parity; epochs are kept in
+// device memory per CTA, which makes the kernel replayable from a CUDA graph.
+// A wait that runs out raises the device status word and the kernel returns; nothing hangs.
+#include "common.cuh"
+
+namespace rptc {
+
+constexpr int kMaxPeers = 8;
+
+struct PeerFinishParams {
+    float *acc;                   // fp32 [rows][ld_acc] local partial (cleared)
+    int64_t ld_acc;
+    const __half *signs_out;
+    float scale;
+    __half *h;                    // fp16 [rows][ld_h] residual stream, updated in place
+    int64_t ld_h;
+    __half *data[kMaxPeers];      // every rank's exchange buffer: [2 parities][world][rows * n] fp16
+    uint32_t *flags[kMaxPeers];   // every rank's flag array: [world][n_ctas]
+    uint32_t *epochs;             // local: [n_ctas]
+    int32_t rank, world, n, block, chunk, rows;
+    unsigned long long timeout_ns;
+    unsigned int *status;
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_128(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Shared FWHT helpers live in hadamard.cu; this file needs only the 8-values-per-thread transform.
+__device__ __forceinline__ void fwht8_ar(float (&v)[8], int block, float *ex) {
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = a + b;
+                v[i + h] = a - b;
+            }
+    for (int lm = 1; lm < 32 && 8 * lm < block; lm <<= 1) {
+        const bool upper = (t & lm) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], lm);
+            v[i] = upper ? o - v[i] : v[i] + o;
+        }
+    }
+    if (block > 256) {
+        const int G = block >> 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
+        __syncthreads();
+        const int n_items = (int)blockDim.x * 8 / G;
+        for (int item = t; item < n_items; item += blockDim.x) {
+            float *base = ex + (item >> 8) * block + (item & 255);
+            float z[16];
+#pragma unroll
+            for (int g = 0; g < 16; ++g) z[g] = g < G ? base[256 * g] : 0.f;
+#pragma unroll
+            for (int h = 1; h < 16; h <<= 1)
+                if (h < G) {
+#pragma unroll
+                    for (int g = 0; g < 16; ++g)
+                        if ((g & h) == 0) {
+                            const float a = z[g], b = z[g + h];
+                            z[g] = a + b;
+                            z[g + h] = a - b;
+                        }
+                }
+#pragma unroll
+            for (int g = 0; g < 16; ++g)
+                if (g < G) base[256 * g] = z[g];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
+    }
+}
+
+__global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams p) {
+    __shared__ float ex[4096];
+    __shared__ int timed_out;
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.y;
+    const int col = blockIdx.x * p.chunk + 8 * t;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y;
+    if (t == 0) timed_out = 0;
+    // ---- this rank's partial: s_out * H(acc) * scale, rounded to fp16 ----
+    float v[8];
+    {
+        float *src = p.acc + row * p.ld_acc + col;
+        const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        *reinterpret_cast<float4 *>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4 *>(src + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
+    if (p.signs_out) sraw = *reinterpret_cast<const uint4 *>(p.signs_out + col);
+    const uint4 hraw = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
+    fwht8_ar(v, p.block, ex);
+    const float sc = p.scale * rsqrtf((float)p.block);
+    uint4 mine;
+    {
+        const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 s2 = __half22float2(u32_as_half2(sw[i]));
+            o[i] = half2_as_u32(__floats2half2_rn(v[2 * i] * sc * s2.x, v[2 * i + 1] * sc * s2.y));
+        }
+        mine = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    // ---- publish to every rank (peer stores), then raise this CTA's flag on every rank ----
+    const uint32_t epoch = p.epochs[cta] + 1u;
+    const int64_t slot_elems = (int64_t)p.rows * p.n;
+    const int64_t off = ((int64_t)(epoch & 1u) * p.world + p.rank) * slot_elems + row * p.n + col;
+    for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4 *>(p.data[r] + off) = mine;
+    __threadfence_system();
+    __syncthreads();
+    if (t < p.world) {
+        st_release_sys(p.flags[t] + (int64_t)p.rank * n_ctas + cta, epoch);
+        // ---- wait (bounded) for rank t's flag in this rank's own array ----
+        const uint32_t *f = p.flags[p.rank] + (int64_t)t * n_ctas + cta;
+        const unsigned long long t0 = global_ns();
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+            if (global_ns() - t0 > p.timeout_ns) {
+                timed_out = 1;
+                atomicExch(p.status, 1u);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (t == 0) p.epochs[cta] = epoch;
+    if (timed_out) return;
+    // ---- sum the partials in rank order, add the residual ----
+    float acc[8];
+    {
+        const uint32_t hw[4] = {hraw.x, hraw.y, hraw.z, hraw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f2 = __half22float2(u32_as_half2(hw[i]));
+            acc[2 * i] = f2.x, acc[2 * i + 1] = f2.y;
+        }
+    }
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const __half *mybuf = p.data[p.rank] + ((int64_t)(epoch & 1u) * p.world) * slot_elems + row * p.n + col;
+    for (int r = 0; r < p.world; ++r) {
+        const uint4 q = ld_volatile_128(mybuf + (int64_t)r * slot_elems);
+        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f2 = __half22float2(u32_as_half2(qw[i]));
+            sum[2 * i] += f2.x, sum[2 * i + 1] += f2.y;
+        }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // the reduced layer output is an fp16 tensor; add it to the residual as the unfused path does
+        const float2 red = __half22float2(__floats2half2_rn(sum[2 * i], sum[2 * i + 1]));
+        o[i] = half2_as_u32(__floats2half2_rn(acc[2 * i] + red.x, acc[2 * i + 1] + red.y));
+    }
+    *reinterpret_cast<uint4 *>(p.h + row * p.ld_h + col) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace rptc
+
+using namespace rptc;
+
+// ---- peer memory plumbing (CUDA IPC; the handles travel through the caller's process group) ----
+extern "C" int rptc_peer_alloc(int64_t bytes, void **ptr) {
+    if (!ptr || bytes <= 0) return RPTC_ERR_ARG;
+    RPTC_CUDA(cudaMalloc(ptr, (size_t)bytes));
+    RPTC_CUDA(cudaMemset(*ptr, 0, (size_t)bytes));
+    return RPTC_OK;
+}
+extern "C" int rptc_peer_free(void *ptr) {
+    RPTC_CUDA(cudaFree(ptr));
+    return RPTC_OK;
+}
+extern "C" int rptc_peer_export(void *ptr, unsigned char *handle64) {
+    if (!ptr || !handle64) return RPTC_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    RPTC_CUDA(cudaIpcGetMemHandle(&h, ptr));
+    memcpy(handle64, &h, 64);
+    return RPTC_OK;
+}
+extern "C" int rptc_peer_import(const unsigned char *handle64, void **ptr) {
+    if (!ptr || !handle64) return RPTC_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    RPTC_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return RPTC_OK;
+}
+extern "C" int rptc_peer_close(void *ptr) {
+    RPTC_CUDA(cudaIpcCloseMemHandle(ptr));
+    return RPTC_OK;
+}
+
+extern "C" int rptc_peer_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *h, int64_t ld_h,
+                                void *const *data_ptrs, void *const *flag_ptrs, void *epochs, int rank, int world, int64_t rows,
+                                int64_t n, int block, int64_t timeout_ms, rptc_stream_t stream) {
+    if (!acc || !h || !data_ptrs || !flag_ptrs || !epochs) return RPTC_ERR_ARG;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return RPTC_ERR_ARG;
+    if (block < 8 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
+    const int chunk = block < 256 ? 256 : block;
+    if (rows <= 0 || rows > 65535 || n <= 0 || (n % chunk) || ld_acc < n || ld_h < n) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(h) & 15) || (ld_acc % 4) || (ld_h % 8) ||
+        (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    PeerFinishParams p;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.signs_out = static_cast<const __half *>(signs_out);
+    p.scale = scale;
+    p.h = static_cast<__half *>(h);
+    p.ld_h = ld_h;
+    for (int r = 0; r < kMaxPeers; ++r) {
+        p.data[r] = r < world ? static_cast<__half *>(data_ptrs[r]) : nullptr;
+        p.flags[r] = r < world ? static_cast<uint32_t *>(flag_ptrs[r]) : nullptr;
+        if (r < world && (!p.data[r] || !p.flags[r])) return RPTC_ERR_ARG;
+    }
+    p.epochs = static_cast<uint32_t *>(epochs);
+    p.rank = rank;
+    p.world = world;
+    p.n = (int32_t)n;
+    p.block = block;
+    p.chunk = chunk;
+    p.rows = (int32_t)rows;
+    p.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+    p.status = device_status_word();
+    if (!p.status) return RPTC_ERR_CUDA;
+    return launch(peer_finish_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0, static_cast<cudaStream_t>(stream), p);
+}

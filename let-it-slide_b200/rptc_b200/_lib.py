@@ -101,6 +101,15 @@ _SIGS = {
                                        ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p]),
     "rptc_dense_gemv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]),
+    "rptc_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]),
+    "rptc_peer_free": (ctypes.c_int, [ctypes.c_void_p]),
+    "rptc_peer_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "rptc_peer_import": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "rptc_peer_close": (ctypes.c_int, [ctypes.c_void_p]),
+    "rptc_peer_finish": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p,
+                                        ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                        ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
+                                        ctypes.c_void_p]),
     "rptc_embed": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                   ctypes.c_int64, ctypes.c_void_p]),
 }

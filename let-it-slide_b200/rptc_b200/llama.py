@@ -76,7 +76,7 @@ class RPTCLlama:
     """Random-init Llama-shape model with all block linears RPTC-quantised; batch-`rows` decode."""
 
     def __init__(self, cfg: LlamaConfig, fmt: Format | None = None, rows: int = 1, seed: int = 0, device="cuda",
-                 incoherent: bool = True, tp_world: int = 1, tp_rank: int = 0, tp_group=None):
+                 incoherent: bool = True, tp_world: int = 1, tp_rank: int = 0, tp_group=None, peer_allreduce: bool = False):
         """tp_world > 1: this object is rank `tp_rank`'s shard of a tensor-parallel model; the partial
         outputs of the row-parallel layers (o, down) are summed over `tp_group` with an NCCL all-reduce.
         Embedding, norms and output head are replicated (same seed on every rank)."""
@@ -112,6 +112,11 @@ class RPTCLlama:
         self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
         self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
         self.acc_gu = torch.zeros((rows, 2 * self.ffn_l), **f32)
+        self.peer = None
+        if tp_world > 1 and peer_allreduce and incoherent:
+            # the fused transform + all-reduce + residual kernel over NVLink peer memory instead of NCCL
+            from .tp import PeerAllReduce
+            self.peer = PeerAllReduce(rows, cfg.hidden, self.blocks[0].o.block_out, tp_rank, tp_world, tp_group)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
 
@@ -203,6 +208,9 @@ class RPTCLlama:
         """h += (sum over tensor-parallel ranks of) this rank's partial output of a row-parallel layer."""
         if self.tp_world == 1:
             lin.finish(self.acc_h, out=self.h, residual=self.h)
+            return
+        if self.peer is not None:
+            self.peer.finish(lin, self.acc_h, self.h)
             return
         import torch.distributed as dist
         lin.finish(self.acc_h, out=self.partial)

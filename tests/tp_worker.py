@@ -20,7 +20,8 @@ def main():
     from rptc_b200.llama import LlamaConfig, RPTCLlama
     cfg = LlamaConfig(hidden=1024, layers=2, heads=8, kv_heads=2, ffn=2048, vocab=512, max_pos=16, weight_scale=0.05)
     rows, T = 2, 6
-    model = RPTCLlama(cfg, rows=rows, seed=3, tp_world=world, tp_rank=rank)
+    use_peer = len(sys.argv) > 4 and sys.argv[4] == "peer"
+    model = RPTCLlama(cfg, rows=rows, seed=3, tp_world=world, tp_rank=rank, peer_allreduce=use_peer)
     g = torch.Generator(device="cuda").manual_seed(5)                    # same tokens on every rank
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
@@ -45,6 +46,8 @@ def main():
     # graphs that captured collectives must be gone before their communicator is torn down
     model.graph = None
     torch.cuda.synchronize()
+    if model.peer is not None:
+        model.peer.close()
     print(f"rank {rank}: worst {worst:.2e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
