@@ -173,7 +173,7 @@ __device__ __forceinline__ uint32_t lut_bytes(int L, int S) {
 // one L2 round trip rather than one per row.
 template <int CODE>
 __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restrict__ g, int L, int S) {
-    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
+    const int tid = threadIdx.x, nt = blockDim.x;
     if (CODE == RPTC_CODE_LUT) {
         const uint4 *src = reinterpret_cast<const uint4 *>(g);
         const int total = (1 << L) / 8;
@@ -190,22 +190,28 @@ __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restric
                                  : "memory");
         }
     } else {
+        // A table row is 32 copies of one 4-byte pair (one per bank): eight 128-bit stores.  Thread i takes
+        // part i & 7 of row i >> 3, four rows in flight per thread.
         const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
         const int rows = (CODE == RPTC_CODE_HASH) ? 256 : (1 << S);
         const uint32_t row_bytes = (CODE == RPTC_CODE_HASH) ? 256u : 128u;
         const int smask = (1 << S) - 1;
-        int per = (rows + nw - 1) / nw;           // rows per warp per pass, at most 32
-        if (per > 32) per = 32;
-        for (int base = warp * per; base < rows; base += nw * per) {
-            uint32_t mine = 0;
-            if (lane < per && base + lane < rows) mine = __ldg(src + ((base + lane) & smask));
-#pragma unroll 8
-            for (int k = 0; k < per; ++k) {
-                uint32_t v = __shfl_sync(0xFFFFFFFFu, mine, k);
-                const int e = base + k;
-                if (e < rows) {
-                    if (CODE == RPTC_CODE_HASH) v = (v & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(table + row_bytes * e + 4u * lane), "r"(v) : "memory");
+        const int total = rows * 8;
+        for (int i0 = tid; i0 < total; i0 += 4 * nt) {
+            uint32_t v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * nt;
+                if (i < total) v[k] = __ldg(src + ((i >> 3) & smask));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * nt;
+                if (i < total) {
+                    const int e = i >> 3;
+                    uint32_t x = v[k];
+                    if (CODE == RPTC_CODE_HASH) x = (x & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(table + row_bytes * e + 16u * (i & 7)), "r"(x) : "memory");
                 }
             }
         }

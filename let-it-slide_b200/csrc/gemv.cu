@@ -437,18 +437,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         }
         __syncthreads();
 
-        // ---- main loop over this warp's granules ----
+        // ---- main loop: runs of consecutive units inside one pair of row blocks ----
         uint32_t rbp = rbp0;
         int32_t u = u0;
-        bool fresh = true;
-        uint32_t prev_a = 0, prev_b = 0;
-        float facc_a[BATCH], facc_b[BATCH];
-#pragma unroll 1
-        for (uint32_t k = 0; k < count; ++k) {
+        uint32_t k = 0;
+        while (k < count && ok) {
+            const uint32_t run = min(count - k, (uint32_t)(nu - u));
             const int64_t row_a = ((int64_t)rbp << 6) + lane;
             const bool has_b = 2 * rbp + 1 < n_rb;
-            if (fresh) {
-                fresh = false;
+            uint32_t prev_a, prev_b;
+            {
                 const int32_t ug = useg0 + u;
                 if (ug == 0) {
                     prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
@@ -459,71 +457,72 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                     prev_a = __ldg(last);
                     prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
                 }
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
             }
-            ok = mbar_wait(bars + 8u * slot, phase, p.status);
-            if (!ok) break;
-            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
-            const uint4 va = lds128(stage_base);
-            const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
-            uint32_t Ra[NW2], Rb[NW2];
-            {
-                const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
-                make_windows<K>(wa, prev_a, Ra);
-                make_windows<K>(wb, prev_b, Rb);
-            }
-            prev_a = va.w;
-            prev_b = vb.w;
-            const uint32_t xu = xs + (uint32_t)u * (WPU * 2u);
-            __half2 ha[BATCH][4], hb[BATCH][4];
-            uint4 xv[BATCH];
+            float facc_a[BATCH], facc_b[BATCH];
 #pragma unroll
-            for (int pi = 0; pi < PAIRS; ++pi) {
-                if ((pi & 3) == 0) {
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+            for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
+            uint32_t xu = xs + (uint32_t)u * (WPU * 2u);
+#pragma unroll 1
+            for (uint32_t j = 0; j < run; ++j) {
+                ok = mbar_wait(bars + 8u * slot, phase, p.status);
+                if (!ok) break;
+                const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
+                const uint4 va = lds128(stage_base);
+                const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
+                uint32_t Ra[NW2], Rb[NW2];
+                {
+                    const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+                    make_windows<K>(wa, prev_a, Ra);
+                    make_windows<K>(wb, prev_b, Rb);
                 }
-                const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
-                const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
+                prev_a = va.w;
+                prev_b = vb.w;
+                __half2 ha[BATCH][4], hb[BATCH][4];
+                uint4 xv[BATCH];
+#pragma unroll
+                for (int pi = 0; pi < PAIRS; ++pi) {
+                    if ((pi & 3) == 0) {
+#pragma unroll
+                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                    }
+                    const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
+                    const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) {
+                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                        const __half2 x2 = u32_as_half2(xq);
+                        ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
+                        hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
+                    }
+                }
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
-                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                    const __half2 x2 = u32_as_half2(xq);
-                    ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
-                    hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
+                    const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
+                    const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
+                    facc_a[b] += fa.x + fa.y;
+                    facc_b[b] += fb.x + fb.y;
+                }
+                xu += WPU * 2u;
+                __syncwarp();                     // every lane has taken its words: the slot can be refilled
+                if (to_issue) {
+                    if (lane == 0) issue_stage(slot);
+                    --to_issue;
+                }
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
                 }
             }
 #pragma unroll
             for (int b = 0; b < BATCH; ++b) {
-                const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
-                const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
-                facc_a[b] += fa.x + fa.y;
-                facc_b[b] += fb.x + fb.y;
+                atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
+                if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
             }
-            __syncwarp();                     // every lane has taken its words: the slot can be refilled
-            if (to_issue) {
-                if (lane == 0) issue_stage(slot);
-                --to_issue;
-            }
-            if (++slot == kStages) {
-                slot = 0;
-                phase ^= 1u;
-            }
-            const bool last_of_block = u == nu - 1;
-            if (last_of_block || k + 1 == count) {
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
-                    if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
-                }
-                fresh = true;
-            }
-            if (last_of_block) {
+            k += run;
+            u += (int32_t)run;
+            if (u == nu) {
                 u = 0;
                 ++rbp;
-            } else {
-                ++u;
             }
         }
         if (!ok) {

@@ -61,6 +61,30 @@ def _timed(fn) -> float:
     return start.elapsed_time(stop)
 
 
+def matvec(decompressed: torch.Tensor, x: torch.Tensor, out: torch.Tensor) -> float:
+    """Dense fp16 matvec out = decompressed @ x.  The reference's tests call it as a bandwidth probe
+    (rptc_kernels/tests/test_matvec.py:18) although wrapper.cpp does not export it."""
+    _check(decompressed, "decompressed", torch.float16, 2)
+    _check(x, "x", torch.float16, 1)
+    _check(out, "out", torch.float16, 1)
+    if decompressed.shape[1] != x.shape[0] or decompressed.shape[0] != out.shape[0]:
+        raise RuntimeError("shapes of decompressed [m, n], x [n] and out [m] do not agree")
+    return _timed(lambda: ops.dense_gemv(decompressed, x, out=out))
+
+
+_ones: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def rowsum(decompressed: torch.Tensor, out: torch.Tensor) -> float:
+    """out[i] = sum_j decompressed[i, j] (rptc_kernels/tests/test_rowsum.py:17; same remark as `matvec`)."""
+    _check(decompressed, "decompressed", torch.float16, 2)
+    _check(out, "out", torch.float16, 1)
+    key = (decompressed.device.index or 0, decompressed.shape[1])
+    if key not in _ones:
+        _ones[key] = torch.ones(decompressed.shape[1], dtype=torch.float16, device=decompressed.device)
+    return _timed(lambda: ops.dense_gemv(decompressed, _ones[key], out=out))
+
+
 def decompress(compressed: torch.Tensor, codebook: torch.Tensor, out: torch.Tensor) -> float:
     """inference.cu:99-160.  compressed int32 [m, n/16] -> out fp16 [m, n] through codebook fp16 [65536]."""
     _check(compressed, "compressed", torch.int32, 2)

@@ -172,3 +172,20 @@ def test_legacy_argument_errors():
     with pytest.raises(RuntimeError):
         rptc_kernels.decompress_matvec_16_8_1(torch.zeros((1, 32, 64), dtype=torch.int32, device="cuda"),
                                               cb[:512], out[0], out[:, 0].contiguous())
+
+
+def test_dense_probes_matvec_and_rowsum():
+    # the calls of rptc_kernels/tests/test_matvec.py:18-31 and test_rowsum.py:17-30, with their rtol
+    import rptc_kernels
+    torch.manual_seed(42)
+    m = n = 4096
+    w = torch.randn((m, n), dtype=torch.float16, device="cuda")
+    x = torch.randn((n,), dtype=torch.float16, device="cuda")
+    out = torch.zeros((m,), dtype=torch.float16, device="cuda")
+    ms = rptc_kernels.matvec(w, x, out)
+    assert ms > 0
+    truth = (w.float() @ x.float())
+    assert (out.float() - truth).abs().max() <= 1e-3 * truth.abs().max() + 2e-2
+    ms = rptc_kernels.rowsum(w, out)
+    truth = w.float().sum(dim=-1)
+    assert (out.float() - truth).abs().max() <= 1e-3 * truth.abs().max() + 2e-2
