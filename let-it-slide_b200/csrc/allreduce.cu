@@ -10,6 +10,7 @@
 // device memory per CTA, which makes the kernel replayable from a CUDA graph.
 // A wait that runs out raises the device status word and the kernel returns; nothing hangs.
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace rptc {
 
@@ -49,58 +50,6 @@ __device__ __forceinline__ uint4 ld_volatile_128(const void *p) {
     return v;
 }
 
-// Shared FWHT helpers live in hadamard.cu; this file needs only the 8-values-per-thread transform.
-__device__ __forceinline__ void fwht8_ar(float (&v)[8], int block, float *ex) {
-    const int t = threadIdx.x;
-#pragma unroll
-    for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if ((i & h) == 0) {
-                const float a = v[i], b = v[i + h];
-                v[i] = a + b;
-                v[i + h] = a - b;
-            }
-    for (int lm = 1; lm < 32 && 8 * lm < block; lm <<= 1) {
-        const bool upper = (t & lm) != 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], lm);
-            v[i] = upper ? o - v[i] : v[i] + o;
-        }
-    }
-    if (block > 256) {
-        const int G = block >> 8;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
-        __syncthreads();
-        const int n_items = (int)blockDim.x * 8 / G;
-        for (int item = t; item < n_items; item += blockDim.x) {
-            float *base = ex + (item >> 8) * block + (item & 255);
-            float z[16];
-#pragma unroll
-            for (int g = 0; g < 16; ++g) z[g] = g < G ? base[256 * g] : 0.f;
-#pragma unroll
-            for (int h = 1; h < 16; h <<= 1)
-                if (h < G) {
-#pragma unroll
-                    for (int g = 0; g < 16; ++g)
-                        if ((g & h) == 0) {
-                            const float a = z[g], b = z[g + h];
-                            z[g] = a + b;
-                            z[g + h] = a - b;
-                        }
-                }
-#pragma unroll
-            for (int g = 0; g < 16; ++g)
-                if (g < G) base[256 * g] = z[g];
-        }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
-    }
-}
-
 __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams p) {
     __shared__ float ex[4096];
     __shared__ int timed_out;
@@ -123,7 +72,7 @@ __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams
     uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
     if (p.signs_out) sraw = *reinterpret_cast<const uint4 *>(p.signs_out + col);
     const uint4 hraw = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
-    fwht8_ar(v, p.block, ex);
+    fwht8(v, p.block, ex);
     const float sc = p.scale * rsqrtf((float)p.block);
     uint4 mine;
     {

@@ -6,6 +6,7 @@
 // run in registers, strides 8..128 as warp shuffles (__shfl_xor), and strides >= 256 through a
 // shared-memory exchange.  Sign flips, the 1/sqrt(block) scale and the fp16 conversion are fused in.
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace rptc {
 
@@ -21,106 +22,6 @@ struct HadParams {
     int32_t in_is_f32, transpose, clear_in;
     float scale;
 };
-
-__device__ __forceinline__ void load8_f16(const __half *p, float (&v)[8]) {
-    const uint4 a = *reinterpret_cast<const uint4 *>(p);
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(u32_as_half2(w[i]));
-        v[2 * i] = f.x, v[2 * i + 1] = f.y;
-    }
-}
-__device__ __forceinline__ void unpack8(const uint4 a, float (&v)[8]) {
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(u32_as_half2(w[i]));
-        v[2 * i] = f.x, v[2 * i + 1] = f.y;
-    }
-}
-// eight fp16 values as raw bits; a null pointer reads as eight ones (0x3C00)
-__device__ __forceinline__ uint4 raw8_or_ones(const __half *p) {
-    return p ? *reinterpret_cast<const uint4 *>(p) : make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
-}
-__device__ __forceinline__ void load8_f32(float *p, float (&v)[8], bool clear) {
-    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-    if (clear) {
-        *reinterpret_cast<float4 *>(p) = make_float4(0.f, 0.f, 0.f, 0.f);
-        *reinterpret_cast<float4 *>(p + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-}
-__device__ __forceinline__ void store8_f16(__half *p, const float (&v)[8]) {
-    uint32_t o[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = half2_as_u32(__floats2half2_rn(v[2 * i], v[2 * i + 1]));
-    *reinterpret_cast<uint4 *>(p) = make_uint4(o[0], o[1], o[2], o[3]);
-}
-
-// Unnormalised Walsh-Hadamard transform of `block`-sized blocks; thread t holds elements 8t..8t+7 of
-// the CTA's chunk.  `ex` is a shared exchange buffer of chunk floats (used when block > 256).
-__device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
-    const int t = threadIdx.x;
-#pragma unroll
-    for (int h = 1; h < 8; h <<= 1) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if ((i & h) == 0) {
-                const float a = v[i], b = v[i + h];
-                v[i] = a + b;
-                v[i + h] = a - b;
-            }
-        }
-    }
-    for (int lm = 1; lm < 32 && 8 * lm < block; lm <<= 1) {
-        const bool upper = (t & lm) != 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], lm);
-            v[i] = upper ? o - v[i] : v[i] + o;
-        }
-    }
-    if (block > 256) {
-        // Strides 256 .. block/2 mix the 256-element groups: element 256*g + r with element 256*g' + r.  Through
-        // shared memory each of the first chunk/16 threads takes the G = block/256 group values of one r,
-        // transforms them in registers, and puts them back (two barriers instead of one per stride).
-        const int G = block >> 8;                      // 2, 4, 8 or 16
-        __syncthreads();          // the buffer may still be read from an earlier transform
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
-        __syncthreads();
-        const int n_items = (int)blockDim.x * 8 / G;       // (block index, r) pairs in the chunk
-        for (int item = t; item < n_items; item += blockDim.x) {
-            const int blk = item >> 8, r = item & 255;
-            float *base = ex + blk * block + r;
-            float z[16];
-#pragma unroll
-            for (int g = 0; g < 16; ++g) z[g] = g < G ? base[256 * g] : 0.f;
-#pragma unroll
-            for (int h = 1; h < 16; h <<= 1) {
-                if (h < G) {
-#pragma unroll
-                    for (int g = 0; g < 16; ++g) {
-                        if ((g & h) == 0) {
-                            const float a = z[g], b = z[g + h];
-                            z[g] = a + b;
-                            z[g + h] = a - b;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < 16; ++g)
-                if (g < G) base[256 * g] = z[g];
-        }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
-    }
-}
-
-__device__ __forceinline__ float hadamard_norm_dev(int block) { return rsqrtf((float)block); }
 
 __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
     __shared__ float ex[4096];

@@ -4,6 +4,7 @@
 // them has a counterpart in the reference, which evaluates models through Hugging Face
 // transformers (quantize_hf.py:230-236).
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace rptc {
 
@@ -93,10 +94,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                                                                   const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
                                                                   const __half *__restrict__ vcache, __half *__restrict__ out,
                                                                   int64_t ld_out, int hq, int hkv, int max_pos, float scale,
-                                                                  const __half *__restrict__ signs_in) {
+                                                                  const __half *__restrict__ signs_in, float *__restrict__ acc,
+                                                                  int64_t ld_acc, const __half *__restrict__ signs_out,
+                                                                  float scale_out, float theta, __half *__restrict__ kcache_w,
+                                                                  __half *__restrict__ vcache_w) {
     extern __shared__ float sc[];       // [max(ctx, 128)] scores, later the 128 outputs
     __shared__ float red[kAttnWarps];
     __shared__ float part[kAttnWarps][128];
+    __shared__ __align__(16) __half qs[128];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     constexpr int D = 128;
@@ -104,6 +109,42 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int ctx = pos[row] + 1;
     const __half *q = qkv + (int64_t)row * ld_qkv + (int64_t)head * D;
+    if (acc) {
+        // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv
+        // layer's accumulator -- per-head 128-wide output transform, fp16 rounding, rotary embedding -- appends
+        // k and v to the caches and keeps q in shared memory.  Sixteen threads x eight values per vector.
+        if (warp < 2) {
+            const int grp = t >> 4, i8 = (t & 15) * 8;              // 0: q, 1: k, 2: v, 3: idle half warp
+            const int col = (grp == 0 ? head : grp == 1 ? hq + kvh : hq + hkv + kvh) * D + i8;
+            float v[8], sg[8];
+            if (grp < 3) {
+                load8_f32(acc + (int64_t)row * ld_acc + col, v, true);
+                unpack8(raw8_or_ones(signs_out ? signs_out + col : nullptr), sg);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.f, sg[i] = 1.f;
+            }
+            fwht8(v, D, nullptr);
+            const float sc_out = scale_out * hadamard_norm_dev(D);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i] * sc_out * sg[i]));
+            float o[8];
+            const int ps = ctx - 1;
+            const bool upper = i8 >= 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
+                float sn, cs;
+                sincosf(ps * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &sn, &cs);
+                o[i] = grp == 2 ? v[i] : (upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn);
+            }
+            if (grp == 0) store8_f16(qs + i8, o);
+            else if (grp == 1) store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+            else if (grp == 2) store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+        }
+        __syncthreads();       // q is in shared memory; this CTA's cache writes are visible to all its threads
+        q = qs;
+    }
     const float2 q01 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane]);
     const float2 q23 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane + 1]);
     const int64_t stride = (int64_t)hkv * D;
@@ -282,7 +323,33 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
     const size_t smem = (size_t)(max_pos < 128 ? 128 : max_pos) * 4;
     return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), smem, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
-                  static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in));
+                  static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in),
+                  static_cast<float *>(nullptr), (int64_t)0, static_cast<const __half *>(nullptr), 0.f, 0.f,
+                  static_cast<__half *>(nullptr), static_cast<__half *>(nullptr));
+}
+
+extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, const int32_t *pos,
+                                    void *kcache, void *vcache, void *out, int64_t ld_out, int64_t rows, int heads, int max_pos,
+                                    float theta, const void *signs_in, rptc_stream_t stream) {
+    if (!acc || !pos || !kcache || !vcache || !out) return RPTC_ERR_ARG;
+    if (rows <= 0 || rows > 65535 || heads <= 0 || max_pos <= 0 || max_pos > 32768 || ld_acc < (int64_t)3 * heads * 128 ||
+        ld_out < (int64_t)heads * 128)
+        return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
+        (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (ld_acc % 4))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    static bool configured = false;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
+        configured = true;
+    }
+    const size_t smem = (size_t)(max_pos < 128 ? 128 : max_pos) * 4;
+    return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), smem, static_cast<cudaStream_t>(stream),
+                  static_cast<const __half *>(nullptr), (int64_t)0, pos, static_cast<const __half *>(kcache),
+                  static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, heads, max_pos, 0.08838834764831845f,
+                  static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, theta,
+                  static_cast<__half *>(kcache), static_cast<__half *>(vcache));
 }
 
 extern "C" int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,

@@ -57,7 +57,8 @@ class Block:
         q, kv, ffn = cfg.heads * cfg.head_dim // tp, cfg.kv_heads * cfg.head_dim // tp, cfg.ffn // tp
         mk = lambda i, o, s: RPTCLinear.random(i, o, fmt, cfg.weight_scale, seed * 16 + s, device, incoherent)
         self.qkv = mk(cfg.hidden, q + 2 * kv, 0)
-        self.qkv.block_out = hadamard_block(math.gcd(q, kv))
+        # per-head output transform when attention is multi-head: lets one kernel finish q, k, v of a head and attend
+        self.qkv.block_out = cfg.head_dim if (cfg.heads == cfg.kv_heads and cfg.head_dim == 128) else hadamard_block(math.gcd(q, kv))
         self.o = mk(q, cfg.hidden, 1)
         self.o.block_in = min(self.o.block_in, cfg.head_dim)      # one Hadamard block per head: fuses into the attention kernel
         self.gate_up = mk(cfg.hidden, 2 * ffn, 2)
@@ -144,10 +145,15 @@ class RPTCLlama:
         n_launch = 2
         for i, b in enumerate(self.blocks):
             b.qkv.matvec_acc(xt, self.acc_qkv)
-            ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
-                           self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
-            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
-                            cfg.head_dim, signs_in=b.o.signs_in)
+            if self.heads_l == self.kv_heads_l and b.qkv.block_out == 128:
+                ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
+                                    self.heads_l, cfg.rope_theta, b.o.signs_in)
+                n_launch -= 1
+            else:
+                ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                               self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+                ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                                cfg.head_dim, signs_in=b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_h)
             ops.finish_norm_hadamard(self.acc_h, b.o.signs_out, b.o.scale, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in, True, xt)
             b.gate_up.matvec_acc(xt, self.acc_gu)

@@ -41,12 +41,14 @@ def test_rptc_linear_state_dict_round_trip():
     assert torch.equal(a(x), b(x))
 
 
+@pytest.mark.parametrize("kv_heads", [2, 4])
 @pytest.mark.parametrize("incoherent,hidden,ffn", [(True, 512, 1024), (False, 512, 1024), (True, 768, 1536), (True, 1024, 2816)])
-def test_decode_engine_logits_match_fp32_reference(incoherent, hidden, ffn):
+def test_decode_engine_logits_match_fp32_reference(incoherent, hidden, ffn, kv_heads):
     # hidden 512 / 1024 take the fused 9-launch chain, hidden 768 (not one Hadamard block) and the
     # non-incoherent model take the unfused chain
     from rptc_b200.llama import LlamaConfig, RPTCLlama
-    cfg = LlamaConfig(hidden=hidden, layers=2, heads=4, kv_heads=2, ffn=ffn, vocab=1024, max_pos=32, weight_scale=0.05)
+    # kv_heads == heads (4) takes the kernel that finishes q, k, v and attends in one launch
+    cfg = LlamaConfig(hidden=hidden, layers=2, heads=4, kv_heads=kv_heads, ffn=ffn, vocab=1024, max_pos=32, weight_scale=0.05)
     rows, T = 2, 10
     model = RPTCLlama(cfg, rows=rows, seed=7, incoherent=incoherent)
     g = torch.Generator(device="cuda").manual_seed(11)
