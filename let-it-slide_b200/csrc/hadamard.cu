@@ -108,85 +108,13 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
 // ---- fused glue kernels of the decode step ------------------------------------------------------------
 // They exist to shorten the chain of small dependent launches between two fused dequant-GEMVs.
 
-__device__ __forceinline__ float block_sum(float v, float *red) {      // red: >= 17 floats; all threads call
-    const int t = threadIdx.x;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    __syncthreads();
-    if ((t & 31) == 0) red[t >> 5] = v;
-    __syncthreads();
-    float tot = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
-    return tot;
-}
-
-// (1) optional: h = residual + s_out * H(acc) * scale   (the output side of a row's previous layer; acc cleared)
-// (2) xn = rmsnorm(h) * w_norm
-// (3) out = H(s_in * xn) * norm   (the input side of the next layer), or out = xn when no transform is wanted.
-// One CTA per row; the row must be a single Hadamard block (n == block <= 4096).
-struct FinishNormParams {
-    float *acc;                  // fp32 [rows][ld_acc] or NULL (then h is read as it is)
-    int64_t ld_acc;
-    const __half *signs_out;     // [n] or NULL
-    float scale_out;
-    __half *h;                   // fp16 [rows][ld_h]: residual in, updated residual out
-    int64_t ld_h;
-    const __half *w_norm;        // [n]
-    float eps;
-    const __half *signs_in;      // [n] or NULL
-    int transform_in;            // apply the input-side Hadamard transform to the normalised row
-    __half *out;                 // fp16 [rows][ld_out]
-    int64_t ld_out;
-    int32_t n;
-};
 
 __global__ void __launch_bounds__(512) finish_norm_hadamard_kernel(const FinishNormParams p) {
     __shared__ float ex[4096];
     __shared__ float red[20];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
-    const int t = threadIdx.x;
-    const int64_t row = blockIdx.x;
-    const int col = 8 * t;
-    const float hn = hadamard_norm_dev(p.n);
-    // every global load is issued before the first dependent use: one memory round trip for the kernel
-    const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
-    const uint4 raw_h = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
-    const uint4 raw_w = *reinterpret_cast<const uint4 *>(p.w_norm + col);
-    const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
-    float v[8], sg[8];
-    if (p.acc) {
-        load8_f32(p.acc + row * p.ld_acc + col, v, true);
-        fwht8(v, p.n, ex);
-        unpack8(raw_so, sg);
-        float r[8];
-        unpack8(raw_h, r);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = r[i] + v[i] * (p.scale_out * hn) * sg[i];
-        store8_f16(p.h + row * p.ld_h + col, v);
-        // continue from the rounded residual stream, as an unfused reader of h would
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i]));
-    } else {
-        unpack8(raw_h, v);
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-    const float inv = rsqrtf(block_sum(ss, red) / p.n + p.eps);
-    float w[8];
-    unpack8(raw_w, w);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i] * inv * w[i]));
-    if (p.transform_in) {
-        unpack8(raw_si, sg);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= sg[i];
-        fwht8(v, p.n, ex);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= hn;
-    }
-    store8_f16(p.out + row * p.ld_out + col, v);
+    finish_norm_row(p, blockIdx.x, ex, red, false);
 }
 
 // Output side of the fused qkv layer, rotary embedding and KV-cache append in one pass:
