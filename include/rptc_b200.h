@@ -113,6 +113,31 @@ int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, cons
               float *acc, int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
               rptc_stream_t stream);
 
+/* rptc_gemv whose activations are not read from memory but computed, by every CTA for itself, from what the
+ * previous layer of a decoder block left behind: the glue between the two layers then costs no launch of its own.
+ *   h' = h_in + s_out * H(acc) * scale_out;   x = H(s_in * rmsnorm(h') * w_norm)
+ * (what rptc_finish_norm_hadamard computes; n must be 4096, one Hadamard block).  CTA 0 stores h' to h_out,
+ * which must not alias h_in (other CTAs still read h_in).  `acc` is read by every CTA and therefore not cleared
+ * here: name it as `clear` in a LATER launch of the same stream (a launch zeroes its own `clear` range once the
+ * launches before it have completed).  TILED layout, no quirk, batch 1-2.  No reference counterpart (the
+ * reference runs these steps as separate JAX ops). */
+typedef struct rptc_gemv_input {
+    const float *acc;       /* previous layer's accumulator, fp32 [batch][ld_acc >= n], or NULL (h_in as it is) */
+    int64_t ld_acc;
+    const void *signs_out;  /* previous layer's output-side signs, fp16 [n]; NULL = ones */
+    float scale_out;        /* previous layer's scale */
+    float eps;              /* RMSNorm epsilon */
+    const void *signs_in;   /* this layer's input-side signs, fp16 [n]; NULL = ones */
+    const void *h_in;       /* residual stream, fp16 [batch][ld_h] */
+    void *h_out;            /* updated residual stream */
+    int64_t ld_h;
+    const void *w_norm;     /* RMSNorm weight, fp16 [n] */
+    float *clear;           /* optional fp32 range this launch zeroes */
+    int64_t clear_count;    /* floats; multiple of 4 */
+} rptc_gemv_input;
+int rptc_gemv_glued(const void *codes, const void *lut, const uint32_t *carry_in, const rptc_gemv_input *in, float *acc,
+                    int64_t ld_acc, int64_t m, int64_t n, int batch, const rptc_format *fmt, rptc_stream_t stream);
+
 /* y[b][i] = fp16(scale * acc[b][i] (+ y[b][i] if accumulate));  acc[b][i] = 0 if clear.
  * accumulate = 1 gives decompress_matvec_t's `out +=` (inference_t.cu:170-171). */
 int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t m, int batch, float scale,

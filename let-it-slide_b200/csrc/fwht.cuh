@@ -104,12 +104,10 @@ __device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
 
 __device__ __forceinline__ float hadamard_norm_dev(int block) { return rsqrtf((float)block); }
 
-// fp32 x 8 read past L1 and zeroed behind the read
-__device__ __forceinline__ void load8_f32_cg(float *p, float (&v)[8]) {
+// fp32 x 8 read past L1 (the values came from another grid's atomics)
+__device__ __forceinline__ void load8_f32_cg(const float *p, float (&v)[8]) {
     const float4 a = __ldcg(reinterpret_cast<const float4 *>(p)), b = __ldcg(reinterpret_cast<const float4 *>(p) + 1);
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-    *reinterpret_cast<float4 *>(p) = make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4 *>(p + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 __device__ __forceinline__ float block_sum(float v, float *red) {      // red: >= 17 floats; all threads call
@@ -134,6 +132,7 @@ struct FinishNormParams {
     const __half *signs_out;     // [n] or NULL
     float scale_out;
     __half *h;                   // fp16 [rows][ld_h]: residual in, updated residual out
+    __half *h_out;               // where the updated residual goes when not in place (NULL: into h)
     int64_t ld_h;
     const __half *w_norm;        // [n]
     float eps;
@@ -144,32 +143,36 @@ struct FinishNormParams {
     int32_t n;
 };
 
-// One row; called by all n/8 threads of a CTA.  `coherent` reads the accumulator past L1 (it was written by
-// other CTAs' atomics in the same kernel).
-__device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64_t row, float *ex, float *red, bool coherent) {
+// One row; called by all n/8 threads of a CTA.  `owner`: this CTA is the one that clears the accumulator behind
+// its read and stores the updated residual.  When several CTAs compute the same row (each for its own use),
+// exactly one of them is the owner of the residual and nobody clears; the residual then needs h_out != h.
+__device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64_t row, float *ex, float *red, bool clear_acc,
+                                                bool write_h) {
     const int t = threadIdx.x;
     const int col = 8 * t;
     const float hn = hadamard_norm_dev(p.n);
     // every global load is issued before the first dependent use: one memory round trip for the kernel
     const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
-    const uint4 raw_h = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
+    const uint4 raw_h = clear_acc ? *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col)
+                                  : __ldcg(reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col));
     const uint4 raw_w = *reinterpret_cast<const uint4 *>(p.w_norm + col);
     const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
     float v[8], sg[8];
     if (p.acc) {
-        if (coherent) load8_f32_cg(p.acc + row * p.ld_acc + col, v);
-        else load8_f32(p.acc + row * p.ld_acc + col, v, true);
+        if (clear_acc) load8_f32(p.acc + row * p.ld_acc + col, v, true);
+        else load8_f32_cg(p.acc + row * p.ld_acc + col, v);
         fwht8(v, p.n, ex);
         unpack8(raw_so, sg);
         float r[8];
         unpack8(raw_h, r);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = r[i] + v[i] * (p.scale_out * hn) * sg[i];
-        store8_f16(p.h + row * p.ld_h + col, v);
+        if (write_h) store8_f16((p.h_out ? p.h_out : p.h) + row * p.ld_h + col, v);
         // continue from the rounded residual stream, as an unfused reader of h would
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(v[i]));
     } else {
+        if (write_h && p.h_out) *reinterpret_cast<uint4 *>(p.h_out + row * p.ld_h + col) = raw_h;
         unpack8(raw_h, v);
     }
     float ss = 0.f;
@@ -189,6 +192,58 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
         for (int i = 0; i < 8; ++i) v[i] *= hn;
     }
     store8_f16(p.out + row * p.ld_out + col, v);
+}
+
+// Fused MLP middle: gate/up pre-activations arrive as the fp32 accumulator of the fused gate-up
+// layer (gate in columns [0, n), up in [n, 2n)).  out = H (s_in * (silu(g) * u)) * scale_in with
+// g, u = s_out * (H acc) * scale_out.  Both transforms use the same block size, so one CTA owns
+// matching blocks of gate and up.
+struct SwigluParams {
+    float *acc;
+    int64_t ld_acc;
+    __half *out;
+    int64_t ld_out;
+    const __half *signs_out;    // [2n] output-side signs of the gate-up layer (may be NULL)
+    const __half *signs_in;     // [n] input-side signs of the down layer (may be NULL)
+    int64_t n;
+    int32_t block, chunk, clear;
+    float scale_out, scale_in;  // both include the 1/sqrt(block) of their transform
+};
+
+// Columns col .. col+7 of one row (thread t of the chunk holds 8t..8t+7); result to dst[0..7].
+__device__ __forceinline__ void swiglu_chunk(const SwigluParams &p, int64_t row, int64_t col, float *ex, bool clear, __half *dst) {
+    float g[8], u[8], sg[8];
+    const uint4 raw_sg = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
+    const uint4 raw_su = raw8_or_ones(p.signs_out ? p.signs_out + p.n + col : nullptr);
+    const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
+    if (clear) {
+        load8_f32(p.acc + row * p.ld_acc + col, g, true);
+        load8_f32(p.acc + row * p.ld_acc + p.n + col, u, true);
+    } else {
+        load8_f32_cg(p.acc + row * p.ld_acc + col, g);
+        load8_f32_cg(p.acc + row * p.ld_acc + p.n + col, u);
+    }
+    fwht8(g, p.block, ex);
+    fwht8(u, p.block, ex);
+    unpack8(raw_sg, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= p.scale_out * sg[i];
+    unpack8(raw_su, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u[i] *= p.scale_out * sg[i];
+    // the layer's own output is fp16; round there as the unfused path would
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float gg = __half2float(__float2half_rn(g[i])), uu = __half2float(__float2half_rn(u[i]));
+        g[i] = __half2float(__float2half_rn(gg / (1.f + __expf(-gg)) * uu));
+    }
+    unpack8(raw_si, sg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= sg[i];
+    fwht8(g, p.block, ex);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= p.scale_in;
+    store8_f16(dst, g);
 }
 
 }  // namespace rptc

@@ -17,6 +17,7 @@
 // Activations are staged once per CTA in shared memory and read back as warp-broadcast LDS.128.
 // Other layouts (and the reference-quirk modes) take a plain 128-bit-load path in the same kernel.
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace rptc {
 
@@ -50,6 +51,8 @@ struct GemvParams {
     int32_t n_units, seg_units;
     int32_t L, S, quirk, x_order;
     unsigned int *status;
+    // activations computed in the launch (pair kernel, INPUT != 0): the caller's descriptor
+    rptc_gemv_input in;
 };
 
 // Source pair of stream pair s under the fused reference kernel's x staging (inference.cu:216-221,249).
@@ -318,7 +321,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 // 64*p + l and 64*p + 32 + l).  The two 512-byte pieces arrive in one ring stage on one mbarrier, and the
 // activation quads read from shared memory serve both rows: the broadcast x loads, which cost more
 // shared-memory wavefronts than their count suggests, are halved per weight.  TILED layout only.
-template <int CODE, int K, int BATCH>
+//
+// INPUT != 0: instead of copying x from memory each CTA computes it from the previous layer's accumulator and
+// the residual stream: the single-CTA glue kernel between two matvecs, its launch and its round trip through
+// memory disappear, at the price of every CTA repeating the arithmetic of one 4096-element row.
+template <int CODE, int K, int BATCH, int INPUT>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;
     constexpr int PAIRS = WPU / 2;
@@ -403,7 +410,36 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
             waited_prior = true;
         }
         if (useg0 > 0) __syncthreads();
-        {
+        if (INPUT != 0) {
+            // one segment by construction (the host refuses wider rows)
+            if (p.in.clear) {
+                float4 *z = reinterpret_cast<float4 *>(p.in.clear);
+                for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.in.clear_count;
+                     i += (int64_t)gridDim.x * kGemvThreads)
+                    z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+            {
+                float *ex = reinterpret_cast<float *>(smem_raw + (xs - s0) + BATCH * x_batch_stride);
+                FinishNormParams q;
+                q.acc = const_cast<float *>(p.in.acc);
+                q.ld_acc = p.in.ld_acc;
+                q.signs_out = static_cast<const __half *>(p.in.signs_out);
+                q.scale_out = p.in.scale_out;
+                q.h = const_cast<__half *>(static_cast<const __half *>(p.in.h_in));
+                q.h_out = static_cast<__half *>(p.in.h_out);
+                q.ld_h = p.in.ld_h;
+                q.w_norm = static_cast<const __half *>(p.in.w_norm);
+                q.eps = p.in.eps;
+                q.signs_in = static_cast<const __half *>(p.in.signs_in);
+                q.transform_in = 1;
+                q.out = x_sm;
+                q.ld_out = x_batch_stride >> 1;
+                q.n = (int32_t)p.n;
+#pragma unroll 1
+                for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
+            }
+        } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
             const int pairs = nu * PAIRS;
             if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
@@ -569,10 +605,10 @@ static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
-template <int CODE, int K, int BATCH>
+template <int CODE, int K, int BATCH, int INPUT = 0>
 static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemv_pair_kernel<CODE, K, BATCH>;
+    auto kern = gemv_pair_kernel<CODE, K, BATCH, INPUT>;
     if (!configured) {
         RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
@@ -593,6 +629,10 @@ static int dispatch_batch(const GemvParams &p, int batch, size_t smem, cudaStrea
 
 template <int CODE, int K>
 static int dispatch_tma(const GemvParams &p, int batch, bool tma, size_t smem, cudaStream_t stream) {
+    if (p.in.h_in) {
+        if (!tma || batch > 2) return RPTC_ERR_UNSUPPORTED;
+        return batch == 1 ? launch_gemv_pair<CODE, K, 1, 1>(p, smem, stream) : launch_gemv_pair<CODE, K, 2, 1>(p, smem, stream);
+    }
     if (tma) return dispatch_batch<CODE, K, true>(p, batch, smem, stream);
     if (batch != 1) return RPTC_ERR_UNSUPPORTED;
     return launch_gemv<CODE, K, 1, false>(p, smem, stream);
@@ -600,7 +640,8 @@ static int dispatch_tma(const GemvParams &p, int batch, bool tma, size_t smem, c
 
 // One launch for batch in {1,2,4,8}.
 static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in, const __half *x, int64_t ld_x, float *acc,
-                    int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format &f, cudaStream_t stream) {
+                    int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format &f, cudaStream_t stream,
+                    const rptc_gemv_input *in = nullptr) {
     const int K = f.K;
     const int wpu = 128 / K;
     GemvParams p;
@@ -622,6 +663,7 @@ static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
     const bool tma = f.layout == RPTC_LAYOUT_TILED && f.quirk == RPTC_QUIRK_NONE;
+    p.in = in ? *in : rptc_gemv_input{};
 
     // shared-memory plan (must mirror the kernel's)
     const size_t kMaxSmem = 227 * 1024 - 1024;     // leave room for the 1 KiB the system may reserve
@@ -637,7 +679,12 @@ static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in
     if (seg < 1) return RPTC_ERR_TOO_LARGE;
     if (seg > p.n_units) seg = p.n_units;
     p.seg_units = (int32_t)seg;
-    const size_t smem = fixed + size_t(seg) * unit_x_bytes;
+    size_t smem = fixed + size_t(seg) * unit_x_bytes;
+    if (in) {
+        if (seg != p.n_units) return RPTC_ERR_TOO_LARGE;                        // computed activations live in one segment
+        smem += 4096 * sizeof(float) + 128;                                     // exchange buffer of the 4096-point transform
+        if (smem > kMaxSmem) return RPTC_ERR_TOO_LARGE;
+    }
 
     switch (f.code) {
         case RPTC_CODE_LUT:
@@ -736,4 +783,26 @@ extern "C" int rptc_gemv_f16_static(const void *codes, const void *lut, const ui
     RPTC_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)batch * (size_t)m, s));
     if (int e = rptc_gemv(codes, lut, carry_in, x, ld_x, acc, m, m, n, batch, x_order, fmt, stream)) return e;
     return rptc_gemv_finish(acc, m, y, ld_y, m, batch, 1.0f, 0, 0, stream);
+}
+
+extern "C" int rptc_gemv_glued(const void *codes, const void *lut, const uint32_t *carry_in, const rptc_gemv_input *in, float *acc,
+                               int64_t ld_acc, int64_t m, int64_t n, int batch, const rptc_format *fmt, rptc_stream_t stream) {
+    if (!codes || !lut || !in || !acc || !fmt) return RPTC_ERR_ARG;
+    if (int e = check_format(fmt)) return e;
+    if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
+    if (fmt->layout != RPTC_LAYOUT_TILED || fmt->quirk != RPTC_QUIRK_NONE || batch < 1 || batch > 2) return RPTC_ERR_UNSUPPORTED;
+    if (m <= 0 || n <= 0 || (m % 32) || (n % (128 / fmt->K)) || ld_acc < m) return RPTC_ERR_SHAPE;
+    if (m > (int64_t(1) << 30) || (m / 32) * (n / (128 / fmt->K)) >= (int64_t(1) << 31)) return RPTC_ERR_TOO_LARGE;
+    auto misaligned = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+    if (misaligned(codes) || misaligned(lut) || misaligned(in->acc) || misaligned(in->signs_out) || misaligned(in->signs_in) ||
+        misaligned(in->clear) || (in->ld_acc % 4) || (in->clear_count % 4))
+        return RPTC_ERR_ALIGN;
+    if (in->clear_count < 0 || (in->clear_count && !in->clear)) return RPTC_ERR_ARG;
+    if (n != 8 * kGemvThreads) return RPTC_ERR_UNSUPPORTED;                     // one 4096-point block, eight values a thread
+    if (!in->h_in || !in->h_out || in->h_in == in->h_out || !in->w_norm) return RPTC_ERR_ARG;
+    if (in->ld_h < n || (in->acc && in->ld_acc < n)) return RPTC_ERR_SHAPE;
+    if (misaligned(in->h_in) || misaligned(in->h_out) || misaligned(in->w_norm) || (in->ld_h % 8)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    return gemv_one(codes, lut, carry_in, nullptr, 0, acc, ld_acc, m, n, batch, RPTC_XORDER_NATURAL, *fmt,
+                    static_cast<cudaStream_t>(stream), in);
 }

@@ -53,56 +53,13 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
     store8_f16(p.out + row * p.ld_out + col, v);
 }
 
-// Fused MLP middle: gate/up pre-activations arrive as the fp32 accumulator of the fused gate-up
-// layer (gate in columns [0, n), up in [n, 2n)).  out = H (s_in * (silu(g) * u)) * scale_in with
-// g, u = s_out * (H acc) * scale_out.  Both transforms use the same block size, so one CTA owns
-// matching blocks of gate and up.
-struct SwigluParams {
-    float *acc;
-    int64_t ld_acc;
-    __half *out;
-    int64_t ld_out;
-    const __half *signs_out;    // [2n] output-side signs of the gate-up layer (may be NULL)
-    const __half *signs_in;     // [n] input-side signs of the down layer (may be NULL)
-    int64_t n;
-    int32_t block, chunk, clear;
-    float scale_out, scale_in;
-};
-
 __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams p) {
     __shared__ float ex[4096];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
-    const int t = threadIdx.x;
     const int64_t row = blockIdx.y;
-    const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
-    float g[8], u[8], sg[8];
-    const uint4 raw_sg = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
-    const uint4 raw_su = raw8_or_ones(p.signs_out ? p.signs_out + p.n + col : nullptr);
-    const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
-    load8_f32(p.acc + row * p.ld_acc + col, g, p.clear != 0);
-    load8_f32(p.acc + row * p.ld_acc + p.n + col, u, p.clear != 0);
-    fwht8(g, p.block, ex);
-    fwht8(u, p.block, ex);
-    unpack8(raw_sg, sg);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] *= p.scale_out * sg[i];
-    unpack8(raw_su, sg);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) u[i] *= p.scale_out * sg[i];
-    // the layer's own output is fp16; round there as the unfused path would
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float gg = __half2float(__float2half_rn(g[i])), uu = __half2float(__float2half_rn(u[i]));
-        g[i] = __half2float(__float2half_rn(gg / (1.f + __expf(-gg)) * uu));
-    }
-    unpack8(raw_si, sg);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] *= sg[i];
-    fwht8(g, p.block, ex);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] *= p.scale_in;
-    store8_f16(p.out + row * p.ld_out + col, g);
+    const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * threadIdx.x;
+    swiglu_chunk(p, row, col, ex, p.clear != 0, p.out + row * p.ld_out + col);
 }
 
 // ---- fused glue kernels of the decode step ------------------------------------------------------------
@@ -114,7 +71,7 @@ __global__ void __launch_bounds__(512) finish_norm_hadamard_kernel(const FinishN
     __shared__ float red[20];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
-    finish_norm_row(p, blockIdx.x, ex, red, false);
+    finish_norm_row(p, blockIdx.x, ex, red, true, true);
 }
 
 // Output side of the fused qkv layer, rotary embedding and KV-cache append in one pass:
@@ -260,6 +217,7 @@ extern "C" int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void 
     p.signs_out = static_cast<const __half *>(signs_out);
     p.scale_out = scale_out;
     p.h = static_cast<__half *>(h);
+    p.h_out = nullptr;
     p.ld_h = ld_h;
     p.w_norm = static_cast<const __half *>(w_norm);
     p.eps = eps;

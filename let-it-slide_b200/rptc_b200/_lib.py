@@ -55,6 +55,14 @@ class Format(ctypes.Structure):
         return 2 << self.S
 
 
+class GemvInput(ctypes.Structure):
+    """Mirror of `rptc_gemv_input`."""
+    _fields_ = [("acc", ctypes.c_void_p), ("ld_acc", ctypes.c_int64),
+                ("signs_out", ctypes.c_void_p), ("scale_out", ctypes.c_float), ("eps", ctypes.c_float),
+                ("signs_in", ctypes.c_void_p), ("h_in", ctypes.c_void_p), ("h_out", ctypes.c_void_p), ("ld_h", ctypes.c_int64),
+                ("w_norm", ctypes.c_void_p), ("clear", ctypes.c_void_p), ("clear_count", ctypes.c_int64)]
+
+
 _lib = None
 
 _SIGS = {
@@ -71,6 +79,9 @@ _SIGS = {
     "rptc_gemv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                  ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
                                  ctypes.POINTER(Format), ctypes.c_void_p]),
+    "rptc_gemv_glued": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(GemvInput), ctypes.c_void_p,
+                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.POINTER(Format),
+                                       ctypes.c_void_p]),
     "rptc_gemv_finish": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                         ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "rptc_gemv_f16_static": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,

@@ -113,11 +113,15 @@ class RPTCLlama:
         self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
         self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
         self.acc_gu = torch.zeros((rows, 2 * self.ffn_l), **f32)
+        # second residual stream and accumulator of the shortest chain, whose matvecs compute their own inputs
+        self.h2 = torch.zeros((rows, cfg.hidden), **f16)
+        self.acc_o = torch.zeros((rows, cfg.hidden), **f32)
         self.peer = None
         if tp_world > 1 and peer_allreduce and incoherent:
             # the fused transform + all-reduce + residual kernel over NVLink peer memory instead of NCCL
             from .tp import PeerAllReduce
             self.peer = PeerAllReduce(rows, cfg.hidden, self.blocks[0].o.block_out, tp_rank, tp_world, tp_group)
+        self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
 
@@ -129,8 +133,17 @@ class RPTCLlama:
         return (self.tp_world == 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 4096
                 and self.cfg.head_dim == 128)
 
+    def _glueable(self) -> bool:
+        """The shortest chain (6 launches per block) additionally needs hidden == 4096 (eight values a thread of the
+        512-thread matvec CTA), at most two rows and multi-head attention."""
+        b = self.blocks[0]
+        return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and self.heads_l == self.kv_heads_l
+                and b.qkv.block_out == 128 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
+
     def step_eager(self) -> None:
-        if self._fusable():
+        if self._glueable():
+            self._step_glued()
+        elif self._fusable():
             self._step_fused()
         else:
             self._step_unfused()
@@ -173,6 +186,35 @@ class RPTCLlama:
         self.ids.copy_(self.next_ids)
         self.pos.add_(1)
         self.launches_per_step = n_launch + 1
+
+    def _step_glued(self) -> None:
+        """qkv matvec -> attention -> o matvec -> gate-up matvec -> SwiGLU -> down matvec.  The two matvecs that
+        follow a row-parallel layer compute their activations (residual update, RMSNorm, input transform) from
+        that layer's accumulator themselves.  The residual stream alternates between h and h2; an accumulator
+        that every CTA of a launch reads is zeroed by a later launch (`clear`)."""
+        cfg, r = self.cfg, self.rows
+        ops.embed(self.embed, self.ids, self.h)
+        for i, b in enumerate(self.blocks):
+            prev = self.blocks[i - 1].down if i else None
+            ops.gemv_norm_input(b.qkv.codes, b.qkv.lut, self.acc_qkv, b.qkv.out_features, cfg.hidden, self.fmt, r,
+                                self.acc_h if prev else None, prev.signs_out if prev else None, prev.scale if prev else 1.0,
+                                self.h, self.h2, b.norm1, cfg.rms_eps, b.qkv.signs_in, clear=self.acc_o)
+            ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
+                                self.heads_l, cfg.rope_theta, b.o.signs_in)
+            b.o.matvec_acc(self.attn, self.acc_o)
+            ops.gemv_norm_input(b.gate_up.codes, b.gate_up.lut, self.acc_gu, b.gate_up.out_features, cfg.hidden, self.fmt, r,
+                                self.acc_o, b.o.signs_out, b.o.scale, self.h2, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in,
+                                clear=self.acc_h if i else None)
+            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                b.gate_up.scale, 1.0, clear=True)
+            b.down.matvec_acc(self.mlp, self.acc_h)
+        last = self.blocks[-1].down
+        ops.finish_norm_hadamard(self.acc_h, last.signs_out, last.scale, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        torch.argmax(self.logits, dim=1, out=self.next_ids)
+        self.ids.copy_(self.next_ids)
+        self.pos.add_(1)
+        self.launches_per_step = 6 * len(self.blocks) + 3
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
@@ -252,6 +294,7 @@ class RPTCLlama:
 
     def reset(self, ids: torch.Tensor | None = None) -> None:
         self.pos.zero_()
+        self.acc_o.zero_()          # the six-launch chain leaves it to the next token's first launch
         if ids is not None:
             self.ids.copy_(ids.to(torch.int32))
 

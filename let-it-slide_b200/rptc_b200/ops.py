@@ -19,6 +19,10 @@ def _cuda_contig(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -
         raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
 
 
+def _ld(t: torch.Tensor, width: int) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(width, t.stride(0))
+
+
 def units_per_row(n: int, K: int) -> int:
     if (n * K) % 128:
         raise RuntimeError(f"n*K = {n * K} bits per row is not a whole number of 128-bit units")
@@ -100,6 +104,20 @@ def gemv_acc(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, acc: torch
                               x_order, ctypes.byref(fmt), stream_ptr()), "rptc_gemv")
 
 
+def gemv_norm_input(codes: torch.Tensor, lut: torch.Tensor, acc: torch.Tensor, m: int, n: int, fmt: Format, rows: int,
+                    prev_acc: torch.Tensor | None, signs_out: torch.Tensor | None, scale_out: float, h_in: torch.Tensor,
+                    h_out: torch.Tensor, w_norm: torch.Tensor, eps: float, signs_in: torch.Tensor | None,
+                    clear: torch.Tensor | None = None, carry_in: torch.Tensor | None = None) -> None:
+    """acc += W x with x = H(s_in * rmsnorm(h_in + s_out * H(prev_acc) * scale_out) * w_norm), computed inside the
+    launch; the updated residual goes to h_out (rptc_gemv_glued).  `clear` is zeroed by the launch."""
+    from ._lib import GemvInput
+    d = GemvInput(ptr(prev_acc), 0 if prev_acc is None else _ld(prev_acc, n), ptr(signs_out), scale_out, eps,
+                  ptr(signs_in), ptr(h_in), ptr(h_out), _ld(h_in, n), ptr(w_norm), ptr(clear), 0 if clear is None else clear.numel())
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_gemv_glued(ptr(codes), ptr(lut), ptr(carry_in), ctypes.byref(d), ptr(acc), _ld(acc, m), m, n, rows,
+                                    ctypes.byref(fmt), stream_ptr()), "rptc_gemv_glued")
+
+
 def gemv_finish(acc: torch.Tensor, y: torch.Tensor, m: int, scale: float = 1.0, accumulate: bool = False,
                 clear: bool = True) -> None:
     """y = fp16(scale * acc) (+ y); optionally zero acc (rptc_gemv_finish)."""
@@ -137,10 +155,6 @@ def gemm(codes: torch.Tensor, lut: torch.Tensor, x: torch.Tensor, m: int, n: int
         check(lib().rptc_gemm(ptr(codes), ptr(lut), ptr(carry_in), ptr(x), x.stride(0), ptr(out), out.stride(0), m, n,
                               x.shape[0], ctypes.byref(fmt), stream_ptr()), "rptc_gemm")
     return out
-
-
-def _ld(t: torch.Tensor, width: int) -> int:
-    return t.stride(0) if t.shape[0] > 1 else max(width, t.stride(0))
 
 
 def hadamard(x: torch.Tensor, signs: torch.Tensor | None, block: int, transpose: bool = False, scale: float = 1.0,

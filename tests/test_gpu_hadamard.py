@@ -67,3 +67,40 @@ def test_finish_norm_hadamard(n, transform_in):
     assert not d_acc.any()                                   # accumulator handed back cleared
     np.testing.assert_allclose(d_h.float().cpu().numpy(), ref_h, atol=4e-3, rtol=2e-3)
     np.testing.assert_allclose(out.float().cpu().numpy(), ref_out, atol=1e-2, rtol=5e-3)
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("m", [4096, 22016])
+@pytest.mark.parametrize("with_acc", [True, False])
+def test_gemv_computing_its_own_input_matches_glue_then_gemv(batch, m, with_acc):
+    """rptc_gemv_glued against rptc_finish_norm_hadamard followed by rptc_gemv, several calls in a row."""
+    from gpu_util import rand_lut, rand_words
+    from rptc_b200 import Format, ops
+    rng = np.random.default_rng(batch * 7 + m + with_acc)
+    n = 4096
+    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
+    codes = to_dev(o.from_rowmajor(rand_words(rng, m, n, 2), o.LAYOUT_TILED))
+    lut = to_dev(rand_lut(rng, o.CODE_B, S=8))
+    w_norm = to_dev((1 + 0.1 * rng.standard_normal(n)).astype(np.float16))
+    s_out, s_in = to_dev(o.signs_from_seed(7, n).astype(np.float16)), to_dev(o.signs_from_seed(8, n).astype(np.float16))
+    dirty = torch.ones(1024, dtype=torch.float32, device="cuda")
+    for rep in range(3):
+        prev = to_dev(rng.standard_normal((batch, n)).astype(np.float32)) if with_acc else None
+        h0 = to_dev(rng.standard_normal((batch, n)).astype(np.float16))
+        h_a, x_a = h0.clone(), torch.empty_like(h0)
+        acc_a = torch.zeros(batch, m, dtype=torch.float32, device="cuda")
+        ops.finish_norm_hadamard(prev.clone() if with_acc else None, s_out, 0.3, h_a, w_norm, 1e-5, s_in, True, x_a)
+        ops.gemv_acc(codes, lut, x_a, acc_a, m, n, fmt)
+        h_b, acc_b = torch.full_like(h0, float("nan")), torch.zeros_like(acc_a)
+        keep = prev.clone() if with_acc else None
+        ops.gemv_norm_input(codes, lut, acc_b, m, n, fmt, batch, prev, s_out, 0.3, h0, h_b, w_norm, 1e-5, s_in, clear=dirty)
+        torch.cuda.synchronize()
+        ops.device_status()
+        assert torch.equal(h_b, h_a)                           # same arithmetic, one writer
+        assert not dirty.any()
+        dirty.fill_(1.0)
+        if with_acc:
+            assert torch.equal(prev, keep)                     # read by every CTA, cleared by none
+        # identical activations; the partial sums meet in a different order
+        scale = acc_a.abs().max().item()
+        assert (acc_b - acc_a).abs().max().item() <= 1e-4 * scale

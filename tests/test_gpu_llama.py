@@ -68,3 +68,44 @@ def test_decode_engine_logits_match_fp32_reference(incoherent, hidden, ffn, kv_h
         assert model.pos.tolist() == [T] * rows
     from rptc_b200 import ops
     ops.device_status()
+
+
+@pytest.mark.parametrize("rows", [1, 2])
+def test_six_launch_chain_matches_reference_and_separate_glue(rows):
+    """hidden 4096, multi-head: the qkv and gate-up matvecs compute their activations from the previous accumulator."""
+    from rptc_b200 import ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=4096, layers=3, heads=32, kv_heads=32, ffn=1792, vocab=512, max_pos=16, weight_scale=0.02)
+    T = 6
+    model = RPTCLlama(cfg, rows=rows, seed=3)
+    assert model._glueable()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
+    ref = model.reference_logits(tokens)
+    logits = {}
+    for glued in (False, True):
+        model.glued = glued
+        for use_graph in (False, True):
+            model.reset()
+            model.graph = None
+            if use_graph:
+                model.capture(pdl=True)
+            for t in range(T):
+                model.ids.copy_(tokens[:, t].to(torch.int32))
+                model.step()
+                torch.cuda.synchronize()
+                got = model.logits.float()
+                err = (got - ref[:, t]).abs().max().item()
+                # 4096-long dot products of fp16 activations: twice the slack of the small models above
+                assert err <= 2e-2 * ref[:, t].abs().max().item(), (glued, use_graph, t, err)
+                logits[glued, use_graph, t] = got.clone()
+            assert model.launches_per_step == (6 if glued else 8) * cfg.layers + 3
+            # every accumulator is handed back zeroed, whichever launch owned the clearing
+            model.graph = None
+            ops.embed(model.embed, model.ids, model.h)        # any launch after the step: orders the check below
+            torch.cuda.synchronize()
+            assert not model.acc_qkv.any() and not model.acc_gu.any() and not model.acc_h.any()
+    for t in range(T):
+        scale = ref[:, t].abs().max().item()
+        assert (logits[True, True, t] - logits[False, True, t]).abs().max().item() <= 4e-3 * scale
+    ops.device_status()
