@@ -266,8 +266,9 @@ __device__ __forceinline__ void make_windows(const uint32_t (&w)[GroupShape<K>::
 }
 
 // Weight pair p (columns 2p, 2p+1) of a group from its window registers.  `p` must be a constant after unrolling.
-template <int CODE, int K>
-__device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[2 * GroupShape<K>::kWords], const Lut<CODE> &lut, int p) {
+// The registers may cover any whole number of words (a group, or a single word with the word before it).
+template <int CODE, int K, int N>
+__device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[N], const Lut<CODE> &lut, int p) {
     if (CODE == RPTC_CODE_LUT) {
         uint32_t h[2];
 #pragma unroll

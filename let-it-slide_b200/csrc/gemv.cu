@@ -65,98 +65,53 @@ __device__ __forceinline__ int64_t k2_legacy_pair(int64_t s, int64_t n) {
     return 4 * (p % q8) + p / q8;
 }
 
-template <int CODE, int K, int BATCH, bool TMA>
+// The general kernel: any layout (strided 128-bit loads straight from memory, one unit of one row block per
+// step), the reference kernels' lane-0 deviations, batch 1.  The native TILED layout takes the two kernels below.
+template <int CODE, int K>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;          // weights per unit
     constexpr int PAIRS = WPU / 2;
-    constexpr int GU = TMA ? kStageUnits : 1;      // units per granule (= per ring stage on the TMA path)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t s0 = smem_addr(smem_raw);
-    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
-    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
     uint32_t lut_tab, xs;
     if (CODE == RPTC_CODE_HASH) {
         lut_tab = kHashLutWindow;
         xs = kHashLutWindow + kHashLutBytes;
     } else {
-        lut_tab = s0 + kBarBytes + (TMA ? kRingBytes : 0u);
+        lut_tab = s0 + kBarBytes;
         xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
-    }
-
-    if (CODE == RPTC_CODE_HASH && TMA && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
-        // the dynamic area starts later in the shared window than this kernel was laid out for
-        if (threadIdx.x == 0) atomicExch(p.status, 2u);
-        return;
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
     lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
-    if (TMA && lane == 0) {
-#pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
-        mbar_fence_init();
-    }
-    __syncwarp();
     const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
     pdl_allow_next_grid();
 
     const uint32_t n_rb = (uint32_t)(p.m >> 5);
     const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
-    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;     // bytes of one batch row in shared memory
-    uint32_t slot = 0, phase = 0;           // ring position of the next stage to consume (kept across segments)
-    bool ok = true;
     bool waited_prior = false;
 
     for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
         const int32_t nu = min(p.seg_units, p.n_units - useg0);
-        // A granule is GU consecutive units of one row block (the last one of a block may be short).
-        const int32_t gpr = (nu + GU - 1) / GU;                 // granules per row block
-        const int32_t tail_units = nu - (gpr - 1) * GU;         // units in a block's last granule
-        // Balanced contiguous split of the T granules over the GW warps of the grid, in 32-bit arithmetic:
-        // the first T % GW warps take one granule more than the others.
-        const uint32_t T = (uint32_t)n_rb * (uint32_t)gpr;
+        // Balanced contiguous split of the T = row blocks x units steps over the GW warps of the grid, in 32-bit
+        // arithmetic: the first T % GW warps take one step more than the others.
+        const uint32_t T = (uint32_t)n_rb * (uint32_t)nu;
         const uint32_t per = T / GW, extra = T - per * GW;
         const uint32_t g0 = gw * per + min(gw, extra);
         const uint32_t count = per + (gw < extra ? 1u : 0u);
-        const uint32_t rb0 = count ? g0 / (uint32_t)gpr : 0u;
-        const int32_t gi0 = count ? (int32_t)(g0 - rb0 * (uint32_t)gpr) : 0;
+        const uint32_t rb0 = count ? g0 / (uint32_t)nu : 0u;
+        const int32_t gi0 = count ? (int32_t)(g0 - rb0 * (uint32_t)nu) : 0;
 
-        // ---- fetch cursor (used by lane 0 on the TMA path, by every lane on the plain-load path) ----
-        int64_t frb = rb0;
+        int64_t frb = rb0;          // fetch cursor, one step ahead of the decode
         int32_t fgi = gi0;
-        const uint4 *fptr = p.codes + unit_index(p.st, useg0 + gi0 * GU, (int64_t)rb0 << 5);
-        const int64_t seg_skip = (int64_t)(p.n_units - nu) << 5;          // TILED: gap between row blocks of a column segment
-        auto issue_stage = [&](uint32_t at_slot) {                        // lane 0, TMA path: one bulk copy per granule
-            const uint32_t units = (fgi == gpr - 1) ? (uint32_t)tail_units : (uint32_t)GU;
-            const uint32_t bar = bars + 8u * at_slot;
-            mbar_expect_tx(bar, units * kUnitBytes);
-            bulk_g2s(ring + at_slot * kStageBytes, fptr, units * kUnitBytes, bar);
-            fptr += units << 5;
-            if (++fgi == gpr) {
-                fgi = 0;
-                fptr += seg_skip;
-            }
-        };
-        auto next_unit_ptr = [&]() -> const uint4 * {                     // plain-load path (GU == 1)
+        auto next_unit_ptr = [&]() -> const uint4 * {
             const uint4 *ptr = p.codes + unit_index(p.st, useg0 + fgi, (frb << 5) + lane);
-            if (++fgi == gpr) {
+            if (++fgi == nu) {
                 fgi = 0;
                 ++frb;
             }
             return ptr;
         };
-        uint32_t to_issue = count;
-        if (TMA) {
-            const uint32_t ahead = min(count, (uint32_t)kStages);
-            if (lane == 0) {
-                uint32_t sl = slot;
-                for (uint32_t k = 0; k < ahead; ++k) {
-                    issue_stage(sl);
-                    if (++sl == kStages) sl = 0;
-                }
-            }
-            to_issue -= ahead;
-        }
 
         // ---- activations of this column segment -> shared memory ----
         if (!waited_prior) {
@@ -167,130 +122,58 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         {
             const int64_t col0 = (int64_t)useg0 * WPU;
             const int pairs = nu * PAIRS;
-            if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
-                // 128-bit copies, four loads in flight per thread
-                const int vecs = pairs >> 2;                 // PAIRS is a multiple of 4
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
-                    const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
-                    for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
-                        uint4 v[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs)
-                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
-                                             "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
-                                             : "memory");
-                    }
-                }
-            } else {
-                for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
-                    const int b = i / pairs, s = i - b * pairs;
-                    int64_t src = (col0 >> 1) + s;
-                    if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
-                }
+            for (int i = threadIdx.x; i < pairs; i += kGemvThreads) {
+                int64_t src = (col0 >> 1) + i;
+                if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x) + src);
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + 4u * i), "r"(v) : "memory");
             }
         }
         __syncthreads();
 
-        // ---- main loop over this warp's granules ----
+        // ---- main loop over this warp's steps ----
         int64_t rb = rb0;
         int32_t gi = gi0;
-        bool fresh = true;                        // the next granule starts a run: fetch its history, zero the sums
+        bool fresh = true;                        // the next step starts a run: fetch its history, zero the sum
         uint32_t prevw = 0;
-        float facc[BATCH];
+        float facc = 0.f;
         uint4 nextv = make_uint4(0, 0, 0, 0);
-        if (!TMA && count > 0) nextv = ldg128_stream(next_unit_ptr());
+        if (count > 0) nextv = ldg128_stream(next_unit_ptr());
 
 #pragma unroll 1
         for (uint32_t k = 0; k < count; ++k) {
             const int64_t row = (rb << 5) + lane;
+            const int32_t u = useg0 + gi;
             if (fresh) {
                 fresh = false;
-                const int32_t u0 = useg0 + gi * GU;
-                if (u0 == 0)
+                if (u == 0)
                     prevw = p.carry_in ? __ldg(p.carry_in + row) : 0u;
                 else
-                    prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u0 - 1, row)) + 3);
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) facc[b] = 0.f;
+                    prevw = __ldg(reinterpret_cast<const uint32_t *>(p.codes + unit_index(p.st, u - 1, row)) + 3);
+                facc = 0.f;
             }
-            const bool last_of_block = gi == gpr - 1;
-            const int units = last_of_block ? tail_units : GU;
-            if (TMA) {
-                ok = mbar_wait(bars + 8u * slot, phase, p.status);
-                if (!ok) break;
+            const bool last_of_block = gi == nu - 1;
+            const uint4 v = nextv;
+            if (k + 1 < count) nextv = ldg128_stream(next_unit_ptr());
+            uint32_t halo = prevw;
+            if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {        // the reference kernels' lane-0 deviations
+                if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
+                else if (u > 0) halo = prevw >> 16;
             }
-            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
-            const uint32_t xg = xs + (uint32_t)(gi * GU) * (WPU * 2u);
-            // Both units of the granule are decoded in one straight-line block so that their lookups overlap.
-            // A short granule (last of a block with an odd unit count) decodes zero words against the first
-            // unit's activations and its sum is dropped.
-            uint4 vq[GU];
-#pragma unroll
-            for (int q = 0; q < GU; ++q) {
-                if (TMA) {
-                    vq[q] = q < units ? lds128(stage_base + q * kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
-                } else {
-                    vq[q] = nextv;
-                    if (k + 1 < count) nextv = ldg128_stream(next_unit_ptr());
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < GU; ++q) {
-                const uint4 v = vq[q];
-                const bool valid = q < units;
-                uint32_t halo = prevw;
-                if (!TMA) {     // the reference kernels' lane-0 deviations are only reproduced on this path
-                    const int32_t u = useg0 + gi;
-                    if (p.quirk != RPTC_QUIRK_NONE && (u & 31) == 0) {
-                        if (p.quirk == RPTC_QUIRK_K2_LANE0_CARRY) halo = v.w;
-                        else if (u > 0) halo = prevw >> 16;
-                    }
-                }
-                if (valid) prevw = v.w;
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                const uint32_t xu = xg + (valid ? q : 0) * (WPU * 2u);
-                __half2 hacc[BATCH][4];
-                uint4 xv[BATCH];
-                decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
-                    if ((pi & 3) == 0) {
-#pragma unroll
-                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
-                    }
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) {
-                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                        hacc[b][pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[b][pi & 3]);
-                    }
-                });
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    const __half2 s = __hadd2(__hadd2(hacc[b][0], hacc[b][1]), __hadd2(hacc[b][2], hacc[b][3]));
-                    const float2 f2 = __half22float2(s);
-                    facc[b] += valid ? f2.x + f2.y : 0.f;
-                }
-            }
-            if (TMA) {
-                __syncwarp();                     // every lane has taken its words: the slot can be refilled
-                if (to_issue) {
-                    if (lane == 0) issue_stage(slot);
-                    --to_issue;
-                }
-                if (++slot == kStages) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-            }
+            prevw = v.w;
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t xu = xs + (uint32_t)gi * (WPU * 2u);
+            __half2 hacc[4];
+            uint4 xv;
+            decode_group<CODE, K>(w, halo, lut, [&](int pi, __half2 wp) {
+                if ((pi & 3) == 0) xv = lds128(xu + 4u * pi);
+                const uint32_t xq = (pi & 3) == 0 ? xv.x : (pi & 3) == 1 ? xv.y : (pi & 3) == 2 ? xv.z : xv.w;
+                hacc[pi & 3] = pi < 4 ? __hmul2(wp, u32_as_half2(xq)) : __hfma2(wp, u32_as_half2(xq), hacc[pi & 3]);
+            });
+            const float2 f2 = __half22float2(__hadd2(__hadd2(hacc[0], hacc[1]), __hadd2(hacc[2], hacc[3])));
+            facc += f2.x + f2.y;
             if (last_of_block || k + 1 == count) {
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row, facc[b]);
+                atomicAdd(p.acc + row, facc);
                 fresh = true;
             }
             if (last_of_block) {
@@ -299,18 +182,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             } else {
                 ++gi;
             }
-        }
-        if (TMA && !ok) {
-            // After a failed wait: give the copies still in flight a bounded chance to land before
-            // the shared memory they target is released, then stop.
-            for (int s = 0; s < kStages; ++s) {
-                mbar_wait(bars + 8u * slot, phase, p.status);
-                if (++slot == kStages) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-            }
-            break;
         }
     }
     if (!waited_prior) pdl_wait_prior_grids();
@@ -577,6 +448,299 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
     if (!waited_prior) pdl_wait_prior_grids();
 }
 
+// ---- tensor-core form of the pair kernel ---------------------------------------------------------------
+// Same granules, ring and work split as gemv_pair_kernel, but the products run on mma.sync m16n8k16 (fp16 in,
+// fp32 accumulate) with the decoded weights as the A operand and up to eight activation rows as B:
+//  * lane (g = lane/4, t = lane%4) decodes WORD t of rows g, g+8, g+16, g+24 of the 32-row tile (the tile is
+//    read as four conflict-free 32-bit loads instead of one 128-bit load per row); the 16 stream bits before a
+//    word come from lane t-1 (same unit) or, for t == 0, from lane t+3's word of the unit before -- one shuffle;
+//  * a word holds PW = 16/K weight pairs.  MMA i of a word takes pairs 2i, 2i+1 of rows g / g+8 as a0..a3, so
+//    the k index of a product is (t, pair, element) -- a permutation of the unit's columns that the B operand
+//    follows by reading the activations of columns [t*2*PW, (t+1)*2*PW) of the unit for lane t, batch row g;
+//  * the accumulator fragment of a lane is rows g, g+8 x batch columns 2t, 2t+1: after a run, lanes with
+//    2t < BATCH add their sums to the caller's accumulator.
+// Per 64 weights a lane issues 4 word loads, 12 window instructions, 4 per pair for the lookup, 8 MMAs and 2
+// activation loads, a third less than the HFMA2 form, there is no fp16 partial sum, and BATCH up to 8 costs
+// only the shared memory for x.
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int CODE, int K, int BATCH, int INPUT>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvParams p) {
+    constexpr int WPU = 128 / K;
+    constexpr int PAIRS = WPU / 2;
+    constexpr int PW = 16 / K;                 // weight pairs in a 32-bit word
+    constexpr uint32_t kXPad = 16;             // bytes between activation rows beyond their length: spreads rows over banks
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const uint32_t s0 = smem_addr(smem_raw);
+    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
+    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
+    uint32_t lut_tab, xs;
+    if (CODE == RPTC_CODE_HASH) {
+        lut_tab = kHashLutWindow;
+        xs = kHashLutWindow + kHashLutBytes;
+    } else {
+        lut_tab = s0 + kBarBytes + kRingBytes;
+        xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
+    }
+    if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
+        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        return;
+    }
+    // ---- prologue: nothing here depends on the kernels before this one ----
+    lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
+    pdl_allow_next_grid();
+
+    const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
+    const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
+    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u + kXPad;
+    const int64_t rb_stride = (int64_t)p.n_units << 5;        // 128-bit units between row blocks of the TILED layout
+    const int halo_src = (lane & ~3) | ((t4 + 3) & 3);
+    uint32_t slot = 0, phase = 0;
+    bool ok = true, waited_prior = false;
+
+    for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
+        const int32_t nu = min(p.seg_units, p.n_units - useg0);
+        const uint32_t T = n_rbp * (uint32_t)nu;
+        const uint32_t per = T / GW, extra = T - per * GW;
+        const uint32_t g0 = gw * per + min(gw, extra);
+        const uint32_t count = per + (gw < extra ? 1u : 0u);
+        const uint32_t rbp0 = count ? g0 / (uint32_t)nu : 0u;
+        const int32_t u0 = count ? (int32_t)(g0 - rbp0 * (uint32_t)nu) : 0;
+
+        // fetch cursor (lane 0)
+        uint32_t frbp = rbp0;
+        int32_t fu = u0;
+        const uint4 *fptr = p.codes + (int64_t)(2 * rbp0) * rb_stride + ((int64_t)(useg0 + u0) << 5);
+        auto issue_stage = [&](uint32_t at_slot) {
+            const bool has_b = 2 * frbp + 1 < n_rb;
+            const uint32_t bar = bars + 8u * at_slot, dst = ring + at_slot * kStageBytes;
+            mbar_expect_tx(bar, has_b ? 2 * kUnitBytes : kUnitBytes);
+            bulk_g2s(dst, fptr, kUnitBytes, bar);
+            if (has_b) bulk_g2s(dst + kUnitBytes, fptr + rb_stride, kUnitBytes, bar);
+            fptr += 32;
+            if (++fu == nu) {
+                fu = 0;
+                ++frbp;
+                fptr = p.codes + (int64_t)(2 * frbp) * rb_stride + ((int64_t)useg0 << 5);
+            }
+        };
+        uint32_t to_issue = count;
+        {
+            const uint32_t ahead = min(count, (uint32_t)kStages);
+            if (lane == 0) {
+                uint32_t sl = slot;
+                for (uint32_t k = 0; k < ahead; ++k) {
+                    issue_stage(sl);
+                    if (++sl == kStages) sl = 0;
+                }
+            }
+            to_issue -= ahead;
+        }
+
+        // ---- activations of this column segment -> shared memory ----
+        if (!waited_prior) {
+            pdl_wait_prior_grids();
+            waited_prior = true;
+        }
+        if (useg0 > 0) __syncthreads();
+        if (INPUT != 0) {
+            // one segment by construction (the host refuses wider rows)
+            if (p.in.clear) {
+                float4 *z = reinterpret_cast<float4 *>(p.in.clear);
+                for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.in.clear_count;
+                     i += (int64_t)gridDim.x * kGemvThreads)
+                    z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float *ex = reinterpret_cast<float *>(smem_raw + (xs - s0) + BATCH * x_batch_stride);
+            FinishNormParams q;
+            q.acc = const_cast<float *>(p.in.acc);
+            q.ld_acc = p.in.ld_acc;
+            q.signs_out = static_cast<const __half *>(p.in.signs_out);
+            q.scale_out = p.in.scale_out;
+            q.h = const_cast<__half *>(static_cast<const __half *>(p.in.h_in));
+            q.h_out = static_cast<__half *>(p.in.h_out);
+            q.ld_h = p.in.ld_h;
+            q.w_norm = static_cast<const __half *>(p.in.w_norm);
+            q.eps = p.in.eps;
+            q.signs_in = static_cast<const __half *>(p.in.signs_in);
+            q.transform_in = 1;
+            q.out = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+            q.ld_out = x_batch_stride >> 1;
+            q.n = (int32_t)p.n;
+#pragma unroll 1
+            for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
+        } else {
+            const int64_t col0 = (int64_t)useg0 * WPU;
+            const int pairs = nu * PAIRS;
+            if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+                const int vecs = pairs >> 2;
+#pragma unroll 1
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
+                    const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
+                    for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
+                        uint4 v[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (i0 + k * kGemvThreads < vecs)
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
+                                             "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                             : "memory");
+                    }
+                }
+            } else {
+                for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
+                    const int b = i / pairs, s = i - b * pairs;
+                    int64_t src = (col0 >> 1) + s;
+                    if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- main loop: runs of consecutive units inside one pair of row blocks ----
+        // this lane's activations: batch row g (any valid row when g >= BATCH: those columns of D are not used)
+        const uint32_t x_lane = xs + (uint32_t)(g < BATCH ? g : 0) * x_batch_stride + (uint32_t)t4 * (PW * 4u);
+        uint32_t rbp = rbp0;
+        int32_t u = u0;
+        uint32_t k = 0;
+        while (k < count && ok) {
+            const uint32_t run = min(count - k, (uint32_t)(nu - u));
+            const int64_t row0 = (int64_t)rbp << 6;               // first row of block a; block b starts 32 later
+            const bool has_b = 2 * rbp + 1 < n_rb;
+            // word 3 of the unit before the run, rows g + 8j of both blocks (lanes t == 3 hand it to lanes t == 0)
+            uint32_t pa[4], pb[4];
+            {
+                const int32_t ug = useg0 + u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t r = row0 + g + 8 * j;
+                    if (ug == 0) {
+                        pa[j] = p.carry_in ? __ldg(p.carry_in + r) : 0u;
+                        pb[j] = (p.carry_in && has_b) ? __ldg(p.carry_in + r + 32) : 0u;
+                    } else {
+                        const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride +
+                                                                                   ((int64_t)(ug - 1) << 5) + (g + 8 * j)) + 3;
+                        pa[j] = __ldg(last);
+                        pb[j] = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+                    }
+                }
+            }
+            float ca[2][4], cb[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ca[h][i] = cb[h][i] = 0.f;
+            uint32_t xu = x_lane + (uint32_t)u * (WPU * 2u);
+#pragma unroll 1
+            for (uint32_t jj = 0; jj < run; ++jj) {
+                ok = mbar_wait(bars + 8u * slot, phase, p.status);
+                if (!ok) break;
+                const uint32_t stage_base = ring + slot * kStageBytes + 4u * lane;
+                uint32_t xr[PW];
+                if (PW == 8) {
+                    const uint4 x0 = lds128(xu), x1 = lds128(xu + 16u);
+                    xr[0] = x0.x, xr[1] = x0.y, xr[2] = x0.z, xr[3] = x0.w;
+                    xr[PW - 4] = x1.x, xr[PW - 3] = x1.y, xr[PW - 2] = x1.z, xr[PW - 1] = x1.w;
+                } else {
+                    const uint4 x0 = lds128(xu);
+                    xr[0] = x0.x, xr[1] = x0.y, xr[2] = x0.z, xr[3] = x0.w;
+                }
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        w[j] = lds32(stage_base + (uint32_t)blk * kUnitBytes + 128u * j);      // block b absent: stale bytes, sums dropped
+                    uint32_t R[4][2];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t &prev = blk == 0 ? pa[j] : pb[j];
+                        const uint32_t give = t4 == 3 ? prev : w[j];
+                        const uint32_t before = __shfl_sync(0xFFFFFFFFu, give, halo_src);
+                        prev = w[j];
+                        R[j][0] = __funnelshift_l(w[j], before, 16);
+                        R[j][1] = w[j];
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                        for (int i = 0; i < PW / 2; ++i) {
+                            const uint32_t a0 = half2_as_u32(decode_pair<CODE, K>(R[2 * h], lut, 2 * i));
+                            const uint32_t a1 = half2_as_u32(decode_pair<CODE, K>(R[2 * h + 1], lut, 2 * i));
+                            const uint32_t a2 = half2_as_u32(decode_pair<CODE, K>(R[2 * h], lut, 2 * i + 1));
+                            const uint32_t a3 = half2_as_u32(decode_pair<CODE, K>(R[2 * h + 1], lut, 2 * i + 1));
+                            mma_16816(blk == 0 ? ca[h] : cb[h], a0, a1, a2, a3, xr[2 * i], xr[2 * i + 1]);
+                        }
+                    }
+                }
+                xu += WPU * 2u;
+                __syncwarp();                     // every lane has taken its words: the slot can be refilled
+                if (to_issue) {
+                    if (lane == 0) issue_stage(slot);
+                    --to_issue;
+                }
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            // c[h][0..1]: row g + 16h, batch columns 2t, 2t+1;  c[h][2..3]: row g + 16h + 8
+            if (2 * t4 < BATCH) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int col = 2 * t4 + (e & 1);
+                        if (col < BATCH) {
+                            const int64_t r = row0 + g + 16 * h + 8 * (e >> 1);
+                            atomicAdd(p.acc + (int64_t)col * p.ld_acc + r, ca[h][e]);
+                            if (has_b) atomicAdd(p.acc + (int64_t)col * p.ld_acc + r + 32, cb[h][e]);
+                        }
+                    }
+                }
+            }
+            k += run;
+            u += (int32_t)run;
+            if (u == nu) {
+                u = 0;
+                ++rbp;
+            }
+        }
+        if (!ok) {
+            // After a failed wait: give the copies still in flight a bounded chance to land before
+            // the shared memory they target is released, then stop.
+            for (int s = 0; s < kStages; ++s) {
+                mbar_wait(bars + 8u * slot, phase, p.status);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            break;
+        }
+    }
+    if (!waited_prior) pdl_wait_prior_grids();
+}
+
 __global__ void gemv_finish_kernel(float *__restrict__ acc, int64_t ld_acc, __half *__restrict__ y, int64_t ld_y,
                                    int64_t m, int batch, float scale, int accumulate, int clear) {
     pdl_allow_next_grid();
@@ -594,10 +758,27 @@ __global__ void gemv_finish_kernel(float *__restrict__ acc, int64_t ld_acc, __ha
     if (clear) acc[b * ld_acc + r] = 0.f;
 }
 
-template <int CODE, int K, int BATCH, bool TMA>
+template <int CODE, int K>
 static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemv_kernel<CODE, K, BATCH, TMA>;
+    auto kern = gemv_kernel<CODE, K>;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
+}
+
+// Smallest batch that takes the tensor-core kernel.  At batch 1 the HFMA2 pair kernel is about 8 % faster (fewer
+// dependent steps between a word and its products); from batch 2 on the tensor-core kernel wins, by 2.5x at 8.
+#ifndef RPTC_GEMV_MMA_MIN_BATCH
+#define RPTC_GEMV_MMA_MIN_BATCH 2
+#endif
+
+template <int CODE, int K, int BATCH, int INPUT = 0>
+static int launch_gemv_mma(const GemvParams &p, size_t smem, cudaStream_t stream) {
+    static bool configured = false;
+    auto kern = gemv_mma_kernel<CODE, K, BATCH, INPUT>;
     if (!configured) {
         RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
@@ -607,6 +788,7 @@ static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
 
 template <int CODE, int K, int BATCH, int INPUT = 0>
 static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t stream) {
+    if (BATCH >= RPTC_GEMV_MMA_MIN_BATCH) return launch_gemv_mma<CODE, K, BATCH, INPUT>(p, smem, stream);
     static bool configured = false;
     auto kern = gemv_pair_kernel<CODE, K, BATCH, INPUT>;
     if (!configured) {
@@ -616,26 +798,20 @@ static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t strea
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
-template <int CODE, int K, bool TMA>
-static int dispatch_batch(const GemvParams &p, int batch, size_t smem, cudaStream_t stream) {
-    switch (batch) {
-        case 1: return TMA ? launch_gemv_pair<CODE, K, 1>(p, smem, stream) : launch_gemv<CODE, K, 1, TMA>(p, smem, stream);
-        case 2: return TMA ? launch_gemv_pair<CODE, K, 2>(p, smem, stream) : launch_gemv<CODE, K, 2, TMA>(p, smem, stream);
-        case 4: return launch_gemv<CODE, K, 4, TMA>(p, smem, stream);
-        case 8: return launch_gemv<CODE, K, 8, TMA>(p, smem, stream);
-    }
-    return RPTC_ERR_ARG;
-}
-
 template <int CODE, int K>
-static int dispatch_tma(const GemvParams &p, int batch, bool tma, size_t smem, cudaStream_t stream) {
+static int dispatch(const GemvParams &p, int batch, bool tiled, size_t smem, cudaStream_t stream) {
+    if (!tiled) return batch == 1 && !p.in.h_in ? launch_gemv<CODE, K>(p, smem, stream) : RPTC_ERR_UNSUPPORTED;
     if (p.in.h_in) {
-        if (!tma || batch > 2) return RPTC_ERR_UNSUPPORTED;
+        if (batch > 2) return RPTC_ERR_UNSUPPORTED;
         return batch == 1 ? launch_gemv_pair<CODE, K, 1, 1>(p, smem, stream) : launch_gemv_pair<CODE, K, 2, 1>(p, smem, stream);
     }
-    if (tma) return dispatch_batch<CODE, K, true>(p, batch, smem, stream);
-    if (batch != 1) return RPTC_ERR_UNSUPPORTED;
-    return launch_gemv<CODE, K, 1, false>(p, smem, stream);
+    switch (batch) {
+        case 1: return launch_gemv_pair<CODE, K, 1>(p, smem, stream);
+        case 2: return launch_gemv_pair<CODE, K, 2>(p, smem, stream);
+        case 4: return launch_gemv_mma<CODE, K, 4>(p, smem, stream);
+        case 8: return launch_gemv_mma<CODE, K, 8>(p, smem, stream);
+    }
+    return RPTC_ERR_ARG;
 }
 
 // One launch for batch in {1,2,4,8}.
@@ -679,7 +855,7 @@ static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in
     if (seg < 1) return RPTC_ERR_TOO_LARGE;
     if (seg > p.n_units) seg = p.n_units;
     p.seg_units = (int32_t)seg;
-    size_t smem = fixed + size_t(seg) * unit_x_bytes;
+    size_t smem = fixed + size_t(seg) * unit_x_bytes + size_t(batch) * 16;     // the tensor-core kernel pads each row of x
     if (in) {
         if (seg != p.n_units) return RPTC_ERR_TOO_LARGE;                        // computed activations live in one segment
         smem += 4096 * sizeof(float) + 128;                                     // exchange buffer of the 4096-point transform
@@ -688,15 +864,15 @@ static int gemv_one(const void *codes, const void *lut, const uint32_t *carry_in
 
     switch (f.code) {
         case RPTC_CODE_LUT:
-            if (K == 2) return dispatch_tma<RPTC_CODE_LUT, 2>(p, batch, tma, smem, stream);
-            if (K == 4) return dispatch_tma<RPTC_CODE_LUT, 4>(p, batch, tma, smem, stream);
+            if (K == 2) return dispatch<RPTC_CODE_LUT, 2>(p, batch, tma, smem, stream);
+            if (K == 4) return dispatch<RPTC_CODE_LUT, 4>(p, batch, tma, smem, stream);
             break;
         case RPTC_CODE_HASH:
-            if (K == 2) return dispatch_tma<RPTC_CODE_HASH, 2>(p, batch, tma, smem, stream);
+            if (K == 2) return dispatch<RPTC_CODE_HASH, 2>(p, batch, tma, smem, stream);
             break;
         case RPTC_CODE_LITE:
-            if (K == 2) return dispatch_tma<RPTC_CODE_LITE, 2>(p, batch, tma, smem, stream);
-            if (K == 4) return dispatch_tma<RPTC_CODE_LITE, 4>(p, batch, tma, smem, stream);
+            if (K == 2) return dispatch<RPTC_CODE_LITE, 2>(p, batch, tma, smem, stream);
+            if (K == 4) return dispatch<RPTC_CODE_LITE, 4>(p, batch, tma, smem, stream);
             break;
     }
     return RPTC_ERR_UNSUPPORTED;
