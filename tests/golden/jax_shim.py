@@ -97,6 +97,12 @@ jnp.sqrt = np.sqrt
 jnp.log2 = np.log2
 jnp.bincount = lambda a, length=None: _wrap(np.bincount(a, minlength=length))
 
+jnp.exp = np.exp
+jnp.log = np.log
+jnp.diag = lambda a: _wrap(np.diag(a))
+jnp.sort = lambda a, axis=-1: _wrap(np.sort(a, axis=axis))
+jnp.interp = lambda x, xp, fp: _wrap(np.interp(x, xp, fp).astype(np.float32))
+
 lax = types.ModuleType("jax.lax")
 
 
@@ -142,6 +148,25 @@ jax.jit = lambda f=None, **kw: f if f is not None else (lambda g: g)
 jax.scipy = types.ModuleType("jax.scipy")
 jax.random = types.ModuleType("jax.random")
 optax = types.ModuleType("optax")
+
+
+def _vmap(f, in_axes):
+    """jax.vmap for in_axes made of None and 0, outputs an array or a tuple of arrays."""
+    def mapped(*args):
+        n = next(len(a) for a, ax in zip(args, in_axes) if ax == 0)
+        outs = [f(*[a[i] if ax == 0 else a for a, ax in zip(args, in_axes)]) for i in range(n)]
+        if isinstance(outs[0], tuple):
+            return tuple(_wrap(np.stack([np.asarray(o[k]) for o in outs])) for k in range(len(outs[0])))
+        return _wrap(np.stack([np.asarray(o) for o in outs]))
+    return mapped
+
+
+# Keys are plain integers here; a permutation is numpy's default_rng(key).permutation -- NOT JAX's
+# threefry stream, so only code that is handed the permuted alphabet can be compared with these vectors.
+jax.vmap = _vmap
+jax.random.PRNGKey = lambda seed: int(seed)
+jax.random.fold_in = lambda key, data: int(key) * 1000003 + int(data)
+jax.random.permutation = lambda key, a: _wrap(np.asarray(a)[np.random.default_rng(int(key)).permutation(len(a))])
 
 
 def install() -> None:

@@ -2,7 +2,7 @@
 
     python tests/golden/make_golden.py [reference_root]     (default /root/reference)
 
-The reference's rptc.py and rptc_lite.py are imported unmodified (with tests/golden/jax_shim.py
+The reference's rptc.py, rptc_lite.py and quantize_hf.py are imported unmodified (with tests/golden/jax_shim.py
 standing in for JAX, which is not installed) and their `dequantize` / `quantize` functions are run
 on small seeded inputs.  The outputs are the golden vectors the CPU oracle is pinned against in
 tests/test_oracle.py.  The reference checkout is only needed to REGENERATE the file; the tests read
@@ -92,6 +92,28 @@ def main(ref_root: str) -> None:
     out["encc_symbols"] = np.stack(qs).astype(np.int32)
     out["encc_loss"] = np.array(losses, dtype=np.float64)
     out["encc_decoded"] = np.stack(recs).astype(np.float32)
+
+    # --- the HF driver's layer functions (quantize_hf.py:77-169): factorize, quantize_layer, evaluate_layer
+    sys.modules["rptc"] = rptc                      # quantize_hf.py does `from rptc import quantize, dequantize`
+    hf = _load(os.path.join(ref_root, "quantize_hf.py"), "ref_quantize_hf")
+    W = (rng.standard_normal((24, 40)) * (1 + rng.random((24, 1))) * (0.5 + rng.random((1, 40))) + 0.3 * rng.standard_normal((24, 1))
+         + 0.2 * rng.standard_normal((1, 40))).astype(np.float32)
+    parts = hf.factorize(jnp.array(W))
+    for name, v in zip(("biases_out", "biases_in", "scales_out", "scales_in", "normalized"), parts):
+        out[f"fact_{name}"] = np.asarray(v, dtype=np.float32)
+    out["fact_W"] = W
+    A = rng.standard_normal((40, 64)).astype(np.float32)
+    H = (A @ A.T / 64).astype(np.float32)
+    recon = (W + 0.05 * rng.standard_normal(W.shape)).astype(np.float32)
+    out["eval_H"], out["eval_recon"] = H, recon
+    out["eval_metrics"] = np.array([float(v) for v in hf.evaluate_layer(jnp.array(H), jnp.array(W), jnp.array(recon))], dtype=np.float64)
+    # quantize_layer at a small state width: 256 rows (32 banks x 1 batch x 8 rows), 16 columns, L = 8
+    Wq = (rng.standard_normal((256, 16)) * (0.5 + rng.random((256, 1)))).astype(np.float32)
+    Aq = rng.standard_normal((16, 32)).astype(np.float32)
+    Hq = (Aq @ Aq.T / 32).astype(np.float32)
+    key = 7
+    out["ql_W"], out["ql_H"], out["ql_key"] = Wq, Hq, np.array(key)
+    out["ql_recon"] = np.asarray(hf.quantize_layer(key, jnp.array(Hq), jnp.array(Wq), 8), dtype=np.float32)
 
     path = os.path.join(HERE, "rptc_reference_golden.npz")
     np.savez_compressed(path, **out)
