@@ -221,8 +221,14 @@ int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out, float sca
  * probe the reference's tests call `matvec` (rptc_kernels/tests/test_matvec.py:18, not exported by wrapper.cpp). */
 int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,
                     int batch, rptc_stream_t stream);
-/* out[r] = table[ids[r]], fp16 rows of length n. */
+/* out[r] = table[ids[r]], fp16 rows of length n.  `ids` may live in pinned host memory (read over PCIe by the
+ * kernel: the step's input then needs no copy of its own). */
 int rptc_embed(const void *table, const int32_t *ids, void *out, int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream);
+/* The end of a greedy decode step: next[r] = argmax(logits[r][0:n]) (first maximum), ids[r] = next[r] and pos[r] += 1
+ * when given, and mirror[r] = next[r] when given (pinned host memory: the host reads the token after synchronising
+ * the stream).  logits fp16 [rows][ld]; n even. */
+int rptc_next_token(const void *logits, int64_t ld, int64_t rows, int64_t n, int64_t *next, int32_t *ids, int32_t *pos,
+                    int64_t *mirror, rptc_stream_t stream);
 
 /* --- tensor-parallel decode: output transform + all-reduce + residual add in one kernel over NVLink peer
  * memory (no reference counterpart; the reference has no distributed code) ---

@@ -282,6 +282,51 @@ __global__ void embed_kernel(const __half *__restrict__ table, const int32_t *__
     for (int i = threadIdx.x; i < n / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// Greedy sampling and the bookkeeping that ends a decode step, one CTA per row: next[r] = argmax(logits[r]) (first
+// maximum), fed back into ids[r]; pos[r] += 1; the id is also written to `mirror` when given (a pinned host
+// buffer mapped into the device's address space: the host reads the token after synchronising the stream).
+__global__ void __launch_bounds__(1024) next_token_kernel(const __half *__restrict__ logits, int64_t ld, int n, int64_t *__restrict__ next,
+                                                          int32_t *__restrict__ ids, int32_t *__restrict__ pos, int64_t *__restrict__ mirror) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    const int r = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const __half *row = logits + (int64_t)r * ld;
+    float best = -INFINITY;
+    int at = 0x7FFFFFFF;
+    for (int i = 2 * t; i < n; i += 2 * 1024) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(row + i));
+        if (v.x > best) best = v.x, at = i;
+        if (i + 1 < n && v.y > best) best = v.y, at = i + 1;
+    }
+    auto better = [](float v, int i, float bvv, int bii) { return v > bvv || (v == bvv && i < bii); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, at, o);
+        if (better(ov, oi, best, at)) best = ov, at = oi;
+    }
+    if (lane == 0) bv[warp] = best, bi[warp] = at;
+    __syncthreads();
+    if (warp == 0) {
+        best = bv[lane], at = bi[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, at, o);
+            if (better(ov, oi, best, at)) best = ov, at = oi;
+        }
+        if (lane == 0) {
+            if (at == 0x7FFFFFFF) at = 0;           // a row of NaNs
+            next[r] = at;
+            if (ids) ids[r] = at;
+            if (pos) pos[r] += 1;
+            if (mirror) mirror[r] = at;
+        }
+    }
+}
+
 }  // namespace rptc
 
 using namespace rptc;
@@ -390,4 +435,14 @@ extern "C" int rptc_embed(const void *table, const int32_t *ids, void *out, int6
     if (int e = rptc_check_device()) return e;
     return launch(embed_kernel, dim3((unsigned)rows), dim3(128), 0, static_cast<cudaStream_t>(stream), static_cast<const __half *>(table),
                   ids, static_cast<__half *>(out), ld_out, (int)n);
+}
+
+extern "C" int rptc_next_token(const void *logits, int64_t ld, int64_t rows, int64_t n, int64_t *next, int32_t *ids, int32_t *pos,
+                               int64_t *mirror, rptc_stream_t stream) {
+    if (!logits || !next) return RPTC_ERR_ARG;
+    if (rows <= 0 || rows > 65535 || n <= 0 || n > (int64_t(1) << 30) || (n % 2) || ld < n) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(logits) & 3) || (ld & 1)) return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    return launch(next_token_kernel, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+                  static_cast<const __half *>(logits), ld, (int)n, next, ids, pos, mirror);
 }

@@ -122,6 +122,8 @@ class RPTCLlama:
             from .tp import PeerAllReduce
             self.peer = PeerAllReduce(rows, cfg.hidden, self.blocks[0].o.block_out, tp_rank, tp_world, tp_group)
         self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
+        self.host_ids: torch.Tensor | None = None      # see bind_host_io
+        self.host_next: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
 
@@ -151,7 +153,7 @@ class RPTCLlama:
     def _step_fused(self) -> None:
         cfg = self.cfg
         q_dim = self.heads_l * cfg.head_dim
-        ops.embed(self.embed, self.ids, self.h)
+        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
         b0 = self.blocks[0]
         xt = self.xt[:, : cfg.hidden]
         ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
@@ -182,10 +184,8 @@ class RPTCLlama:
                                          self.xn)
             n_launch += 9
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        torch.argmax(self.logits, dim=1, out=self.next_ids)
-        self.ids.copy_(self.next_ids)
-        self.pos.add_(1)
-        self.launches_per_step = n_launch + 1
+        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self.launches_per_step = n_launch + 2
 
     def _step_glued(self) -> None:
         """qkv matvec -> attention -> o matvec -> gate-up matvec -> SwiGLU -> down matvec.  The two matvecs that
@@ -193,7 +193,7 @@ class RPTCLlama:
         that layer's accumulator themselves.  The residual stream alternates between h and h2; an accumulator
         that every CTA of a launch reads is zeroed by a later launch (`clear`)."""
         cfg, r = self.cfg, self.rows
-        ops.embed(self.embed, self.ids, self.h)
+        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
         for i, b in enumerate(self.blocks):
             prev = self.blocks[i - 1].down if i else None
             ops.gemv_norm_input(b.qkv.codes, b.qkv.lut, self.acc_qkv, b.qkv.out_features, cfg.hidden, self.fmt, r,
@@ -211,15 +211,13 @@ class RPTCLlama:
         last = self.blocks[-1].down
         ops.finish_norm_hadamard(self.acc_h, last.signs_out, last.scale, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        torch.argmax(self.logits, dim=1, out=self.next_ids)
-        self.ids.copy_(self.next_ids)
-        self.pos.add_(1)
-        self.launches_per_step = 6 * len(self.blocks) + 3
+        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self.launches_per_step = 6 * len(self.blocks) + 4
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
         n_launch = 0
-        ops.embed(self.embed, self.ids, self.h)
+        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
         n_launch += 1
         for i, b in enumerate(self.blocks):
             ops.rmsnorm(self.h, b.norm1, self.xn, cfg.rms_eps)
@@ -247,10 +245,8 @@ class RPTCLlama:
             self._finish_row_parallel(b.down)
         ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        torch.argmax(self.logits, dim=1, out=self.next_ids)
-        self.ids.copy_(self.next_ids)
-        self.pos.add_(1)
-        self.launches_per_step = n_launch + 2
+        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self.launches_per_step = n_launch + 3
 
     def _finish_row_parallel(self, lin: RPTCLinear) -> None:
         """h += (sum over tensor-parallel ranks of) this rank's partial output of a row-parallel layer."""
@@ -264,6 +260,16 @@ class RPTCLlama:
         lin.finish(self.acc_h, out=self.partial)
         dist.all_reduce(self.partial, group=self.tp_group)
         self.h.add_(self.partial)
+
+    def bind_host_io(self, host_ids: torch.Tensor | None, host_next: torch.Tensor | None) -> None:
+        """Token ids in and out through pinned host memory without copies of their own: the step's first kernel reads
+        `host_ids` (int32 [rows]) over PCIe, its last kernel writes the chosen ids to `host_next` (int64 [rows]); the host
+        sees them once the stream is synchronised.  Call before `capture`; None restores device-resident feedback."""
+        for t, dt in ((host_ids, torch.int32), (host_next, torch.int64)):
+            if t is not None and (not t.is_pinned() or t.dtype != dt or t.numel() != self.rows):
+                raise ValueError("host buffers must be pinned, int32 ids / int64 next ids, one element per row")
+        self.host_ids, self.host_next = host_ids, host_next
+        self.graph = None
 
     def capture(self, pdl: bool = True) -> None:
         """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""

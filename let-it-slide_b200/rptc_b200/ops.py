@@ -272,6 +272,17 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
+def next_token(logits: torch.Tensor, next_ids: torch.Tensor, ids: torch.Tensor | None = None, pos: torch.Tensor | None = None,
+               mirror: torch.Tensor | None = None) -> None:
+    """Greedy choice + feedback + position bump in one launch (rptc_next_token).  `mirror`: pinned host int64."""
+    rows, n = logits.shape
+    if next_ids.dtype != torch.int64 or (mirror is not None and (mirror.dtype != torch.int64 or not mirror.is_pinned())):
+        raise RuntimeError("next_ids must be int64 and mirror a pinned int64 host tensor")
+    with torch.cuda.device(logits.device):
+        check(lib().rptc_next_token(ptr(logits), _ld(logits, n), rows, n, ptr(next_ids), ptr(ids), ptr(pos), ptr(mirror),
+                                    stream_ptr()), "rptc_next_token")
+
+
 def device_status() -> None:
     """Raises if a kernel reported a timed-out wait since the last call."""
     check(lib().rptc_device_status(), "rptc_device_status")

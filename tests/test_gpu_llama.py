@@ -99,7 +99,7 @@ def test_six_launch_chain_matches_reference_and_separate_glue(rows):
                 # 4096-long dot products of fp16 activations: twice the slack of the small models above
                 assert err <= 2e-2 * ref[:, t].abs().max().item(), (glued, use_graph, t, err)
                 logits[glued, use_graph, t] = got.clone()
-            assert model.launches_per_step == (6 if glued else 8) * cfg.layers + 3
+            assert model.launches_per_step == (6 if glued else 8) * cfg.layers + 4
             # every accumulator is handed back zeroed, whichever launch owned the clearing
             model.graph = None
             ops.embed(model.embed, model.ids, model.h)        # any launch after the step: orders the check below
@@ -109,3 +109,48 @@ def test_six_launch_chain_matches_reference_and_separate_glue(rows):
         scale = ref[:, t].abs().max().item()
         assert (logits[True, True, t] - logits[False, True, t]).abs().max().item() <= 4e-3 * scale
     ops.device_status()
+
+
+def test_next_token_kernel_matches_argmax():
+    from rptc_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(2)
+    logits = torch.randn((3, 32000), device="cuda", generator=g).half()
+    logits[1, 777] = logits[1, 31999] = 9.0                       # a tie: the first maximum wins
+    nxt = torch.zeros(3, dtype=torch.int64, device="cuda")
+    ids = torch.zeros(3, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([4, 5, 6], dtype=torch.int32, device="cuda")
+    mirror = torch.zeros(3, dtype=torch.int64).pin_memory()
+    ops.next_token(logits, nxt, ids, pos, mirror)
+    torch.cuda.synchronize()
+    want = logits.float().argmax(dim=1)
+    want[1] = 777
+    assert torch.equal(nxt, want) and torch.equal(ids.long(), want) and pos.tolist() == [5, 6, 7]
+    assert torch.equal(mirror, want.cpu())
+
+
+def test_host_token_io_generates_the_same_tokens():
+    """Token ids through pinned host memory (read by the first kernel, written by the last) against the
+    device-resident feedback loop."""
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=4, ffn=1024, vocab=1024, max_pos=32, weight_scale=0.05)
+    model = RPTCLlama(cfg, rows=1, seed=4)
+    model.reset(torch.tensor([17]))
+    model.capture()
+    dev_tokens = []
+    for _ in range(8):
+        model.step()
+        dev_tokens.append(int(model.next_ids.item()))
+    host_in = torch.tensor([17], dtype=torch.int32).pin_memory()
+    host_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    model.bind_host_io(host_in, host_out)
+    model.reset()
+    model.capture()
+    host_tokens = []
+    for _ in range(8):
+        model.step()
+        torch.cuda.current_stream().synchronize()
+        host_tokens.append(int(host_out[0]))
+        host_in[0] = host_tokens[-1]
+    assert host_tokens == dev_tokens
+    with pytest.raises(ValueError):
+        model.bind_host_io(torch.zeros(1, dtype=torch.int32), host_out)       # not pinned
