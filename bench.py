@@ -225,6 +225,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     # ---- device-resident decode: token feedback stays on the GPU ----
     sampler = ClockSampler(local)
     barrier()
+    pos_timed = model.pos.clone()          # both timed legs decode the same positions (same attention work)
     sampler.start()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -236,25 +237,38 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     clocks = sampler.stop()
     ms = a.elapsed_time(b)
     # ---- end to end: host token in, host token out, every step ----
-    # The step's first kernel reads the token id from pinned host memory (4 bytes over PCIe) and its last kernel
-    # writes the chosen id to pinned host memory (8 bytes); the host waits for the stream, reads the id and feeds it
-    # back as the next step's input.
-    host_in = torch.zeros(1, dtype=torch.int32).pin_memory()
-    host_out = torch.zeros(1, dtype=torch.int64).pin_memory()
-    host_in[0] = int(model.ids.item())
+    # Single GPU / replicas: the mailbox loop of rptc_b200.llama.HostTokenLoop -- the host posts each step's token id
+    # in pinned memory (8 bytes, read over PCIe by the step's first kernel) and polls the id the step's last kernel
+    # writes back (8 bytes), keeping one graph launch queued ahead.  Tensor parallel: the step's first kernel reads a
+    # pinned int32, the last writes a pinned int64, and the host synchronises the stream every step.
+    first = int(model.ids.item())
     torch.cuda.synchronize()
-    model.bind_host_io(host_in, host_out)
-    model.capture(pdl=True)
-    for _ in range(3):
-        model.step()
-        torch.cuda.current_stream().synchronize()
-        host_in[0] = int(host_out[0])
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        model.step()
-        torch.cuda.current_stream().synchronize()
-        host_in[0] = int(host_out[0])
+    model.pos.copy_(pos_timed - 3)         # three untimed steps, then the positions of the device-resident leg
+    if not tp:
+        loop = model.host_loop()
+        first = loop.run([first], 3)[-1][0]
+        h2d, d2h = 8, 8
+        barrier()
+        t0 = time.perf_counter()
+        loop.run([first], args.steps)
+        torch.cuda.synchronize()
+    else:
+        host_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+        host_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+        host_in[0] = first
+        model.bind_host_io(host_in, host_out)
+        model.capture(pdl=True)
+        h2d, d2h = 4, 8
+        for _ in range(3):
+            model.step()
+            torch.cuda.current_stream().synchronize()
+            host_in[0] = int(host_out[0])
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            model.step()
+            torch.cuda.current_stream().synchronize()
+            host_in[0] = int(host_out[0])
     e2e_s = time.perf_counter() - t0
     barrier()
     ops.device_status()
@@ -276,7 +290,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
                "config": {"workload": args.workload, "code": "HASH S=8 K=2 L=16", "layout": "TILED", "incoherence": "RHT both sides",
                           "prompt": args.prompt, "batch_per_gpu": 1, "allreduce": (args.allreduce if tp else None), "parallelism": (f"tp{world}" if tp else ("replicas" if world > 1 else "single")),
                           "l2": "weights 1.6 GB per token exceed L2", "bytes_per_token": bt},
-               "e2e": {"value": seqs * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 8},
+               "e2e": {"value": seqs * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks, "roofline": roof,
                "cpu_baseline": {"value": 1.0 / cpu_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
                "token_stream_gbs": (bt["packed"] + bt["head"] + bt["kv"]) / (ms / args.steps * 1e-3) / 1e9}

@@ -226,9 +226,17 @@ int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, vo
 int rptc_embed(const void *table, const int32_t *ids, void *out, int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream);
 /* The end of a greedy decode step: next[r] = argmax(logits[r][0:n]) (first maximum), ids[r] = next[r] and pos[r] += 1
  * when given, and mirror[r] = next[r] when given (pinned host memory: the host reads the token after synchronising
- * the stream).  logits fp16 [rows][ld]; n even. */
+ * the stream; see rptc_embed_mailbox for steps_done, NULL otherwise).  logits fp16 [rows][ld]; n even. */
 int rptc_next_token(const void *logits, int64_t ld, int64_t rows, int64_t n, int64_t *next, int32_t *ids, int32_t *pos,
-                    int64_t *mirror, rptc_stream_t stream);
+                    int64_t *mirror, const uint32_t *steps_done, rptc_stream_t stream);
+/* Token ids through a mailbox in pinned host memory, for a host that queues the next step before it knows the
+ * step's token.  slots[r] = (sequence << 32) | id, written by the host with one 8-byte store.  The kernel polls
+ * until every slot carries sequence *steps_done + 1 (device counter, starts at 0), for at most timeout_ms; on
+ * expiry rptc_device_status() reports RPTC_ERR_TIMEOUT and the step runs with the ids it found.  It then stores
+ * the ids to `ids`, sets *steps_done to the sequence number and copies the embedding rows to `out`.  With the same
+ * `steps_done`, rptc_next_token writes mirror[r] = (sequence << 32) | chosen id.  rows <= 64. */
+int rptc_embed_mailbox(const void *table, const uint64_t *slots, uint32_t *steps_done, int32_t *ids, void *out, int64_t ld_out,
+                       int64_t rows, int64_t n, int64_t vocab, int timeout_ms, rptc_stream_t stream);
 
 /* --- tensor-parallel decode: output transform + all-reduce + residual add in one kernel over NVLink peer
  * memory (no reference counterpart; the reference has no distributed code) ---

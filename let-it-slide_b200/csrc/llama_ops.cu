@@ -282,11 +282,56 @@ __global__ void embed_kernel(const __half *__restrict__ table, const int32_t *__
     for (int i = threadIdx.x; i < n / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// The embedding lookup of a step whose token ids come from the host through a mailbox in pinned memory: slot r
+// holds (sequence number << 32) | id.  The launch may be queued before the host knows the id (behind the step that
+// produces it), so one thread polls slot 0.. until every slot shows sequence *steps_done + 1, for at most
+// `timeout_ns`; on expiry it raises the status word and goes on with whatever ids are there, so that the stream
+// always drains.  The sequence number is then published in *steps_done for the step's last kernel.
+__global__ void __launch_bounds__(256) embed_mailbox_kernel(const __half *__restrict__ table, const unsigned long long *slots,
+                                                            uint32_t *steps_done, int32_t *__restrict__ ids, __half *__restrict__ out,
+                                                            int64_t ld_out, int rows, int n, int64_t vocab,
+                                                            unsigned long long timeout_ns, unsigned int *status) {
+    __shared__ int tok[64];
+    pdl_allow_next_grid();
+    pdl_wait_prior_grids();
+    if (threadIdx.x == 0) {
+        const uint32_t want = *steps_done + 1u;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        for (int r = 0; r < rows; ++r) {
+            unsigned long long v;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(slots + r) : "memory");
+                if ((uint32_t)(v >> 32) == want) break;
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                if (now - t0 > timeout_ns) {
+                    atomicExch(status, 3u);
+                    break;
+                }
+                __nanosleep(100);
+            }
+            int64_t id = (int64_t)(uint32_t)v;
+            if (id >= vocab) id = 0;
+            tok[r] = (int)id;
+            ids[r] = (int)id;
+        }
+        *steps_done = want;
+    }
+    __syncthreads();
+    for (int r = 0; r < rows; ++r) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(table + (int64_t)tok[r] * n);
+        uint4 *dst = reinterpret_cast<uint4 *>(out + (int64_t)r * ld_out);
+        for (int i = threadIdx.x; i < n / 8; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 // Greedy sampling and the bookkeeping that ends a decode step, one CTA per row: next[r] = argmax(logits[r]) (first
 // maximum), fed back into ids[r]; pos[r] += 1; the id is also written to `mirror` when given (a pinned host
 // buffer mapped into the device's address space: the host reads the token after synchronising the stream).
 __global__ void __launch_bounds__(1024) next_token_kernel(const __half *__restrict__ logits, int64_t ld, int n, int64_t *__restrict__ next,
-                                                          int32_t *__restrict__ ids, int32_t *__restrict__ pos, int64_t *__restrict__ mirror) {
+                                                          int32_t *__restrict__ ids, int32_t *__restrict__ pos, int64_t *__restrict__ mirror,
+                                                          const uint32_t *__restrict__ steps_done) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     pdl_allow_next_grid();
@@ -322,7 +367,11 @@ __global__ void __launch_bounds__(1024) next_token_kernel(const __half *__restri
             next[r] = at;
             if (ids) ids[r] = at;
             if (pos) pos[r] += 1;
-            if (mirror) mirror[r] = at;
+            if (mirror) {
+                // with a step counter the slot is a mailbox entry: (sequence << 32) | id, one store, pushed to the host
+                mirror[r] = steps_done ? (int64_t)(((unsigned long long)*steps_done << 32) | (unsigned)at) : (int64_t)at;
+                __threadfence_system();
+            }
         }
     }
 }
@@ -438,11 +487,26 @@ extern "C" int rptc_embed(const void *table, const int32_t *ids, void *out, int6
 }
 
 extern "C" int rptc_next_token(const void *logits, int64_t ld, int64_t rows, int64_t n, int64_t *next, int32_t *ids, int32_t *pos,
-                               int64_t *mirror, rptc_stream_t stream) {
+                               int64_t *mirror, const uint32_t *steps_done, rptc_stream_t stream) {
     if (!logits || !next) return RPTC_ERR_ARG;
     if (rows <= 0 || rows > 65535 || n <= 0 || n > (int64_t(1) << 30) || (n % 2) || ld < n) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(logits) & 3) || (ld & 1)) return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
     return launch(next_token_kernel, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream),
-                  static_cast<const __half *>(logits), ld, (int)n, next, ids, pos, mirror);
+                  static_cast<const __half *>(logits), ld, (int)n, next, ids, pos, mirror, steps_done);
+}
+
+extern "C" int rptc_embed_mailbox(const void *table, const uint64_t *slots, uint32_t *steps_done, int32_t *ids, void *out,
+                                  int64_t ld_out, int64_t rows, int64_t n, int64_t vocab, int timeout_ms, rptc_stream_t stream) {
+    if (!table || !slots || !steps_done || !ids || !out) return RPTC_ERR_ARG;
+    if (rows <= 0 || rows > 64 || n <= 0 || (n % 8) || ld_out < n || vocab <= 0 || timeout_ms <= 0) return RPTC_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(table) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (ld_out % 8) ||
+        (reinterpret_cast<uintptr_t>(slots) & 7))
+        return RPTC_ERR_ALIGN;
+    if (int e = rptc_check_device()) return e;
+    unsigned int *status = device_status_word();
+    if (!status) return RPTC_ERR_CUDA;
+    return launch(embed_mailbox_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half *>(table),
+                  reinterpret_cast<const unsigned long long *>(slots), steps_done, ids, static_cast<__half *>(out), ld_out, (int)rows,
+                  (int)n, vocab, (unsigned long long)timeout_ms * 1000000ull, status);
 }

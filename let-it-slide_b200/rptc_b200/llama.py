@@ -124,6 +124,7 @@ class RPTCLlama:
         self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
         self.host_ids: torch.Tensor | None = None      # see bind_host_io
         self.host_next: torch.Tensor | None = None
+        self.mailbox = None                            # see bind_mailbox
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
 
@@ -150,10 +151,23 @@ class RPTCLlama:
         else:
             self._step_unfused()
 
+    def _embed_ids(self) -> None:
+        if self.mailbox is not None:
+            slots_in, _, steps_done, timeout_ms = self.mailbox
+            ops.embed_mailbox(self.embed, slots_in, steps_done, self.ids, self.h, timeout_ms)
+        else:
+            ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
+
+    def _next_token(self) -> None:
+        if self.mailbox is not None:
+            ops.next_token(self.logits, self.next_ids, None, self.pos, self.mailbox[1], self.mailbox[2])
+        else:
+            ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+
     def _step_fused(self) -> None:
         cfg = self.cfg
         q_dim = self.heads_l * cfg.head_dim
-        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
+        self._embed_ids()
         b0 = self.blocks[0]
         xt = self.xt[:, : cfg.hidden]
         ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
@@ -184,7 +198,7 @@ class RPTCLlama:
                                          self.xn)
             n_launch += 9
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self._next_token()
         self.launches_per_step = n_launch + 2
 
     def _step_glued(self) -> None:
@@ -193,7 +207,7 @@ class RPTCLlama:
         that layer's accumulator themselves.  The residual stream alternates between h and h2; an accumulator
         that every CTA of a launch reads is zeroed by a later launch (`clear`)."""
         cfg, r = self.cfg, self.rows
-        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
+        self._embed_ids()
         for i, b in enumerate(self.blocks):
             prev = self.blocks[i - 1].down if i else None
             ops.gemv_norm_input(b.qkv.codes, b.qkv.lut, self.acc_qkv, b.qkv.out_features, cfg.hidden, self.fmt, r,
@@ -211,13 +225,13 @@ class RPTCLlama:
         last = self.blocks[-1].down
         ops.finish_norm_hadamard(self.acc_h, last.signs_out, last.scale, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self._next_token()
         self.launches_per_step = 6 * len(self.blocks) + 4
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
         n_launch = 0
-        ops.embed(self.embed, self.ids if self.host_ids is None else self.host_ids, self.h)
+        self._embed_ids()
         n_launch += 1
         for i, b in enumerate(self.blocks):
             ops.rmsnorm(self.h, b.norm1, self.xn, cfg.rms_eps)
@@ -245,7 +259,7 @@ class RPTCLlama:
             self._finish_row_parallel(b.down)
         ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
-        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, self.host_next)
+        self._next_token()
         self.launches_per_step = n_launch + 3
 
     def _finish_row_parallel(self, lin: RPTCLinear) -> None:
@@ -271,6 +285,18 @@ class RPTCLlama:
         self.host_ids, self.host_next = host_ids, host_next
         self.graph = None
 
+    def bind_mailbox(self, timeout_ms: int = 2000):
+        """Token ids through a mailbox in pinned host memory (see HostTokenLoop): the step's first kernel waits, for at
+        most `timeout_ms`, until the host has posted the ids of this step.  Returns (slots_in, slots_out), pinned
+        int64 [rows] holding (sequence << 32) | id.  Call before `capture`."""
+        slots_in = torch.zeros(self.rows, dtype=torch.int64).pin_memory()
+        slots_out = torch.zeros(self.rows, dtype=torch.int64).pin_memory()
+        steps_done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.host_ids = self.host_next = None
+        self.mailbox = (slots_in, slots_out, steps_done, timeout_ms)
+        self.graph = None
+        return slots_in, slots_out
+
     def capture(self, pdl: bool = True) -> None:
         """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""
         # Programmatic dependent launch is kept off when NCCL kernels sit in the same graph.
@@ -279,7 +305,9 @@ class RPTCLlama:
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
+            mailbox, self.mailbox = self.mailbox, None        # the warm-up step must not wait for a host that is here
             self.step_eager()
+            self.mailbox = mailbox
             self.ids.copy_(ids0)
             self.pos.copy_(pos0)
             torch.cuda.synchronize()
@@ -291,6 +319,9 @@ class RPTCLlama:
         self.ids.copy_(ids0)
         self.pos.copy_(pos0)
         lib().rptc_set_pdl(0)
+
+    def host_loop(self, timeout_ms: int = 2000) -> "HostTokenLoop":
+        return HostTokenLoop(self, timeout_ms)
 
     def step(self) -> None:
         if self.graph is not None:
@@ -354,3 +385,58 @@ class RPTCLlama:
             gu = x @ b.gate_up.effective_weight().t()
             h = h + reduce((torch.nn.functional.silu(gu[..., : self.ffn_l]) * gu[..., self.ffn_l:]) @ b.down.effective_weight().t())
         return rms(h, self.norm_f) @ self.head.float().t()
+
+
+class HostTokenLoop:
+    """Greedy decoding with the host in the loop: every step's input ids come from host memory and every step's
+    chosen ids go back to it, yet the GPU does not idle while the host turns a token around.
+
+    The host keeps one graph launch queued ahead.  The queued step's first kernel waits (bounded) for the mailbox
+    entry that carries its sequence number; the host posts it as soon as it has read the previous step's result from
+    the outgoing mailbox, which the step's last kernel writes.  Per step: one 8-byte store by the host that the GPU
+    reads over PCIe, and one 8-byte store by the GPU that the host polls."""
+
+    def __init__(self, model: RPTCLlama, timeout_ms: int = 2000):
+        import numpy as np
+        self.model = model
+        self.slots_in, self.slots_out = model.bind_mailbox(timeout_ms)
+        self._in, self._out = self.slots_in.numpy(), self.slots_out.numpy()       # views of the pinned buffers
+        self._np = np
+        self.seq = 0                       # steps completed (== the device's counter once the stream drains)
+        self.timeout_s = timeout_ms * 1e-3
+        model.capture(pdl=True)
+
+    def _post(self, seq: int, ids) -> None:
+        for r in range(self.model.rows):
+            self._in[r] = (seq << 32) | int(ids[r])
+
+    def _await(self, seq: int):
+        import time
+        deadline = None
+        out = self._out
+        while True:
+            vals = [int(v) for v in out]
+            if all((v >> 32) == seq for v in vals):
+                return [v & 0xFFFFFFFF for v in vals]
+            if deadline is None:
+                deadline = time.perf_counter() + self.timeout_s + 5.0
+            elif time.perf_counter() > deadline:
+                raise TimeoutError(f"no result for step {seq}")
+
+    def run(self, first_ids, n_steps: int) -> list[list[int]]:
+        """Decodes n_steps tokens per row starting from `first_ids`; returns the chosen ids, one list per step."""
+        model, tokens = self.model, []
+        if n_steps <= 0:
+            return tokens
+        self._post(self.seq + 1, first_ids)
+        model.graph.replay()
+        for i in range(n_steps):
+            more = i + 1 < n_steps
+            if more:
+                model.graph.replay()               # queued behind the running step; waits for its mailbox entry
+            got = self._await(self.seq + 1)
+            self.seq += 1
+            tokens.append(got)
+            if more:
+                self._post(self.seq + 1, got)
+        return tokens

@@ -272,15 +272,26 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
+def embed_mailbox(table: torch.Tensor, slots: torch.Tensor, steps_done: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
+                  timeout_ms: int = 2000) -> None:
+    """Embedding rows of the ids the host posts in `slots` (pinned int64: sequence << 32 | id); waits for them, bounded
+    (rptc_embed_mailbox)."""
+    if not slots.is_pinned() or slots.dtype != torch.int64 or steps_done.dtype != torch.int32:
+        raise RuntimeError("slots must be a pinned int64 host tensor and steps_done an int32 device tensor")
+    with torch.cuda.device(table.device):
+        check(lib().rptc_embed_mailbox(ptr(table), ptr(slots), ptr(steps_done), ptr(ids), ptr(out), _ld(out, table.shape[1]),
+                                       ids.shape[0], table.shape[1], table.shape[0], timeout_ms, stream_ptr()), "rptc_embed_mailbox")
+
+
 def next_token(logits: torch.Tensor, next_ids: torch.Tensor, ids: torch.Tensor | None = None, pos: torch.Tensor | None = None,
-               mirror: torch.Tensor | None = None) -> None:
+               mirror: torch.Tensor | None = None, steps_done: torch.Tensor | None = None) -> None:
     """Greedy choice + feedback + position bump in one launch (rptc_next_token).  `mirror`: pinned host int64."""
     rows, n = logits.shape
     if next_ids.dtype != torch.int64 or (mirror is not None and (mirror.dtype != torch.int64 or not mirror.is_pinned())):
         raise RuntimeError("next_ids must be int64 and mirror a pinned int64 host tensor")
     with torch.cuda.device(logits.device):
         check(lib().rptc_next_token(ptr(logits), _ld(logits, n), rows, n, ptr(next_ids), ptr(ids), ptr(pos), ptr(mirror),
-                                    stream_ptr()), "rptc_next_token")
+                                    ptr(steps_done), stream_ptr()), "rptc_next_token")
 
 
 def device_status() -> None:

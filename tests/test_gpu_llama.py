@@ -38,7 +38,8 @@ def test_rptc_linear_state_dict_round_trip():
     b = RPTCLinear.random(2048, 256, seed=2)
     b.load_state_dict(a.state_dict())
     x = torch.randn((2, 2048), dtype=torch.float16, device="cuda")
-    assert torch.equal(a(x), b(x))
+    # same codes and tables; the matvec's partial sums meet in a different order on every launch
+    torch.testing.assert_close(a(x).float(), b(x).float(), rtol=2e-3, atol=2e-3)
 
 
 @pytest.mark.parametrize("kv_heads", [2, 4])
@@ -154,3 +155,49 @@ def test_host_token_io_generates_the_same_tokens():
     assert host_tokens == dev_tokens
     with pytest.raises(ValueError):
         model.bind_host_io(torch.zeros(1, dtype=torch.int32), host_out)       # not pinned
+
+
+def test_host_token_loop_with_a_launch_queued_ahead():
+    """The mailbox loop (next step queued before its token is known) generates the device-resident loop's tokens."""
+    from rptc_b200 import ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=4, ffn=1024, vocab=1024, max_pos=48, weight_scale=0.05)
+    model = RPTCLlama(cfg, rows=2, seed=4)
+    model.reset(torch.tensor([17, 400]))
+    model.capture()
+    dev_tokens = []
+    for _ in range(12):
+        model.step()
+        dev_tokens.append(model.next_ids.tolist())
+    loop = model.host_loop(timeout_ms=2000)
+    model.reset()
+    first = loop.run([17, 400], 5)
+    rest = loop.run(first[-1], 7)                       # a second call continues the sequence numbers
+    torch.cuda.synchronize()
+    assert first + rest == dev_tokens
+    assert model.pos.tolist() == [12, 12]
+    ops.device_status()
+
+
+def test_mailbox_wait_runs_out_and_reports():
+    """Nobody posts the ids: the kernel gives up after its time limit, the stream drains, the status says so."""
+    import time
+    from rptc_b200 import RPTCError, ops
+    table = torch.randn((64, 256), device="cuda").half()
+    slots = torch.zeros(1, dtype=torch.int64).pin_memory()
+    steps_done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ids = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros((1, 256), dtype=torch.float16, device="cuda")
+    t0 = time.perf_counter()
+    ops.embed_mailbox(table, slots, steps_done, ids, out, timeout_ms=50)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    with pytest.raises(RPTCError):
+        ops.device_status()
+    ops.device_status()                                  # the report clears the word
+    assert torch.equal(out[0], table[0])                 # it went on with the id it found
+    slots[0] = (2 << 32) | 9                             # a posted entry is taken at once
+    ops.embed_mailbox(table, slots, steps_done, ids, out, timeout_ms=50)
+    torch.cuda.synchronize()
+    ops.device_status()
+    assert torch.equal(out[0], table[9]) and int(steps_done) == 2
