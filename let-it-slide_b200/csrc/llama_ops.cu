@@ -86,10 +86,25 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     }
 }
 
-// Single-query attention over the cache: one CTA of 1024 threads per (row, q head); d == 128.
-// Both passes are spread over the 32 warps by position (a warp reads one 256-byte K or V row per step,
-// eight steps in flight), partial outputs meet in shared memory.
-constexpr int kAttnThreads = 1024, kAttnWarps = 32, kAttnUnroll = 8;     // 256 positions in flight per pass
+// Loads that stay where they are written relative to griddepcontrol.wait: the compiler may move a plain load through
+// a const __restrict__ pointer above the wait, which is only right for data no prior grid writes.
+__device__ __forceinline__ uint2 ld_ordered_u64(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_ordered_s32(const void *p) {
+    int v;
+    asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Single-query attention over the cache: one CTA of 512 threads per (row, q head); d == 128.
+// One trip to memory: every warp fetches the K AND V rows of its positions (16 of each in flight, positions
+// interleaved over the 16 warps) before anything that depends on the kernel in front, then keeps a running
+// maximum / sum / weighted V sum of its own (online softmax); the 16 partial states meet in shared memory.
+// Contexts beyond 256 take further chunks of 256 positions through the same registers.
+constexpr int kAttnThreads = 512, kAttnWarps = 16, kAttnUnroll = 16;     // 256 positions in flight
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv,
                                                                   const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
                                                                   const __half *__restrict__ vcache, __half *__restrict__ out,
@@ -98,21 +113,37 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                                                                   int64_t ld_acc, const __half *__restrict__ signs_out,
                                                                   float scale_out, float theta, __half *__restrict__ kcache_w,
                                                                   __half *__restrict__ vcache_w) {
-    extern __shared__ float sc[];       // [max(ctx, 128)] scores, later the 128 outputs
-    __shared__ float red[kAttnWarps];
     __shared__ float part[kAttnWarps][128];
-    __shared__ __align__(16) __half qs[128];
+    __shared__ float pm[kAttnWarps], pl[kAttnWarps];
+    __shared__ float tr[128];
+    __shared__ __align__(16) __half qs[128], ks[128], vs[128];
     pdl_allow_next_grid();
-    pdl_wait_prior_grids();
     constexpr int D = 128;
+    const bool fused = acc != nullptr;
+    // Without the fused front end q and the newest K/V row come from the kernel in front: wait for it first.
+    // With it, the rows already in the cache and the position were written at least a step ago.
+    if (!fused) pdl_wait_prior_grids();
     const int row = blockIdx.y, head = blockIdx.x, kvh = head / (hq / hkv);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int ctx = pos[row] + 1;
-    const __half *q = qkv + (int64_t)row * ld_qkv + (int64_t)head * D;
-    if (acc) {
+    const int ctx = ld_ordered_s32(pos + row) + 1;
+    const int n_old = fused ? ctx - 1 : ctx;                     // rows to read from the cache
+    const int64_t stride = (int64_t)hkv * D;
+    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
+    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
+    uint2 kk[kAttnUnroll], vv[kAttnUnroll];
+#pragma unroll
+    for (int u = 0; u < kAttnUnroll; ++u) {
+        const int j = warp + u * kAttnWarps;
+        kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
+        vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
+    }
+    uint2 qraw = make_uint2(0u, 0u);
+    if (!fused) qraw = ld_ordered_u64(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 4 * lane);
+    if (fused) {
         // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv
         // layer's accumulator -- per-head 128-wide output transform, fp16 rounding, rotary embedding -- appends
-        // k and v to the caches and keeps q in shared memory.  Sixteen threads x eight values per vector.
+        // k and v to the caches and keeps all three in shared memory.  Sixteen threads x eight values per vector.
+        pdl_wait_prior_grids();
         if (warp < 2) {
             const int grp = t >> 4, i8 = (t & 15) * 8;              // 0: q, 1: k, 2: v, 3: idle half warp
             const int col = (grp == 0 ? head : grp == 1 ? hq + kvh : hq + hkv + kvh) * D + i8;
@@ -138,96 +169,91 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                 sincosf(ps * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &sn, &cs);
                 o[i] = grp == 2 ? v[i] : (upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn);
             }
-            if (grp == 0) store8_f16(qs + i8, o);
-            else if (grp == 1) store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
-            else if (grp == 2) store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
-        }
-        __syncthreads();       // q is in shared memory; this CTA's cache writes are visible to all its threads
-        q = qs;
-    }
-    const float2 q01 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane]);
-    const float2 q23 = __half22float2(reinterpret_cast<const __half2 *>(q)[2 * lane + 1]);
-    const int64_t stride = (int64_t)hkv * D;
-    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
-    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
-    // ---- scores ----
-    float mx = -1e30f;
-    for (int j0 = warp; j0 < ctx; j0 += kAttnUnroll * kAttnWarps) {
-        uint2 kk[kAttnUnroll];
-#pragma unroll
-        for (int u = 0; u < kAttnUnroll; ++u) {
-            const int j = j0 + u * kAttnWarps;
-            kk[u] = j < ctx ? *reinterpret_cast<const uint2 *>(kb + j * stride) : make_uint2(0u, 0u);
-        }
-#pragma unroll
-        for (int u = 0; u < kAttnUnroll; ++u) {
-            const int j = j0 + u * kAttnWarps;
-            const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
-            float s = q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
-            s = warp_sum(s) * scale;
-            if (j < ctx) {
-                if (lane == 0) sc[j] = s;
-                mx = fmaxf(mx, s);
+            if (grp == 0) {
+                store8_f16(qs + i8, o);
+            } else if (grp == 1) {
+                store8_f16(ks + i8, o);
+                store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+            } else if (grp == 2) {
+                store8_f16(vs + i8, o);
+                store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
             }
         }
+        __syncthreads();
+        qraw = *reinterpret_cast<const uint2 *>(qs + 4 * lane);
     }
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = red[0];
+    const float2 q01 = __half22float2(u32_as_half2(qraw.x)), q23 = __half22float2(u32_as_half2(qraw.y));
+    // ---- this warp's positions: running maximum m, sum l and weighted V sum a (dims 4*lane .. 4*lane+3) ----
+    float m = -1e30f, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    auto fold = [&](float s, bool valid, uint2 vraw) {       // one position into the running state
+        const float m_new = valid ? fmaxf(m, s) : m;
+        const float corr = __expf(m - m_new), p = valid ? __expf(s - m_new) : 0.f;
+        const float2 v01 = __half22float2(u32_as_half2(vraw.x)), v23 = __half22float2(u32_as_half2(vraw.y));
+        l = l * corr + p;
+        a0 = a0 * corr + p * v01.x, a1 = a1 * corr + p * v01.y, a2 = a2 * corr + p * v23.x, a3 = a3 * corr + p * v23.y;
+        m = m_new;
+    };
+    for (int j0 = warp; j0 < n_old || j0 == warp; j0 += kAttnUnroll * kAttnWarps) {
+        if (j0 != warp) {
 #pragma unroll
-    for (int w = 1; w < kAttnWarps; ++w) mx = fmaxf(mx, red[w]);
-    __syncthreads();
-    float sum = 0.f;
-    for (int j = t; j < ctx; j += kAttnThreads) {
-        const float e = __expf(sc[j] - mx);
-        sc[j] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    if (lane == 0) red[warp] = sum;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) tot += red[w];
-    const float inv = 1.f / tot;
-    // ---- weighted sum of V: lane owns dims 4*lane .. 4*lane+3 of its warp's positions ----
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    for (int j0 = warp; j0 < ctx; j0 += kAttnUnroll * kAttnWarps) {
-        uint2 vv[kAttnUnroll];
-        float pw[kAttnUnroll];
-#pragma unroll
-        for (int u = 0; u < kAttnUnroll; ++u) {
-            const int j = j0 + u * kAttnWarps;
-            vv[u] = j < ctx ? *reinterpret_cast<const uint2 *>(vb + j * stride) : make_uint2(0u, 0u);
-            pw[u] = j < ctx ? sc[j] : 0.f;
+            for (int u = 0; u < kAttnUnroll; ++u) {
+                const int j = j0 + u * kAttnWarps;
+                kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
+                vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
+            }
         }
+        float s[kAttnUnroll];
+        float mc = -1e30f;
 #pragma unroll
         for (int u = 0; u < kAttnUnroll; ++u) {
+            const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
+            s[u] = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale;
+            if (j0 + u * kAttnWarps < n_old) mc = fmaxf(mc, s[u]);
+        }
+        // one rescale per chunk: the chunk's maximum first, then plain accumulation
+        const float m_new = fmaxf(m, mc), corr = __expf(m - m_new);
+        l *= corr, a0 *= corr, a1 *= corr, a2 *= corr, a3 *= corr;
+        m = m_new;
+#pragma unroll
+        for (int u = 0; u < kAttnUnroll; ++u) {
+            const float p = (j0 + u * kAttnWarps < n_old) ? __expf(s[u] - m) : 0.f;
             const float2 v01 = __half22float2(u32_as_half2(vv[u].x)), v23 = __half22float2(u32_as_half2(vv[u].y));
-            a0 += pw[u] * v01.x, a1 += pw[u] * v01.y, a2 += pw[u] * v23.x, a3 += pw[u] * v23.y;
+            l += p;
+            a0 += p * v01.x, a1 += p * v01.y, a2 += p * v23.x, a3 += p * v23.y;
         }
+    }
+    if (fused && warp == 0) {      // the position made above, from shared memory
+        const uint2 kr = *reinterpret_cast<const uint2 *>(ks + 4 * lane), vr = *reinterpret_cast<const uint2 *>(vs + 4 * lane);
+        const float2 k01 = __half22float2(u32_as_half2(kr.x)), k23 = __half22float2(u32_as_half2(kr.y));
+        fold(warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale, true, vr);
     }
     *reinterpret_cast<float4 *>(&part[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+    if (lane == 0) pm[warp] = m, pl[warp] = l;
     __syncthreads();
     if (t < D) {
-        float acc = 0.f;
+        float mx = pm[0];
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) acc += part[w][t];
-        float o = __half2float(__float2half_rn(acc * inv));            // the attention output in fp16
+        for (int w = 1; w < kAttnWarps; ++w) mx = fmaxf(mx, pm[w]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float e = __expf(pm[w] - mx);
+            num += e * part[w][t];
+            den += e * pl[w];
+        }
+        float o = __half2float(__float2half_rn(num / den));            // the attention output in fp16
         if (signs_in) {
             // input-side transform of the output projection, one 128-wide Hadamard block per head:
             // o <- H_128(s * o) / sqrt(128); thread t holds element t (threads 0..127 = warps 0..3)
             o *= __half2float(signs_in[head * D + t]);
 #pragma unroll
-            for (int m = 1; m < 32; m <<= 1) {
-                const float other = __shfl_xor_sync(0xFFFFFFFFu, o, m);
-                o = (lane & m) ? other - o : o + other;
+            for (int mm = 1; mm < 32; mm <<= 1) {
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, o, mm);
+                o = (lane & mm) ? other - o : o + other;
             }
-            sc[t] = o;                                                   // scores are no longer needed
-        }
-        if (signs_in) {
+            tr[t] = o;
             asm volatile("bar.sync 1, 128;" ::: "memory");             // only the four warps that hold outputs
-            const float e0 = sc[lane], e1 = sc[32 + lane], e2 = sc[64 + lane], e3 = sc[96 + lane];
+            const float e0 = tr[lane], e1 = tr[32 + lane], e2 = tr[64 + lane], e3 = tr[96 + lane];
             const float b0 = e0 + e1, b1 = e0 - e1, b2 = e2 + e3, b3 = e2 - e3;
             const float c = warp == 0 ? b0 + b2 : warp == 1 ? b1 + b3 : warp == 2 ? b0 - b2 : b1 - b3;
             o = c * 0.08838834764831845f;
@@ -409,13 +435,7 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
     if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || max_pos <= 0 || max_pos > 32768) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(kcache) & 7) || (ld_qkv & 3)) return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
-    static bool configured = false;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
-        configured = true;
-    }
-    const size_t smem = (size_t)(max_pos < 128 ? 128 : max_pos) * 4;
-    return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), smem, static_cast<cudaStream_t>(stream),
+    return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
                   static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in),
                   static_cast<float *>(nullptr), (int64_t)0, static_cast<const __half *>(nullptr), 0.f, 0.f,
@@ -433,13 +453,7 @@ extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *sign
         (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (ld_acc % 4))
         return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
-    static bool configured = false;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4));
-        configured = true;
-    }
-    const size_t smem = (size_t)(max_pos < 128 ? 128 : max_pos) * 4;
-    return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), smem, static_cast<cudaStream_t>(stream),
+    return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(nullptr), (int64_t)0, pos, static_cast<const __half *>(kcache),
                   static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, heads, max_pos, 0.08838834764831845f,
                   static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, theta,
