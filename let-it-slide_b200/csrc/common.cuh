@@ -121,6 +121,23 @@ __device__ __forceinline__ uint4 ldg128_stream(const void *p) {
                  : "l"(p));
     return v;
 }
+// Loads of data that a prior grid writes.  Volatile asm with a memory clobber: they stay behind griddepcontrol.wait,
+// whereas the compiler may hoist a plain (or __ldg) load through a const __restrict__ pointer above the wait.
+__device__ __forceinline__ uint4 ld_ordered_u128(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_ordered_u64(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_ordered_u32(const void *p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 __device__ __forceinline__ uint32_t half2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 

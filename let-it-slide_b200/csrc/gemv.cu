@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             for (int i = threadIdx.x; i < pairs; i += kGemvThreads) {
                 int64_t src = (col0 >> 1) + i;
                 if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x) + src);
+                const uint32_t v = ld_ordered_u32(reinterpret_cast<const uint32_t *>(p.x) + src);
                 asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + 4u * i), "r"(v) : "memory");
             }
         }
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                         uint4 v[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
+                            if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs)
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                     const int b = i / pairs, s = i - b * pairs;
                     int64_t src = (col0 >> 1) + s;
                     if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                    const uint32_t v = ld_ordered_u32(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
                 }
             }
@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
                         uint4 v[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs) v[k] = __ldg(src + i0 + k * kGemvThreads);
+                            if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs)
@@ -609,7 +609,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
                     const int b = i / pairs, s = i - b * pairs;
                     int64_t src = (col0 >> 1) + s;
                     if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                    const uint32_t v = ld_ordered_u32(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
                 }
             }

@@ -86,19 +86,6 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     }
 }
 
-// Loads that stay where they are written relative to griddepcontrol.wait: the compiler may move a plain load through
-// a const __restrict__ pointer above the wait, which is only right for data no prior grid writes.
-__device__ __forceinline__ uint2 ld_ordered_u64(const void *p) {
-    uint2 v;
-    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ int ld_ordered_s32(const void *p) {
-    int v;
-    asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 // Single-query attention over the cache: one CTA of 512 threads per (row, q head); d == 128.
 // One trip to memory: every warp fetches the K AND V rows of its positions (16 of each in flight, positions
 // interleaved over the 16 warps) before anything that depends on the kernel in front, then keeps a running
@@ -125,7 +112,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     if (!fused) pdl_wait_prior_grids();
     const int row = blockIdx.y, head = blockIdx.x, kvh = head / (hq / hkv);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int ctx = ld_ordered_s32(pos + row) + 1;
+    const int ctx = (int)ld_ordered_u32(pos + row) + 1;
     const int n_old = fused ? ctx - 1 : ctx;                     // rows to read from the cache
     const int64_t stride = (int64_t)hkv * D;
     const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
