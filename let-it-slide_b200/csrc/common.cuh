@@ -235,6 +235,49 @@ __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restric
     }
 }
 
+// The same fill in two steps, for kernels that have something to wait for in between (the table's trip through L2
+// then overlaps the wait): `begin` issues the codebook loads and `end` writes the rows.  Only the one-pass case (HASH,
+// or LITE with at most four rows per thread) is split; anything else is filled completely by `begin`.
+struct LutPending {
+    uint32_t v[4];
+    bool deferred;
+};
+template <int CODE>
+__device__ __forceinline__ LutPending lut_fill_begin(uint32_t table, const __half *__restrict__ g, int L, int S) {
+    LutPending pend;
+    const int rows = (CODE == RPTC_CODE_HASH) ? 256 : (1 << S);
+    pend.deferred = CODE != RPTC_CODE_LUT && rows * 8 <= 4 * (int)blockDim.x;
+    if (!pend.deferred) {
+        lut_fill<CODE>(table, g, L, S);
+        return pend;
+    }
+    const int smask = (1 << S) - 1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        pend.v[k] = 0u;
+        if (i < rows * 8)      // volatile: stays in front of the wait that follows
+            asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(pend.v[k]) : "l"(reinterpret_cast<const uint32_t *>(g) + ((i >> 3) & smask)));
+    }
+    return pend;
+}
+template <int CODE>
+__device__ __forceinline__ void lut_fill_end(uint32_t table, const LutPending &pend, int S) {
+    if (!pend.deferred) return;
+    const int rows = (CODE == RPTC_CODE_HASH) ? 256 : (1 << S);
+    const uint32_t row_bytes = (CODE == RPTC_CODE_HASH) ? 256u : 128u;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < rows * 8) {
+            const int e = i >> 3;
+            uint32_t x = pend.v[k];
+            if (CODE == RPTC_CODE_HASH) x = (x & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(table + row_bytes * e + 16u * (i & 7)), "r"(x) : "memory");
+        }
+    }
+}
+
 template <int CODE>
 __device__ __forceinline__ Lut<CODE> lut_view(uint32_t table, int L, int S) {
     const uint32_t lane4 = 4u * (threadIdx.x & 31);

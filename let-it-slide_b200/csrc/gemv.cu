@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         return;
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
-    lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
+    const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
@@ -279,6 +279,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
+            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);      // the codebook loads were issued before the wait
         }
         if (useg0 > 0) __syncthreads();
         if (INPUT != 0) {
@@ -493,7 +494,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         return;
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
-    lut_fill<CODE>(lut_tab, p.lut, p.L, p.S);
+    const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
@@ -554,6 +555,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
+            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);      // the codebook loads were issued before the wait
         }
         if (useg0 > 0) __syncthreads();
         if (INPUT != 0) {
