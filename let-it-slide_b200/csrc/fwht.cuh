@@ -125,7 +125,7 @@ __device__ __forceinline__ float block_sum(float v, float *red) {      // red: >
 // (1) optional: h = residual + s_out * H(acc) * scale   (the output side of a row's previous layer; acc cleared)
 // (2) xn = rmsnorm(h) * w_norm
 // (3) out = H(s_in * xn) * norm   (the input side of the next layer), or out = xn when no transform is wanted.
-// One CTA per row; the row must be a single Hadamard block (n == block <= 4096).
+// One CTA per row: n / 8 threads; the row is one Hadamard block (n <= 4096) or two of 4096 (n = 8192).
 struct FinishNormParams {
     float *acc;                  // fp32 [rows][ld_acc] or NULL (then h is read as it is)
     int64_t ld_acc;
@@ -140,7 +140,8 @@ struct FinishNormParams {
     int transform_in;            // apply the input-side Hadamard transform to the normalised row
     __half *out;                 // fp16 [rows][ld_out]
     int64_t ld_out;
-    int32_t n;
+    int32_t n;                   // row length = 8 x threads of the CTA
+    int32_t block;               // Hadamard block of both transforms (n, or 4096 when n = 8192)
 };
 
 // One row; called by all n/8 threads of a CTA.  `owner`: this CTA is the one that clears the accumulator behind
@@ -150,7 +151,7 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
                                                 bool write_h) {
     const int t = threadIdx.x;
     const int col = 8 * t;
-    const float hn = hadamard_norm_dev(p.n);
+    const float hn = hadamard_norm_dev(p.block);
     // every global load is issued before the first dependent use: one memory round trip for the kernel
     const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
     const uint4 raw_h = clear_acc ? *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col)
@@ -161,7 +162,7 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
     if (p.acc) {
         if (clear_acc) load8_f32(p.acc + row * p.ld_acc + col, v, true);
         else load8_f32_cg(p.acc + row * p.ld_acc + col, v);
-        fwht8(v, p.n, ex);
+        fwht8(v, p.block, ex);
         unpack8(raw_so, sg);
         float r[8];
         unpack8(raw_h, r);
@@ -187,7 +188,7 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
         unpack8(raw_si, sg);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= sg[i];
-        fwht8(v, p.n, ex);
+        fwht8(v, p.block, ex);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= hn;
     }

@@ -308,6 +308,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 q.out = x_sm;
                 q.ld_out = x_batch_stride >> 1;
                 q.n = (int32_t)p.n;
+                q.block = (int32_t)p.n;
 #pragma unroll 1
                 for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
             }
@@ -582,6 +583,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             q.out = reinterpret_cast<__half *>(smem_raw + (xs - s0));
             q.ld_out = x_batch_stride >> 1;
             q.n = (int32_t)p.n;
+            q.block = (int32_t)p.n;
 #pragma unroll 1
             for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
         } else {

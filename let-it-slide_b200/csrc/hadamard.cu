@@ -66,9 +66,10 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
 // They exist to shorten the chain of small dependent launches between two fused dequant-GEMVs.
 
 
-__global__ void __launch_bounds__(512) finish_norm_hadamard_kernel(const FinishNormParams p) {
-    __shared__ float ex[4096];
-    __shared__ float red[20];
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) finish_norm_hadamard_kernel(const FinishNormParams p) {
+    __shared__ float ex[8 * THREADS];
+    __shared__ float red[36];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     finish_norm_row(p, blockIdx.x, ex, red, true, true);
@@ -205,7 +206,7 @@ extern "C" int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void 
                                          const void *w_norm, float eps, const void *signs_in, int transform_in, void *out,
                                          int64_t ld_out, int64_t rows, int64_t n, rptc_stream_t stream) {
     if (!h || !w_norm || !out) return RPTC_ERR_ARG;
-    if (n < 256 || n > 4096 || (n & (n - 1))) return RPTC_ERR_UNSUPPORTED;      // one Hadamard block per row
+    if (n < 256 || n > 8192 || (n & (n - 1))) return RPTC_ERR_UNSUPPORTED;      // one Hadamard block per row, or two of 4096
     if (rows <= 0 || ld_h < n || ld_out < n || (acc && ld_acc < n)) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(w_norm) & 15) ||
         (acc && (reinterpret_cast<uintptr_t>(acc) & 15)) || (ld_h % 8) || (ld_out % 8) || (ld_acc % 4))
@@ -226,7 +227,10 @@ extern "C" int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void 
     p.out = static_cast<__half *>(out);
     p.ld_out = ld_out;
     p.n = (int32_t)n;
-    return launch(finish_norm_hadamard_kernel, dim3((unsigned)rows), dim3((unsigned)(n / 8)), 0, static_cast<cudaStream_t>(stream), p);
+    p.block = (int32_t)(n > 4096 ? 4096 : n);
+    if (n > 4096)
+        return launch(finish_norm_hadamard_kernel<1024>, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), p);
+    return launch(finish_norm_hadamard_kernel<512>, dim3((unsigned)rows), dim3((unsigned)(n / 8)), 0, static_cast<cudaStream_t>(stream), p);
 }
 
 extern "C" int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *q_out, int64_t ld_q,

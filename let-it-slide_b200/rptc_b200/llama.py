@@ -122,6 +122,7 @@ class RPTCLlama:
             from .tp import PeerAllReduce
             self.peer = PeerAllReduce(rows, cfg.hidden, self.blocks[0].o.block_out, tp_rank, tp_world, tp_group)
         self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
+        self.fused_tp = True        # False: the 15-launch chain under tensor parallelism
         self.host_ids: torch.Tensor | None = None      # see bind_host_io
         self.host_next: torch.Tensor | None = None
         self.mailbox = None                            # see bind_mailbox
@@ -143,9 +144,18 @@ class RPTCLlama:
         return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and self.heads_l == self.kv_heads_l
                 and b.qkv.block_out == 128 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
 
+    def _fusable_tp(self) -> bool:
+        """The tensor-parallel short chain (11 launches per block with the peer all-reduce): incoherent layers, hidden a
+        power of two up to 8192 (one or two 4096-point Hadamard blocks), 128-wide heads."""
+        n = self.cfg.hidden
+        return (self.tp_world > 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 8192
+                and self.cfg.head_dim == 128 and self.blocks[0].qkv.block_out >= 128 and self.fused_tp)
+
     def step_eager(self) -> None:
         if self._glueable():
             self._step_glued()
+        elif self._fusable_tp():
+            self._step_fused_tp()
         elif self._fusable():
             self._step_fused()
         else:
@@ -228,6 +238,39 @@ class RPTCLlama:
         self._next_token()
         self.launches_per_step = 6 * len(self.blocks) + 4
 
+    def _step_fused_tp(self) -> None:
+        """Tensor-parallel decode step with the glue fused as far as the all-reduce allows: RMSNorm + input transform in
+        one kernel, q/k/v finish + RoPE + KV append in one, the output projection's input transform inside attention,
+        the gated-MLP middle in one; the row-parallel layers end in the all-reduce (+ transform + residual)."""
+        cfg = self.cfg
+        xt = self.xt[:, : cfg.hidden]
+        self._embed_ids()
+        b0 = self.blocks[0]
+        ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
+        per_reduce = 1 if self.peer is not None else 3
+        for i, b in enumerate(self.blocks):
+            b.qkv.matvec_acc(xt, self.acc_qkv)
+            ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                           self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                            cfg.head_dim, signs_in=b.o.signs_in)
+            b.o.matvec_acc(self.attn, self.acc_h)
+            self._finish_row_parallel(b.o)
+            ops.finish_norm_hadamard(None, None, 1.0, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in, True, xt)
+            b.gate_up.matvec_acc(xt, self.acc_gu)
+            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                b.gate_up.scale, 1.0, clear=True)
+            b.down.matvec_acc(self.mlp, self.acc_h)
+            self._finish_row_parallel(b.down)
+            if i + 1 < len(self.blocks):
+                nb = self.blocks[i + 1]
+                ops.finish_norm_hadamard(None, None, 1.0, self.h, nb.norm1, cfg.rms_eps, nb.qkv.signs_in, True, xt)
+            else:
+                ops.finish_norm_hadamard(None, None, 1.0, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        self._next_token()
+        self.launches_per_step = (9 + 2 * per_reduce) * len(self.blocks) + 4
+
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
         n_launch = 0
@@ -299,8 +342,9 @@ class RPTCLlama:
 
     def capture(self, pdl: bool = True) -> None:
         """Captures one decode step into a CUDA graph (after a warm-up step that is then undone)."""
-        # Programmatic dependent launch is kept off when NCCL kernels sit in the same graph.
-        lib().rptc_set_pdl(1 if (pdl and self.tp_world == 1) else 0)
+        # Programmatic dependent launch is kept off when NCCL kernels sit in the same graph; the peer all-reduce is one
+        # of this library's kernels and waits for the grid in front like the others.
+        lib().rptc_set_pdl(1 if (pdl and (self.tp_world == 1 or self.peer is not None)) else 0)
         ids0, pos0 = self.ids.clone(), self.pos.clone()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())

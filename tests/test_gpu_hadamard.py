@@ -42,14 +42,15 @@ def test_hadamard_fp32_in_clear_and_inverse():
 def _glue_reference(acc, s_out, scale, h, w_norm, eps, s_in, transform_in):
     """fp64 statement of the decoder-block glue: residual update, RMSNorm, next layer's input transform."""
     n = acc.shape[-1]
-    h_new = h.astype(np.float64) + o.rht(acc, s_out, n, transpose=True) * scale
+    block = min(n, 4096)                                     # 8192-wide rows are two blocks of 4096
+    h_new = h.astype(np.float64) + o.rht(acc, s_out, block, transpose=True) * scale
     h16 = h_new.astype(np.float16).astype(np.float64)
     xn = h16 / np.sqrt((h16 ** 2).mean(-1, keepdims=True) + eps) * w_norm.astype(np.float64)
     xn = xn.astype(np.float16).astype(np.float64)
-    return h_new, (o.rht(xn, s_in, n) if transform_in else xn)
+    return h_new, (o.rht(xn, s_in, block) if transform_in else xn)
 
 
-@pytest.mark.parametrize("n", [256, 1024, 4096])
+@pytest.mark.parametrize("n", [256, 1024, 4096, 8192])
 @pytest.mark.parametrize("transform_in", [True, False])
 def test_finish_norm_hadamard(n, transform_in):
     from rptc_b200 import ops

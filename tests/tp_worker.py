@@ -22,6 +22,8 @@ def main():
     rows, T = 2, 6
     use_peer = len(sys.argv) > 4 and sys.argv[4] == "peer"
     model = RPTCLlama(cfg, rows=rows, seed=3, tp_world=world, tp_rank=rank, peer_allreduce=use_peer)
+    model.fused_tp = not (len(sys.argv) > 5 and sys.argv[5] == "unfused")
+    assert model._fusable_tp() == model.fused_tp
     g = torch.Generator(device="cuda").manual_seed(5)                    # same tokens on every rank
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
