@@ -388,6 +388,56 @@ class RPTCLlama:
 
     # -- dense fp32 reference of the same model (decode weights with the GPU's bit-exact decompress) --------
     @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Pushes a whole prompt `tokens` [rows, T] through the network in one pass: every block linear runs as the
+        fused dequant-GEMM on the tensor cores (rows x T tokens at once), the KV caches are filled for positions
+        0..T-1, `pos` is set to T and `ids` to the greedy choice after the last prompt token.  Returns the logits of
+        the last position, fp16 [rows, vocab].  Attention over the prompt is torch's scaled_dot_product_attention
+        and the elementwise steps between the GEMMs are torch ops; decoding continues with `step`."""
+        cfg = self.cfg
+        R, T = tokens.shape
+        if R != self.rows or T > cfg.max_pos:
+            raise ValueError("tokens must be [rows, T] with T <= max_pos")
+        D, half = cfg.head_dim, cfg.head_dim // 2
+        q_dim, kv_dim = self.heads_l * D, self.kv_heads_l * D
+        h = self.embed[tokens.long()].reshape(R * T, cfg.hidden)                     # fp16 residual stream
+        inv = cfg.rope_theta ** (-torch.arange(half, device=self.device, dtype=torch.float32) * 2 / D)
+        ang = torch.arange(T, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
+        cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+
+        def rope(x):                                                                # [R, T, heads, D], rotate-half pairs
+            a, b = x[..., :half].float(), x[..., half:].float()
+            return torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1).to(torch.float16)
+
+        def reduce(y):
+            if self.tp_world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(y, group=self.tp_group)
+            return y
+
+        xn = torch.empty_like(h)
+        for i, b in enumerate(self.blocks):
+            ops.rmsnorm(h, b.norm1, xn, cfg.rms_eps)
+            qkv = b.qkv(xn).reshape(R, T, -1)
+            q = rope(qkv[..., :q_dim].reshape(R, T, self.heads_l, D))
+            k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(R, T, self.kv_heads_l, D))
+            v = qkv[..., q_dim + kv_dim:].reshape(R, T, self.kv_heads_l, D)
+            self.kcache[i][:, :T] = k
+            self.vcache[i][:, :T] = v
+            att = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                                   is_causal=True, enable_gqa=self.heads_l != self.kv_heads_l)
+            h = h + reduce(b.o(att.transpose(1, 2).reshape(R * T, q_dim)))
+            ops.rmsnorm(h, b.norm2, xn, cfg.rms_eps)
+            gu = b.gate_up(xn)
+            mlp = torch.nn.functional.silu(gu[:, : self.ffn_l].float()).mul_(gu[:, self.ffn_l:].float()).to(torch.float16)
+            h = h + reduce(b.down(mlp))
+        last = h.reshape(R, T, cfg.hidden)[:, -1].contiguous()
+        ops.rmsnorm(last, self.norm_f, self.xn, cfg.rms_eps)
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        self.pos.fill_(T - 1)
+        ops.next_token(self.logits, self.next_ids, self.ids, self.pos, None)        # pos -> T, ids -> greedy choice
+        return self.logits
+
     def reference_logits(self, tokens: torch.Tensor) -> torch.Tensor:
         """fp32 torch forward of the same network on `tokens` [rows, T] -> logits [rows, T, vocab]."""
         cfg = self.cfg

@@ -201,3 +201,30 @@ def test_mailbox_wait_runs_out_and_reports():
     torch.cuda.synchronize()
     ops.device_status()
     assert torch.equal(out[0], table[9]) and int(steps_done) == 2
+
+
+@pytest.mark.parametrize("kv_heads", [2, 4])
+def test_prefill_on_the_tensor_core_gemm_then_decode(kv_heads):
+    """A 40-token prompt in one pass through the fused dequant-GEMM, then token-by-token decoding from the caches it
+    filled: logits against the fp32 reference of the same network at every position that is checked."""
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=kv_heads, ffn=1024, vocab=1024, max_pos=64, weight_scale=0.05)
+    rows, T, extra = 2, 40, 5
+    model = RPTCLlama(cfg, rows=rows, seed=9)
+    g = torch.Generator(device="cuda").manual_seed(13)
+    tokens = torch.randint(0, cfg.vocab, (rows, T + extra), device="cuda", generator=g)
+    ref = model.reference_logits(tokens)
+    model.reset()
+    got = model.prefill(tokens[:, :T]).float()
+    torch.cuda.synchronize()
+    err = (got - ref[:, T - 1]).abs().max().item()
+    assert err <= 1.5e-2 * ref[:, T - 1].abs().max().item(), err
+    assert model.pos.tolist() == [T] * rows
+    assert torch.equal(model.ids.long(), got.argmax(dim=1))
+    model.capture()
+    for t in range(T, T + extra):                         # decode continues from the prefilled caches
+        model.ids.copy_(tokens[:, t].to(torch.int32))
+        model.step()
+        torch.cuda.synchronize()
+        err = (model.logits.float() - ref[:, t]).abs().max().item()
+        assert err <= 1.5e-2 * ref[:, t].abs().max().item(), (t, err)
