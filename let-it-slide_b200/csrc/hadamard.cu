@@ -18,9 +18,10 @@ struct HadParams {
     const __half *signs;
     const __half *residual;     // optional fp16 [rows][ld_res], added to the result
     int64_t ld_res;
-    int32_t block, chunk;
+    int32_t block, chunk;       // chunk: columns per CTA (a block, or 2048 = eight warps of 256 when blocks are <= 256)
     int32_t in_is_f32, transpose, clear_in;
     float scale;
+    int64_t n;
 };
 
 __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
@@ -30,6 +31,7 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
     const int t = threadIdx.x;
     const int64_t row = blockIdx.y;
     const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * t;
+    if (col >= p.n) return;     // only with blocks <= 256 (whole warps leave; such blocks need no CTA barrier)
     float v[8];
     if (p.in_is_f32) load8_f32(const_cast<float *>(static_cast<const float *>(p.in)) + row * p.ld_in + col, v, p.clear_in != 0);
     else load8_f16(static_cast<const __half *>(p.in) + row * p.ld_in + col, v);
@@ -167,6 +169,14 @@ extern "C" int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void 
     p.transpose = transpose;
     p.clear_in = clear_in;
     p.scale = scale * hadamard_norm(block);
+    p.n = n;
+    if (block <= 256 && n > 256) {
+        // small blocks: a warp per 256 columns, eight warps per CTA, so that many-row inputs do not become
+        // hundreds of thousands of one-warp CTAs
+        p.chunk = 2048;
+        return launch(hadamard_kernel, dim3((unsigned)((n + 2047) / 2048), (unsigned)rows), dim3(256), 0,
+                      static_cast<cudaStream_t>(stream), p);
+    }
     return launch(hadamard_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0,
                   static_cast<cudaStream_t>(stream), p);
 }

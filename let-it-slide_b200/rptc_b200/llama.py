@@ -429,7 +429,7 @@ class RPTCLlama:
             h = h + reduce(b.o(att.transpose(1, 2).reshape(R * T, q_dim)))
             ops.rmsnorm(h, b.norm2, xn, cfg.rms_eps)
             gu = b.gate_up(xn)
-            mlp = torch.nn.functional.silu(gu[:, : self.ffn_l].float()).mul_(gu[:, self.ffn_l:].float()).to(torch.float16)
+            mlp = torch.nn.functional.silu(gu[:, : self.ffn_l]).mul_(gu[:, self.ffn_l:])          # fp32 inside, fp16 in and out
             h = h + reduce(b.down(mlp))
         last = h.reshape(R, T, cfg.hidden)[:, -1].contiguous()
         ops.rmsnorm(last, self.norm_f, self.xn, cfg.rms_eps)
