@@ -238,6 +238,17 @@ int rptc_next_token(const void *logits, int64_t ld, int64_t rows, int64_t n, int
 int rptc_embed_mailbox(const void *table, const uint64_t *slots, uint32_t *steps_done, int32_t *ids, void *out, int64_t ld_out,
                        int64_t rows, int64_t n, int64_t vocab, int timeout_ms, rptc_stream_t stream);
 
+/* --- the code-A trellis encoder (rptc.py:13-71 `quantize`, diagonal corrections; K = 2 bits per weight) ---
+ * For each of `rows` sample rows (fp32 [rows][ld_samples], n used) the symbols in 0..3 (int32 [rows][ld_sym]) whose
+ * shift-register walk from state 0 minimises sum_i pos_weight[i] * (samples[i] - alphabet[state_i])^2, and that
+ * minimum (loss[rows]).  alphabet fp32 [2^L], 4 <= L <= 16.  First-minimum tie breaks and unfused fp32 arithmetic, as
+ * in the reference.  workspace: rptc_viterbi_workspace_bytes(rows, n, L) bytes of device memory, 256-byte aligned
+ * (two cost arrays and one survivor byte per position, row and state prefix: 16 KiB per row and position at L = 16). */
+int64_t rptc_viterbi_workspace_bytes(int64_t rows, int64_t n, int L);
+int rptc_viterbi_encode(const float *alphabet, const float *pos_weight, const float *samples, int64_t ld_samples, int64_t rows,
+                        int64_t n, int L, int32_t *symbols, int64_t ld_sym, float *loss, void *workspace, int64_t workspace_bytes,
+                        rptc_stream_t stream);
+
 /* --- tensor-parallel decode: output transform + all-reduce + residual add in one kernel over NVLink peer
  * memory (no reference counterpart; the reference has no distributed code) ---
  * rptc_peer_alloc / export / import / close / free: an exchange buffer of this process (cudaMalloc, zeroed),

@@ -4,7 +4,8 @@
     dequantize(permuted_alphabet, quantized) -> dequantized
 
 `quantize` is the Viterbi encoder of rptc.py:13-71 (state = last L bits, 2 bits per step, start
-state 0, first-minimum tie break); it is the offline half and runs wherever its tensors live.
+state 0, first-minimum tie break); it is the offline half: CUDA fp32 tensors take the CUDA encoder
+(csrc/viterbi.cu), anything else a torch restatement of the same recurrence.
 `dequantize` is the decoder of rptc.py:74-85 and is the hot path: it packs the symbols into the
 MSB-first bitstream the kernels read and calls the CUDA decompress kernel, so it needs CUDA tensors
 (there is no CPU decode path in this package).  The codebook is held in fp16 on the device, as in
@@ -25,6 +26,9 @@ def quantize_rows(permuted_alphabet: torch.Tensor, weights: torch.Tensor, sample
     L = M.bit_length() - 1
     B, length = samples.shape
     dev, dt = samples.device, permuted_alphabet.dtype
+    if samples.is_cuda and dt == torch.float32 and 4 <= L <= 16:
+        # the CUDA encoder: same recurrence, ties and fp32 arithmetic, one launch per position for a batch of rows
+        return ops.viterbi_encode(permuted_alphabet, weights, samples)
     rho = torch.full((B, M), float("inf"), dtype=dt, device=dev)
     rho[:, 0] = 0                                              # initial state is zero (rptc.py:57-58)
     back = torch.empty((length, B, M >> 2), dtype=torch.uint8, device=dev)

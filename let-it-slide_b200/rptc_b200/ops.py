@@ -294,6 +294,31 @@ def next_token(logits: torch.Tensor, next_ids: torch.Tensor, ids: torch.Tensor |
                                     ptr(steps_done), stream_ptr()), "rptc_next_token")
 
 
+def viterbi_encode(alphabet: torch.Tensor, pos_weight: torch.Tensor, samples: torch.Tensor, workspace_limit: int = 12 << 30):
+    """Code-A trellis encoder on the GPU (rptc_viterbi_encode): samples fp32 [rows, n] -> (symbols int32 [rows, n],
+    loss fp32 [rows]).  Rows go through in batches sized so that the survivor memory stays under `workspace_limit`."""
+    M = alphabet.numel()
+    L = M.bit_length() - 1
+    if M != 1 << L:
+        raise RuntimeError("the alphabet must have 2^L entries")
+    alphabet = alphabet.to(torch.float32).contiguous()
+    pos_weight = pos_weight.to(torch.float32).contiguous()
+    samples = samples.to(torch.float32).contiguous()
+    rows, n = samples.shape
+    symbols = torch.empty((rows, n), dtype=torch.int32, device=samples.device)
+    loss = torch.empty(rows, dtype=torch.float32, device=samples.device)
+    per_row = lib().rptc_viterbi_workspace_bytes(1, n, L)
+    batch = max(1, min(rows, 128, workspace_limit // per_row))
+    with torch.cuda.device(samples.device):
+        need = lib().rptc_viterbi_workspace_bytes(batch, n, L)
+        ws = torch.empty(need, dtype=torch.uint8, device=samples.device)
+        for r0 in range(0, rows, batch):
+            r = min(batch, rows - r0)
+            check(lib().rptc_viterbi_encode(ptr(alphabet), ptr(pos_weight), ptr(samples[r0:]), n, r, n, L, ptr(symbols[r0:]), n,
+                                            ptr(loss[r0:]), ptr(ws), need, stream_ptr()), "rptc_viterbi_encode")
+    return symbols, loss
+
+
 def device_status() -> None:
     """Raises if a kernel reported a timed-out wait since the last call."""
     check(lib().rptc_device_status(), "rptc_device_status")
