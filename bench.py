@@ -5,7 +5,7 @@
 
 A "step" is one decode token (batch 1 per GPU) through a Llama-2-7B-shape network whose block
 linears are RPTC 2-bit (HASH code, S=8, native TILED layout, randomized-Hadamard incoherence on
-both sides), random-init weights and uniform-random token ids (synthetic; see DESIGN.md).  The
+both sides), random-init weights and uniform-random token ids (synthetic).  The
 prompt (128 tokens) is pushed through the same decode step before timing starts.  With N > 1 every
 rank decodes its own sequence (replicas, weak scaling; no data-path collective): only the 70B shape
 is partitioned, `--workload llama2-70b-tp`.

@@ -6,9 +6,9 @@
 # parity tests import it as `rptc_kernels_reference` to pin the CPU oracle's "refkernel" mode
 # against what the reference's own kernels really compute.
 #
-#   usage: oracle/build_ref.sh [reference_root]      (default /root/reference)
+#   usage: oracle/build_ref.sh [reference_root]      (default: $RPTC_REFERENCE_ROOT)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${RPTC_REFERENCE_ROOT:-/root/reference}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 SRC="$REF/rptc_kernels/csrc/rptc_kernels"
 OUT="$HERE/_ref"

@@ -1,6 +1,6 @@
 """Generates tests/golden/rptc_reference_golden.npz by running the reference's OWN Python code.
 
-    python tests/golden/make_golden.py [reference_root]     (default /root/reference)
+    python tests/golden/make_golden.py [reference_root]     (default: $RPTC_REFERENCE_ROOT)
 
 The reference's rptc.py, rptc_lite.py and quantize_hf.py are imported unmodified (with tests/golden/jax_shim.py
 standing in for JAX, which is not installed) and their `dequantize` / `quantize` functions are run
@@ -121,4 +121,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RPTC_REFERENCE_ROOT", "/root/reference"))
