@@ -228,3 +228,27 @@ def test_prefill_on_the_tensor_core_gemm_then_decode(kv_heads):
         torch.cuda.synchronize()
         err = (model.logits.float() - ref[:, t]).abs().max().item()
         assert err <= 1.5e-2 * ref[:, t].abs().max().item(), (t, err)
+
+
+@pytest.mark.parametrize("kv_heads", [2, 4])
+def test_decode_attention_beyond_one_chunk_of_positions(kv_heads):
+    """Contexts of 300-560 positions: the attention kernel takes two and three chunks of 256 positions through its
+    registers (online softmax across chunks), in both its forms (q/k/v finish fused in, or not)."""
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=kv_heads, ffn=1024, vocab=1024, max_pos=600, weight_scale=0.05)
+    rows = 2
+    model = RPTCLlama(cfg, rows=rows, seed=21)
+    g = torch.Generator(device="cuda").manual_seed(23)
+    for T in (300, 555):
+        tokens = torch.randint(0, cfg.vocab, (rows, T + 4), device="cuda", generator=g)
+        ref = model.reference_logits(tokens)
+        model.reset()
+        model.graph = None
+        model.prefill(tokens[:, :T])
+        model.capture()
+        for t in range(T, T + 4):
+            model.ids.copy_(tokens[:, t].to(torch.int32))
+            model.step()
+            torch.cuda.synchronize()
+            err = (model.logits.float() - ref[:, t]).abs().max().item()
+            assert err <= 1.5e-2 * ref[:, t].abs().max().item(), (T, t, err)
