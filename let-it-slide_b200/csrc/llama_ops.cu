@@ -126,6 +126,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     }
     uint2 qraw = make_uint2(0u, 0u);
     if (!fused) qraw = ld_ordered_u64(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 4 * lane);
+    // rotary angles of the new position: they depend on the position only, so they are ready before the wait
+    float rot_cs[8], rot_sn[8];
+    if (fused && warp < 2) {
+        const int i8 = (t & 15) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &rot_sn[i], &rot_cs[i]);
+    }
     if (fused) {
         // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv
         // layer's accumulator -- per-head 128-wide output transform, fp16 rounding, rotary embedding -- appends
@@ -152,8 +159,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
-                float sn, cs;
-                sincosf(ps * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &sn, &cs);
+                const float sn = rot_sn[i], cs = rot_cs[i];
                 o[i] = grp == 2 ? v[i] : (upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn);
             }
             if (grp == 0) {
