@@ -128,8 +128,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     if (!fused) qraw = ld_ordered_u64(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 4 * lane);
     // rotary angles of the new position: they depend on the position only, so they are ready before the wait
     float rot_cs[8], rot_sn[8];
+    uint4 so_raw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
+    const float si_mine = (signs_in && t < D) ? __half2float(signs_in[head * D + t]) : 1.f;      // constants: fetched early
     if (fused && warp < 2) {
         const int i8 = (t & 15) * 8;
+        const int grp0 = t >> 4;
+        if (signs_out && grp0 < 3) so_raw = *reinterpret_cast<const uint4 *>(signs_out + (grp0 == 0 ? head : grp0 == 1 ? hq + kvh : hq + hkv + kvh) * D + i8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &rot_sn[i], &rot_cs[i]);
     }
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
             float v[8], sg[8];
             if (grp < 3) {
                 load8_f32(acc + (int64_t)row * ld_acc + col, v, true);
-                unpack8(raw8_or_ones(signs_out ? signs_out + col : nullptr), sg);
+                unpack8(so_raw, sg);
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = 0.f, sg[i] = 1.f;
@@ -238,7 +242,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         if (signs_in) {
             // input-side transform of the output projection, one 128-wide Hadamard block per head:
             // o <- H_128(s * o) / sqrt(128); thread t holds element t (threads 0..127 = warps 0..3)
-            o *= __half2float(signs_in[head * D + t]);
+            o *= si_mine;
 #pragma unroll
             for (int mm = 1; mm < 32; mm <<= 1) {
                 const float other = __shfl_xor_sync(0xFFFFFFFFu, o, mm);
