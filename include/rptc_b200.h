@@ -138,6 +138,18 @@ typedef struct rptc_gemv_input {
 int rptc_gemv_glued(const void *codes, const void *lut, const uint32_t *carry_in, const rptc_gemv_input *in, float *acc,
                     int64_t ld_acc, int64_t m, int64_t n, int batch, const rptc_format *fmt, rptc_stream_t stream);
 
+/* The down projection of a gated MLP with its activations made inside the launch: rptc_gemv whose x is what
+ * rptc_swiglu_hadamard would have written from the gate-up layer's accumulator `prev_acc` (fp32 [batch][ld_prev >= 2n],
+ * gate in columns [0, n), up in [n, 2n)): x = H(s_in * silu(g) * u), (g | u) = s_out * H(prev_acc) * scale_out, with
+ * Hadamard blocks of `block` <= 256 columns.  The work is ordered by 256-column blocks so that a CTA makes only the
+ * one or two blocks of x that its share of the matrix multiplies.  prev_acc is read by several CTAs and not cleared;
+ * `clear` (optional, fp32, clear_count a multiple of 4) is a range this launch zeroes once the launches before it
+ * have completed.  TILED layout, no quirk, batch 1-2, n % 256 == 0.  No reference counterpart. */
+int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32_t *carry_in, const float *prev_acc, int64_t ld_prev,
+                     const void *signs_out, float scale_out, const void *signs_in, int block, float *acc, int64_t ld_acc,
+                     int64_t m, int64_t n, int batch, const rptc_format *fmt, float *clear, int64_t clear_count,
+                     rptc_stream_t stream);
+
 /* y[b][i] = fp16(scale * acc[b][i] (+ y[b][i] if accumulate));  acc[b][i] = 0 if clear.
  * accumulate = 1 gives decompress_matvec_t's `out +=` (inference_t.cu:170-171). */
 int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_y, int64_t m, int batch, float scale,

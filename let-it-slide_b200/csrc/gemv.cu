@@ -53,6 +53,10 @@ struct GemvParams {
     unsigned int *status;
     // activations computed in the launch (pair kernel, INPUT != 0): the caller's descriptor
     rptc_gemv_input in;
+    // gemv_colblock_kernel: the gated-MLP middle that produces this layer's activations, and a range to zero
+    SwigluParams sw;
+    float *clear;
+    int64_t clear_count;
 };
 
 // Source pair of stream pair s under the fused reference kernel's x staging (inference.cu:216-221,249).
@@ -448,6 +452,210 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         }
     }
     if (!waited_prior) pdl_wait_prior_grids();
+}
+
+// ---- the down projection of a gated MLP: activations made from the gate-up accumulator, block by block -----------
+// The pair kernel's granules in a different order: 256-column blocks outermost, then pairs of row blocks, then the
+// units of the block.  A CTA's granules then lie in one or two column blocks, so the CTA needs only those 256-column
+// pieces of x -- and makes them itself from the gate-up layer's fp32 accumulator (output transform of gate and up,
+// SiLU(gate) * up, this layer's input transform; one warp per block and row, no CTA barrier inside).  The separate
+// SwiGLU launch and the staging of the full activation row disappear.  Runs are as long as in the row-major order
+// (a warp holds ~4.6 granules of the 7B down projection either way).  The accumulator it reads is shared by several
+// CTAs and therefore zeroed by a later launch.
+template <int CODE, int K, int BATCH>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const GemvParams p) {
+    constexpr int WPU = 128 / K;
+    constexpr int PAIRS = WPU / 2;
+    constexpr int NW2 = 2 * GroupShape<K>::kWords;
+    constexpr uint32_t UPB = 256 / WPU;                       // units per 256-column block
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t s0 = smem_addr(smem_raw);
+    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
+    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
+    uint32_t lut_tab, xs;
+    if (CODE == RPTC_CODE_HASH) {
+        lut_tab = kHashLutWindow;
+        xs = kHashLutWindow + kHashLutBytes;
+    } else {
+        lut_tab = s0 + kBarBytes + kRingBytes;
+        xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
+    }
+    if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
+        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        return;
+    }
+    const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
+    pdl_allow_next_grid();
+
+    const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
+    const uint32_t GW = gridDim.x * kGemvWarps, gw = blockIdx.x * kGemvWarps + warp;
+    const uint32_t cell = n_rbp * UPB;                          // granules of one column block
+    const uint32_t T = n_rbp * (uint32_t)p.n_units;
+    const uint32_t per = T / GW, extra = T - per * GW;
+    auto first_of = [&](uint32_t w) { return w * per + min(w, extra); };
+    const uint32_t g0 = first_of(gw), count = per + (gw < extra ? 1u : 0u);
+    // column blocks of this CTA's warps together (its granules are consecutive)
+    const uint32_t cta_g0 = first_of(blockIdx.x * kGemvWarps), cta_g1 = first_of((blockIdx.x + 1) * kGemvWarps);
+    const uint32_t cb_first = cta_g0 / cell, cb_last = cta_g1 > cta_g0 ? (cta_g1 - 1) / cell : cb_first;
+    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;       // seg_units: the most units a CTA can need
+    const int64_t rb_stride = (int64_t)p.n_units << 5;
+    uint32_t slot = 0, phase = 0;
+    bool ok = true;
+
+    // this warp's first granule
+    const uint32_t cb0 = g0 / cell, rem0 = g0 - cb0 * cell, rbp0 = rem0 / UPB, u40 = rem0 - rbp0 * UPB;
+    uint32_t fcb = cb0, frbp = rbp0, fu4 = u40;                 // fetch cursor (lane 0)
+    const uint4 *fptr = p.codes + (int64_t)(2 * rbp0) * rb_stride + ((int64_t)(cb0 * UPB + u40) << 5);
+    auto issue_stage = [&](uint32_t at_slot) {
+        const bool has_b = 2 * frbp + 1 < n_rb;
+        const uint32_t bar = bars + 8u * at_slot, dst = ring + at_slot * kStageBytes;
+        mbar_expect_tx(bar, has_b ? 2 * kUnitBytes : kUnitBytes);
+        bulk_g2s(dst, fptr, kUnitBytes, bar);
+        if (has_b) bulk_g2s(dst + kUnitBytes, fptr + rb_stride, kUnitBytes, bar);
+        fptr += 32;
+        if (++fu4 == UPB) {
+            fu4 = 0;
+            if (++frbp == n_rbp) {
+                frbp = 0;
+                ++fcb;
+            }
+            fptr = p.codes + (int64_t)(2 * frbp) * rb_stride + ((int64_t)(fcb * UPB) << 5);
+        }
+    };
+    uint32_t to_issue = count;
+    {
+        const uint32_t ahead = min(count, (uint32_t)kStages);
+        if (lane == 0) {
+            uint32_t sl = slot;
+            for (uint32_t k = 0; k < ahead; ++k) {
+                issue_stage(sl);
+                if (++sl == kStages) sl = 0;
+            }
+        }
+        to_issue -= ahead;
+    }
+
+    pdl_wait_prior_grids();
+    lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+    if (p.clear) {
+        float4 *z = reinterpret_cast<float4 *>(p.clear);
+        for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.clear_count; i += (int64_t)gridDim.x * kGemvThreads)
+            z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // ---- activations of this CTA's column blocks: one warp per block and row ----
+    {
+        __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+        for (uint32_t b = cb_first + warp; b <= cb_last; b += kGemvWarps)
+#pragma unroll 1
+            for (int r = 0; r < BATCH; ++r)
+                swiglu_chunk(p.sw, r, (int64_t)b * 256 + 8 * lane, nullptr, false,
+                             x_sm + (size_t)r * (x_batch_stride >> 1) + (size_t)(b - cb_first) * 256 + 8 * lane);
+    }
+    __syncthreads();
+
+    // ---- main loop: runs of consecutive units inside one column block and pair of row blocks ----
+    uint32_t cb = cb0, rbp = rbp0, u4 = u40, k = 0;
+    while (k < count && ok) {
+        const uint32_t run = min(count - k, UPB - u4);
+        const int64_t row_a = ((int64_t)rbp << 6) + lane;
+        const bool has_b = 2 * rbp + 1 < n_rb;
+        const int32_t ug = (int32_t)(cb * UPB + u4);
+        uint32_t prev_a, prev_b;
+        if (ug == 0) {
+            prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
+            prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
+        } else {
+            const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride + ((int64_t)(ug - 1) << 5) + lane) + 3;
+            prev_a = __ldg(last);
+            prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+        }
+        float facc_a[BATCH], facc_b[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
+        uint32_t xu = xs + ((cb - cb_first) * UPB + u4) * (WPU * 2u);
+#pragma unroll 1
+        for (uint32_t j = 0; j < run; ++j) {
+            ok = mbar_wait(bars + 8u * slot, phase, p.status);
+            if (!ok) break;
+            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
+            const uint4 va = lds128(stage_base);
+            const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
+            uint32_t Ra[NW2], Rb[NW2];
+            {
+                const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+                make_windows<K>(wa, prev_a, Ra);
+                make_windows<K>(wb, prev_b, Rb);
+            }
+            prev_a = va.w;
+            prev_b = vb.w;
+            __half2 ha[BATCH][4], hb[BATCH][4];
+            uint4 xv[BATCH];
+#pragma unroll
+            for (int pi = 0; pi < PAIRS; ++pi) {
+                if ((pi & 3) == 0) {
+#pragma unroll
+                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+                }
+                const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
+                const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
+                    const __half2 x2 = u32_as_half2(xq);
+                    ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
+                    hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+                const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
+                const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
+                facc_a[b] += fa.x + fa.y;
+                facc_b[b] += fb.x + fb.y;
+            }
+            xu += WPU * 2u;
+            __syncwarp();
+            if (to_issue) {
+                if (lane == 0) issue_stage(slot);
+                --to_issue;
+            }
+            if (++slot == kStages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
+            if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
+        }
+        k += run;
+        u4 += run;
+        if (u4 == UPB) {
+            u4 = 0;
+            if (++rbp == n_rbp) {
+                rbp = 0;
+                ++cb;
+            }
+        }
+    }
+    if (!ok) {
+        for (int s = 0; s < kStages; ++s) {      // bounded chance for the copies in flight to land
+            mbar_wait(bars + 8u * slot, phase, p.status);
+            if (++slot == kStages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+    }
 }
 
 // ---- tensor-core form of the pair kernel ---------------------------------------------------------------
@@ -985,4 +1193,93 @@ extern "C" int rptc_gemv_glued(const void *codes, const void *lut, const uint32_
     if (int e = rptc_check_device()) return e;
     return gemv_one(codes, lut, carry_in, nullptr, 0, acc, ld_acc, m, n, batch, RPTC_XORDER_NATURAL, *fmt,
                     static_cast<cudaStream_t>(stream), in);
+}
+
+template <int CODE, int K, int BATCH>
+static int launch_gemv_colblock(const GemvParams &p, size_t smem, cudaStream_t stream) {
+    static bool configured = false;
+    auto kern = gemv_colblock_kernel<CODE, K, BATCH>;
+    if (!configured) {
+        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
+}
+
+extern "C" int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32_t *carry_in, const float *prev_acc, int64_t ld_prev,
+                                const void *signs_out, float scale_out, const void *signs_in, int block, float *acc, int64_t ld_acc,
+                                int64_t m, int64_t n, int batch, const rptc_format *fmt, float *clear, int64_t clear_count,
+                                rptc_stream_t stream) {
+    if (!codes || !lut || !prev_acc || !acc || !fmt) return RPTC_ERR_ARG;
+    if (int e = check_format(fmt)) return e;
+    if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
+    if (fmt->layout != RPTC_LAYOUT_TILED || fmt->quirk != RPTC_QUIRK_NONE || batch < 1 || batch > 2) return RPTC_ERR_UNSUPPORTED;
+    if (block < 8 || block > 256 || (block & (block - 1))) return RPTC_ERR_UNSUPPORTED;
+    if (m <= 0 || n <= 0 || (m % 32) || (n % 256) || ld_acc < m || ld_prev < 2 * n) return RPTC_ERR_SHAPE;
+    if (m > (int64_t(1) << 30) || (m / 32) * (n / (128 / fmt->K)) >= (int64_t(1) << 31)) return RPTC_ERR_TOO_LARGE;
+    auto misaligned = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+    if (misaligned(codes) || misaligned(lut) || misaligned(prev_acc) || misaligned(signs_out) || misaligned(signs_in) || misaligned(clear) ||
+        (ld_prev % 4) || (clear_count % 4))
+        return RPTC_ERR_ALIGN;
+    if (clear_count < 0 || (clear_count && !clear)) return RPTC_ERR_ARG;
+    if (int e = rptc_check_device()) return e;
+    const int K = fmt->K, wpu = 128 / K;
+    GemvParams p{};
+    p.codes = static_cast<const uint4 *>(codes);
+    p.n_units = (int32_t)(n / wpu);
+    p.st = unit_strides(fmt->layout, m, p.n_units);
+    p.lut = static_cast<const __half *>(lut);
+    p.carry_in = carry_in;
+    p.acc = acc;
+    p.ld_acc = ld_acc;
+    p.m = m;
+    p.n = n;
+    p.L = fmt->L;
+    p.S = fmt->S;
+    p.quirk = fmt->quirk;
+    p.x_order = RPTC_XORDER_NATURAL;
+    p.status = device_status_word();
+    if (!p.status) return RPTC_ERR_CUDA;
+    float norm = 1.f;
+    for (int b = block; b > 1; b >>= 2) norm *= (b >= 4) ? 0.5f : 0.70710678118654752f;
+    p.sw.acc = const_cast<float *>(prev_acc);
+    p.sw.ld_acc = ld_prev;
+    p.sw.out = nullptr;
+    p.sw.ld_out = 0;
+    p.sw.signs_out = static_cast<const __half *>(signs_out);
+    p.sw.signs_in = static_cast<const __half *>(signs_in);
+    p.sw.n = n;
+    p.sw.block = block;
+    p.sw.chunk = 256;
+    p.sw.clear = 0;
+    p.sw.scale_out = scale_out * norm;
+    p.sw.scale_in = norm;
+    p.clear = clear;
+    p.clear_count = clear_count;
+    // the most 256-column blocks one CTA's granules can touch
+    const int64_t upb = 256 / wpu, n_rbp = (m / 32 + 1) / 2, cell = n_rbp * upb;
+    const int64_t T = n_rbp * p.n_units, GW = (int64_t)num_sms() * kGemvWarps;
+    const int64_t cta_granules = (T / GW + 1) * kGemvWarps;
+    int64_t max_blocks = (cta_granules + cell - 2) / cell + 1;
+    if (max_blocks > n / 256) max_blocks = n / 256;
+    p.seg_units = (int32_t)(max_blocks * upb);
+    const size_t kMaxSmem = 227 * 1024 - 1024;
+    size_t fixed;
+    if (fmt->code == RPTC_CODE_HASH) fixed = kHashLutWindow + kHashLutBytes;
+    else fixed = kBarBytes + kRingBytes + (fmt->code == RPTC_CODE_LUT ? (size_t(2) << fmt->L) : (size_t(128) << fmt->S)) + 128;
+    const size_t smem = fixed + (size_t)batch * max_blocks * 512;
+    if (smem > kMaxSmem) return RPTC_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (fmt->code) {
+        case RPTC_CODE_LUT:
+            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LUT, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LUT, 2, 2>(p, smem, s);
+            return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LUT, 4, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LUT, 4, 2>(p, smem, s);
+        case RPTC_CODE_HASH:
+            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_HASH, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_HASH, 2, 2>(p, smem, s);
+            break;
+        case RPTC_CODE_LITE:
+            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LITE, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LITE, 2, 2>(p, smem, s);
+            return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LITE, 4, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LITE, 4, 2>(p, smem, s);
+    }
+    return RPTC_ERR_UNSUPPORTED;
 }

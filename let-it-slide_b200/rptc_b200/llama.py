@@ -112,10 +112,12 @@ class RPTCLlama:
         f32 = dict(dtype=torch.float32, device=device)
         self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
         self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
-        self.acc_gu = torch.zeros((rows, 2 * self.ffn_l), **f32)
-        # second residual stream and accumulator of the shortest chain, whose matvecs compute their own inputs
+        # second residual stream and accumulator of the shortest chain, whose matvecs compute their own inputs; the
+        # accumulators that a later launch zeroes (acc_o, acc_gu) share one allocation so that one range covers both
         self.h2 = torch.zeros((rows, cfg.hidden), **f16)
-        self.acc_o = torch.zeros((rows, cfg.hidden), **f32)
+        self._acc_pool = torch.zeros(rows * (cfg.hidden + 2 * self.ffn_l), **f32)
+        self.acc_o = self._acc_pool[: rows * cfg.hidden].view(rows, cfg.hidden)
+        self.acc_gu = self._acc_pool[rows * cfg.hidden:].view(rows, 2 * self.ffn_l)
         self.peer = None
         if tp_world > 1 and peer_allreduce and incoherent:
             # the fused transform + all-reduce + residual kernel over NVLink peer memory instead of NCCL
@@ -123,6 +125,7 @@ class RPTCLlama:
             self.peer = PeerAllReduce(rows, cfg.hidden, self.blocks[0].o.block_out, tp_rank, tp_world, tp_group)
         self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
         self.fused_tp = True        # False: the 15-launch chain under tensor parallelism
+        self.glued_mlp = True       # False: SwiGLU in a launch of its own inside the short chain
         self.host_ids: torch.Tensor | None = None      # see bind_host_io
         self.host_next: torch.Tensor | None = None
         self.mailbox = None                            # see bind_mailbox
@@ -143,6 +146,12 @@ class RPTCLlama:
         b = self.blocks[0]
         return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and self.heads_l == self.kv_heads_l
                 and b.qkv.block_out == 128 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
+
+    def _mlp_glueable(self) -> bool:
+        """The down projection can make its own activations (five launches per block) when the MLP width is a whole
+        number of 256-column blocks and both transforms around the SwiGLU use blocks of at most 256."""
+        b = self.blocks[0]
+        return (self.glued_mlp and self.ffn_l % 256 == 0 and b.down.block_in <= 256 and b.down.block_in == b.gate_up.block_out)
 
     def _fusable_tp(self) -> bool:
         """The tensor-parallel short chain (11 launches per block with the peer all-reduce): incoherent layers, hidden a
@@ -218,25 +227,34 @@ class RPTCLlama:
         that every CTA of a launch reads is zeroed by a later launch (`clear`)."""
         cfg, r = self.cfg, self.rows
         self._embed_ids()
+        mlp_glued = self._mlp_glueable()
+        # the launch that opens a block zeroes what the block before it left: acc_o always, acc_gu too when the down
+        # projection reads it in every CTA
+        stale = self._acc_pool if mlp_glued else self.acc_o
         for i, b in enumerate(self.blocks):
             prev = self.blocks[i - 1].down if i else None
             ops.gemv_norm_input(b.qkv.codes, b.qkv.lut, self.acc_qkv, b.qkv.out_features, cfg.hidden, self.fmt, r,
                                 self.acc_h if prev else None, prev.signs_out if prev else None, prev.scale if prev else 1.0,
-                                self.h, self.h2, b.norm1, cfg.rms_eps, b.qkv.signs_in, clear=self.acc_o)
+                                self.h, self.h2, b.norm1, cfg.rms_eps, b.qkv.signs_in, clear=stale)
             ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
                                 self.heads_l, cfg.rope_theta, b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_o)
             ops.gemv_norm_input(b.gate_up.codes, b.gate_up.lut, self.acc_gu, b.gate_up.out_features, cfg.hidden, self.fmt, r,
                                 self.acc_o, b.o.signs_out, b.o.scale, self.h2, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in,
                                 clear=self.acc_h if i else None)
-            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
-                                b.gate_up.scale, 1.0, clear=True)
-            b.down.matvec_acc(self.mlp, self.acc_h)
+            if mlp_glued:
+                ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, r, self.acc_gu,
+                                      b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in,
+                                      carry_in=b.down.carry_in)
+            else:
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                    b.gate_up.scale, 1.0, clear=True)
+                b.down.matvec_acc(self.mlp, self.acc_h)
         last = self.blocks[-1].down
         ops.finish_norm_hadamard(self.acc_h, last.signs_out, last.scale, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = 6 * len(self.blocks) + 4
+        self.launches_per_step = (5 if mlp_glued else 6) * len(self.blocks) + 4
 
     def _step_fused_tp(self) -> None:
         """Tensor-parallel decode step with the glue fused as far as the all-reduce allows: RMSNorm + input transform in
@@ -375,7 +393,7 @@ class RPTCLlama:
 
     def reset(self, ids: torch.Tensor | None = None) -> None:
         self.pos.zero_()
-        self.acc_o.zero_()          # the six-launch chain leaves it to the next token's first launch
+        self._acc_pool.zero_()      # the short chain leaves acc_o / acc_gu to the next token's first launch
         if ids is not None:
             self.ids.copy_(ids.to(torch.int32))
 

@@ -118,6 +118,17 @@ def gemv_norm_input(codes: torch.Tensor, lut: torch.Tensor, acc: torch.Tensor, m
                                     ctypes.byref(fmt), stream_ptr()), "rptc_gemv_glued")
 
 
+def gemv_swiglu_input(codes: torch.Tensor, lut: torch.Tensor, acc: torch.Tensor, m: int, n: int, fmt: Format, rows: int,
+                      prev_acc: torch.Tensor, signs_out: torch.Tensor | None, scale_out: float, signs_in: torch.Tensor | None,
+                      block: int, clear: torch.Tensor | None = None, carry_in: torch.Tensor | None = None) -> None:
+    """acc += W x with x = H(s_in * silu(g) * u), (g | u) = s_out * H(prev_acc) * scale_out, made inside the launch
+    block by block (rptc_gemv_swiglu).  `clear` is zeroed by the launch."""
+    with torch.cuda.device(codes.device):
+        check(lib().rptc_gemv_swiglu(ptr(codes), ptr(lut), ptr(carry_in), ptr(prev_acc), _ld(prev_acc, 2 * n), ptr(signs_out), scale_out,
+                                     ptr(signs_in), block, ptr(acc), _ld(acc, m), m, n, rows, ctypes.byref(fmt), ptr(clear),
+                                     0 if clear is None else clear.numel(), stream_ptr()), "rptc_gemv_swiglu")
+
+
 def gemv_finish(acc: torch.Tensor, y: torch.Tensor, m: int, scale: float = 1.0, accumulate: bool = False,
                 clear: bool = True) -> None:
     """y = fp16(scale * acc) (+ y); optionally zero acc (rptc_gemv_finish)."""

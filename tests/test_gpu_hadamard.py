@@ -105,3 +105,34 @@ def test_gemv_computing_its_own_input_matches_glue_then_gemv(batch, m, with_acc)
         # identical activations; the partial sums meet in a different order
         scale = acc_a.abs().max().item()
         assert (acc_b - acc_a).abs().max().item() <= 1e-4 * scale
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("m,n,block", [(4096, 11008, 256), (4096, 1792, 256), (64, 512, 128), (1056, 2048, 64)])
+def test_down_projection_making_its_own_swiglu_input(batch, m, n, block):
+    """rptc_gemv_swiglu against rptc_swiglu_hadamard followed by rptc_gemv, several calls in a row."""
+    from gpu_util import rand_lut, rand_words
+    from rptc_b200 import Format, ops
+    rng = np.random.default_rng(batch * 11 + m + n)
+    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
+    codes = to_dev(o.from_rowmajor(rand_words(rng, m, n, 2), o.LAYOUT_TILED))
+    lut = to_dev(rand_lut(rng, o.CODE_B, S=8))
+    s_out, s_in = to_dev(o.signs_from_seed(3, 2 * n).astype(np.float16)), to_dev(o.signs_from_seed(4, n).astype(np.float16))
+    dirty = torch.ones(2048, dtype=torch.float32, device="cuda")
+    for rep in range(3):
+        prev = to_dev(rng.standard_normal((batch, 2 * n)).astype(np.float32))
+        keep = prev.clone()
+        x_a = torch.empty((batch, n), dtype=torch.float16, device="cuda")
+        ops.swiglu_hadamard(prev.clone(), x_a, s_out, s_in, n, block, 0.7, 1.0, clear=True)
+        acc_a = torch.zeros(batch, m, dtype=torch.float32, device="cuda")
+        ops.gemv_acc(codes, lut, x_a, acc_a, m, n, fmt)
+        acc_b = torch.zeros_like(acc_a)
+        ops.gemv_swiglu_input(codes, lut, acc_b, m, n, fmt, batch, prev, s_out, 0.7, s_in, block, clear=dirty)
+        torch.cuda.synchronize()
+        ops.device_status()
+        assert torch.equal(prev, keep) and not dirty.any()
+        dirty.fill_(1.0)
+        # identical activations; the products are summed in fp16 groups here and, at batch 2, in fp32 by the
+        # tensor-core kernel on the other side
+        scale = acc_a.abs().max().item()
+        assert (acc_b - acc_a).abs().max().item() <= (1e-4 if batch == 1 else 2e-3) * scale
