@@ -63,8 +63,9 @@ class Block:
         self.o.block_in = min(self.o.block_in, cfg.head_dim)      # one Hadamard block per head: fuses into the attention kernel
         self.gate_up = mk(cfg.hidden, 2 * ffn, 2)
         # gate and up are transformed separately, so that the fused SwiGLU kernel can own matching blocks of both
-        self.gate_up.block_out = hadamard_block(ffn)
+        self.gate_up.block_out = min(hadamard_block(ffn), 256)        # at most 256: the SwiGLU middle stays warp-local
         self.down = mk(ffn, cfg.hidden, 3)
+        self.down.block_in = self.gate_up.block_out
         g = torch.Generator(device=device).manual_seed((seed if norm_seed is None else norm_seed) * 16 + 9)   # replicated
         self.norm1 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
         self.norm2 = (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).to(torch.float16)
@@ -118,6 +119,7 @@ class RPTCLlama:
         self._acc_pool = torch.zeros(rows * (cfg.hidden + 2 * self.ffn_l), **f32)
         self.acc_o = self._acc_pool[: rows * cfg.hidden].view(rows, cfg.hidden)
         self.acc_gu = self._acc_pool[rows * cfg.hidden:].view(rows, 2 * self.ffn_l)
+        self.acc_gu2 = torch.zeros_like(self.acc_gu) if tp_world > 1 else None     # see _step_fused_tp
         self.peer = None
         if tp_world > 1 and peer_allreduce and incoherent:
             # the fused transform + all-reduce + residual kernel over NVLink peer memory instead of NCCL
@@ -266,6 +268,8 @@ class RPTCLlama:
         b0 = self.blocks[0]
         ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
         per_reduce = 1 if self.peer is not None else 3
+        mlp_glued = (self._mlp_glueable() and self.rows <= 2 and len(self.blocks) % 2 == 0 and self.fmt.layout == LAYOUT_TILED
+                     and self.fmt.K in (2, 4))
         for i, b in enumerate(self.blocks):
             b.qkv.matvec_acc(xt, self.acc_qkv)
             ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
@@ -275,10 +279,20 @@ class RPTCLlama:
             b.o.matvec_acc(self.attn, self.acc_h)
             self._finish_row_parallel(b.o)
             ops.finish_norm_hadamard(None, None, 1.0, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in, True, xt)
-            b.gate_up.matvec_acc(xt, self.acc_gu)
-            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
-                                b.gate_up.scale, 1.0, clear=True)
-            b.down.matvec_acc(self.mlp, self.acc_h)
+            if mlp_glued:
+                # The down projection makes its SwiGLU input from the gate-up accumulator in every CTA that needs a
+                # piece of it, so nobody owns the clearing: two accumulators alternate from block to block and each
+                # down projection zeroes the one the block before it used.
+                gu, other = (self.acc_gu, self.acc_gu2) if i % 2 == 0 else (self.acc_gu2, self.acc_gu)
+                b.gate_up.matvec_acc(xt, gu)
+                ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, self.rows, gu,
+                                      b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in, clear=other,
+                                      carry_in=b.down.carry_in)
+            else:
+                b.gate_up.matvec_acc(xt, self.acc_gu)
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                    b.gate_up.scale, 1.0, clear=True)
+                b.down.matvec_acc(self.mlp, self.acc_h)
             self._finish_row_parallel(b.down)
             if i + 1 < len(self.blocks):
                 nb = self.blocks[i + 1]
@@ -287,7 +301,7 @@ class RPTCLlama:
                 ops.finish_norm_hadamard(None, None, 1.0, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = (9 + 2 * per_reduce) * len(self.blocks) + 4
+        self.launches_per_step = ((8 if mlp_glued else 9) + 2 * per_reduce) * len(self.blocks) + 4
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
@@ -394,6 +408,8 @@ class RPTCLlama:
     def reset(self, ids: torch.Tensor | None = None) -> None:
         self.pos.zero_()
         self._acc_pool.zero_()      # the short chain leaves acc_o / acc_gu to the next token's first launch
+        if self.acc_gu2 is not None:
+            self.acc_gu2.zero_()
         if ids is not None:
             self.ids.copy_(ids.to(torch.int32))
 
