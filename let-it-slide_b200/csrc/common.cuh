@@ -49,6 +49,14 @@ inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
 // Programmatic dependent launch: both are no-ops for a kernel launched without the attribute.
 __device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_allow_next_grid() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Used right after pdl_wait_prior_grids() on a pointer to data that a prior grid writes: the pointer's value becomes
+// opaque to the compiler, so no load through it -- not even a read-only-path load through a const __restrict__
+// kernel parameter, which a memory clobber alone does not pin -- can be scheduled ahead of the wait.
+template <typename T>
+__device__ __forceinline__ T *after_wait(T *p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

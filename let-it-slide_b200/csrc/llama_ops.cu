@@ -25,6 +25,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__
     __shared__ float red[8];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
+    x = after_wait(x);
     const __half2 *xr = reinterpret_cast<const __half2 *>(x + (int64_t)blockIdx.x * ld_x);
     float ss = 0.f;
     for (int i = threadIdx.x; i < n / 2; i += 256) {
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(256) dense_gemv_kernel(const __half *__restric
                                                          int64_t ld_x, __half *__restrict__ y, int64_t ld_y, int64_t m, int n) {
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
+    x = after_wait(x);
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= m) return;
@@ -300,6 +302,7 @@ __global__ void embed_kernel(const __half *__restrict__ table, const int32_t *__
                              int n) {
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
+    ids = after_wait(ids);
     const uint4 *src = reinterpret_cast<const uint4 *>(table + (int64_t)ids[blockIdx.x] * n);
     uint4 *dst = reinterpret_cast<uint4 *>(out + (int64_t)blockIdx.x * ld_out);
     for (int i = threadIdx.x; i < n / 8; i += blockDim.x) dst[i] = src[i];
@@ -359,6 +362,8 @@ __global__ void __launch_bounds__(1024) next_token_kernel(const __half *__restri
     __shared__ int bi[32];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
+    logits = after_wait(logits);
+    steps_done = after_wait(steps_done);
     const int r = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const __half *row = logits + (int64_t)r * ld;
     float best = -INFINITY;
