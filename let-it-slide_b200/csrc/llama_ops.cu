@@ -192,14 +192,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         m = m_new;
     };
     for (int j0 = warp; j0 < n_old || j0 == warp; j0 += kAttnUnroll * kAttnWarps) {
-        if (j0 != warp) {
-#pragma unroll
-            for (int u = 0; u < kAttnUnroll; ++u) {
-                const int j = j0 + u * kAttnWarps;
-                kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
-                vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
-            }
-        }
+        const int j_next = j0 + kAttnUnroll * kAttnWarps;       // this warp's first position of the next chunk
         float s[kAttnUnroll];
         float mc = -1e30f;
 #pragma unroll
@@ -207,6 +200,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
             const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
             s[u] = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale;
             if (j0 + u * kAttnWarps < n_old) mc = fmaxf(mc, s[u]);
+        }
+        if (j_next < n_old) {      // the K registers are free: the next chunk's K rows travel under this chunk's V pass
+#pragma unroll
+            for (int u = 0; u < kAttnUnroll; ++u) {
+                const int j = j_next + u * kAttnWarps;
+                kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
+            }
         }
         // one rescale per chunk: the chunk's maximum first, then plain accumulation
         const float m_new = fmaxf(m, mc), corr = __expf(m - m_new);
@@ -218,6 +218,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
             const float2 v01 = __half22float2(u32_as_half2(vv[u].x)), v23 = __half22float2(u32_as_half2(vv[u].y));
             l += p;
             a0 += p * v01.x, a1 += p * v01.y, a2 += p * v23.x, a3 += p * v23.y;
+        }
+        if (j_next < n_old) {      // and its V rows under the next chunk's scores
+#pragma unroll
+            for (int u = 0; u < kAttnUnroll; ++u) {
+                const int j = j_next + u * kAttnWarps;
+                vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
+            }
         }
     }
     if (fused && warp == 0) {      // the position made above, from shared memory
