@@ -193,6 +193,10 @@ int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void *out, int64
  * out = H (s_in * (silu(g) * u)) * scale_in, fp16 [rows][ld_out].  No reference counterpart. */
 int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64_t ld_out, const void *signs_out, const void *signs_in,
                          int64_t rows, int64_t n, int block, float scale_out, float scale_in, int clear, rptc_stream_t stream);
+/* The same from the fp16 output of a matrix product (the prefill path): gate_up fp16 [rows][ld_in >= 2n]. */
+int rptc_swiglu_hadamard_f16(const void *gate_up, int64_t ld_in, void *out, int64_t ld_out, const void *signs_out,
+                             const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in,
+                             rptc_stream_t stream);
 
 /* --- the non-quantised pieces of a Llama-architecture decode step (no reference counterpart: the
  * reference evaluates models through Hugging Face transformers, quantize_hf.py:230-236) --- */

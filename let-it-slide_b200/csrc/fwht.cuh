@@ -200,7 +200,8 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
 // g, u = s_out * (H acc) * scale_out.  Both transforms use the same block size, so one CTA owns
 // matching blocks of gate and up.
 struct SwigluParams {
-    float *acc;
+    float *acc;                 // fp32 input (an accumulator), or NULL when the input is fp16
+    const __half *in16;         // fp16 input [rows][ld_acc] (the output of a matrix product), or NULL
     int64_t ld_acc;
     __half *out;
     int64_t ld_out;
@@ -217,7 +218,10 @@ __device__ __forceinline__ void swiglu_chunk(const SwigluParams &p, int64_t row,
     const uint4 raw_sg = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
     const uint4 raw_su = raw8_or_ones(p.signs_out ? p.signs_out + p.n + col : nullptr);
     const uint4 raw_si = raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr);
-    if (clear) {
+    if (p.in16) {
+        load8_f16(p.in16 + row * p.ld_acc + col, g);
+        load8_f16(p.in16 + row * p.ld_acc + p.n + col, u);
+    } else if (clear) {
         load8_f32(p.acc + row * p.ld_acc + col, g, true);
         load8_f32(p.acc + row * p.ld_acc + p.n + col, u, true);
     } else {

@@ -1243,6 +1243,7 @@ extern "C" int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32
     float norm = 1.f;
     for (int b = block; b > 1; b >>= 2) norm *= (b >= 4) ? 0.5f : 0.70710678118654752f;
     p.sw.acc = const_cast<float *>(prev_acc);
+    p.sw.in16 = nullptr;
     p.sw.ld_acc = ld_prev;
     p.sw.out = nullptr;
     p.sw.ld_out = 0;

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
     pdl_wait_prior_grids();
     const int64_t row = blockIdx.y;
     const int64_t col = (int64_t)blockIdx.x * p.chunk + 8 * threadIdx.x;
+    if (col >= p.n) return;     // only with blocks <= 256 (whole warps leave; such blocks need no CTA barrier)
     swiglu_chunk(p, row, col, ex, p.clear != 0, p.out + row * p.ld_out + col);
 }
 
@@ -181,23 +182,25 @@ extern "C" int rptc_hadamard(const void *in, int in_is_f32, int64_t ld_in, void 
                   static_cast<cudaStream_t>(stream), p);
 }
 
-extern "C" int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64_t ld_out, const void *signs_out,
-                                    const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in,
-                                    int clear, rptc_stream_t stream) {
-    if (!acc || !out) return RPTC_ERR_ARG;
+static int swiglu_launch(float *acc, const void *in16, int64_t ld_in, void *out, int64_t ld_out, const void *signs_out,
+                         const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in, int clear,
+                         rptc_stream_t stream) {
+    if ((!acc && !in16) || !out) return RPTC_ERR_ARG;
     if (block < 8 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
-    if (rows <= 0 || n <= 0 || (n % block) || ld_acc < 2 * n || ld_out < n) return RPTC_ERR_SHAPE;
+    if (rows <= 0 || n <= 0 || (n % block) || ld_in < 2 * n || ld_out < n) return RPTC_ERR_SHAPE;
     if (rows > 65535) return RPTC_ERR_TOO_LARGE;
     const int chunk = block < 256 ? 256 : block;
     if (n % chunk) return RPTC_ERR_SHAPE;
-    if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+    const void *in = acc ? static_cast<const void *>(acc) : in16;
+    if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (signs_in && (reinterpret_cast<uintptr_t>(signs_in) & 15)) ||
-        (ld_acc % 4) || (ld_out % 8) || (n % 8))
+        (ld_in % (acc ? 4 : 8)) || (ld_out % 8) || (n % 8))
         return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
     SwigluParams p;
     p.acc = acc;
-    p.ld_acc = ld_acc;
+    p.in16 = acc ? nullptr : static_cast<const __half *>(in16);
+    p.ld_acc = ld_in;
     p.out = static_cast<__half *>(out);
     p.ld_out = ld_out;
     p.signs_out = static_cast<const __half *>(signs_out);
@@ -205,11 +208,30 @@ extern "C" int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64
     p.n = n;
     p.block = block;
     p.chunk = chunk;
-    p.clear = clear;
+    p.clear = acc ? clear : 0;
     p.scale_out = scale_out * hadamard_norm(block);
     p.scale_in = scale_in * hadamard_norm(block);
+    if (block <= 256 && n > 256) {      // a warp per 256 columns, eight warps per CTA
+        p.chunk = 2048;
+        return launch(swiglu_hadamard_kernel, dim3((unsigned)((n + 2047) / 2048), (unsigned)rows), dim3(256), 0,
+                      static_cast<cudaStream_t>(stream), p);
+    }
     return launch(swiglu_hadamard_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0,
                   static_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int rptc_swiglu_hadamard(float *acc, int64_t ld_acc, void *out, int64_t ld_out, const void *signs_out,
+                                    const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in,
+                                    int clear, rptc_stream_t stream) {
+    if (!acc) return RPTC_ERR_ARG;
+    return swiglu_launch(acc, nullptr, ld_acc, out, ld_out, signs_out, signs_in, rows, n, block, scale_out, scale_in, clear, stream);
+}
+
+extern "C" int rptc_swiglu_hadamard_f16(const void *gate_up, int64_t ld_in, void *out, int64_t ld_out, const void *signs_out,
+                                        const void *signs_in, int64_t rows, int64_t n, int block, float scale_out, float scale_in,
+                                        rptc_stream_t stream) {
+    if (!gate_up) return RPTC_ERR_ARG;
+    return swiglu_launch(nullptr, gate_up, ld_in, out, ld_out, signs_out, signs_in, rows, n, block, scale_out, scale_in, 0, stream);
 }
 
 extern "C" int rptc_finish_norm_hadamard(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, void *h, int64_t ld_h,

@@ -108,6 +108,18 @@ class RPTCLinear(nn.Module):
             ops.gemv_finish(acc, out, self.out_features, scale=self.scale, clear=True)
         return out
 
+    def product_t(self, xt: torch.Tensor) -> torch.Tensor:
+        """W_hat xt for already-transformed activations xt fp16 [rows > 8, in]: the tensor-core GEMM, unscaled and
+        before the output transform."""
+        return ops.gemm(self.codes, self.lut, xt, self.out_features, self.in_features, self.fmt, carry_in=self.carry_in)
+
+    def finish_t(self, y: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Output side of `product_t`: s_out * H(y) * scale (+ residual), fp16."""
+        if self.incoherent:
+            return ops.hadamard(y, self.signs_out, self.block_out, transpose=True, scale=self.scale, residual=residual)
+        y = y * self.scale if self.scale != 1.0 else y
+        return y if residual is None else y + residual
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, self.in_features).to(torch.float16).contiguous()

@@ -460,11 +460,22 @@ class RPTCLlama:
             self.vcache[i][:, :T] = v
             att = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                                    is_causal=True, enable_gqa=self.heads_l != self.kv_heads_l)
-            h = h + reduce(b.o(att.transpose(1, 2).reshape(R * T, q_dim)))
+            att = att.transpose(1, 2).reshape(R * T, q_dim)
+            fused = b.o.incoherent and R * T > 8 and self.tp_world == 1       # residual and SwiGLU inside the glue kernels
+            if fused:
+                h = b.o.finish_t(b.o.product_t(b.o.transform_in(att)), residual=h)
+            else:
+                h = h + reduce(b.o(att))
             ops.rmsnorm(h, b.norm2, xn, cfg.rms_eps)
-            gu = b.gate_up(xn)
-            mlp = torch.nn.functional.silu(gu[:, : self.ffn_l]).mul_(gu[:, self.ffn_l:])          # fp32 inside, fp16 in and out
-            h = h + reduce(b.down(mlp))
+            if fused:
+                gu = b.gate_up.product_t(b.gate_up.transform_in(xn))                  # before gate-up's output transform
+                mlp_t = ops.swiglu_hadamard_f16(gu, torch.empty((R * T, self.ffn_l), dtype=torch.float16, device=self.device),
+                                                b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in, b.gate_up.scale)
+                h = b.down.finish_t(b.down.product_t(mlp_t), residual=h)
+            else:
+                gu = b.gate_up(xn)
+                mlp = torch.nn.functional.silu(gu[:, : self.ffn_l]).mul_(gu[:, self.ffn_l:])      # fp32 inside, fp16 in and out
+                h = h + reduce(b.down(mlp))
         last = h.reshape(R, T, cfg.hidden)[:, -1].contiguous()
         ops.rmsnorm(last, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)

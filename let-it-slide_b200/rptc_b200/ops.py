@@ -202,6 +202,17 @@ def swiglu_hadamard(acc: torch.Tensor, out: torch.Tensor, signs_out: torch.Tenso
     return out
 
 
+def swiglu_hadamard_f16(gate_up: torch.Tensor, out: torch.Tensor, signs_out: torch.Tensor | None, signs_in: torch.Tensor | None,
+                        n: int, block: int, scale_out: float, scale_in: float = 1.0) -> torch.Tensor:
+    """Fused gated-MLP middle from the fp16 output of a matrix product (rptc_swiglu_hadamard_f16):
+    gate_up fp16 [rows, 2n] -> out fp16 [rows, n]."""
+    with torch.cuda.device(gate_up.device):
+        check(lib().rptc_swiglu_hadamard_f16(ptr(gate_up), _ld(gate_up, 2 * n), ptr(out), _ld(out, n), ptr(signs_out), ptr(signs_in),
+                                             gate_up.shape[0], n, block, scale_out, scale_in, stream_ptr()),
+              "rptc_swiglu_hadamard_f16")
+    return out
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float) -> torch.Tensor:
     rows, n = x.shape
     with torch.cuda.device(x.device):
