@@ -208,6 +208,10 @@ int rptc_rmsnorm(const void *x, int64_t ld_x, const void *w, void *out, int64_t 
  * q in place, rotated k and v appended to caches [rows][max_pos][hkv][d] at pos[row]. */
 int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, void *kcache, void *vcache, int64_t rows, int hq, int hkv,
                     int d, int max_pos, float theta, rptc_stream_t stream);
+/* The same for a whole prompt: qkv fp16 [rows * tokens][ld_qkv], token t of row r in row r * tokens + t, written to
+ * cache positions 0 .. tokens-1. */
+int rptc_rope_cache_prompt(void *qkv, int64_t ld_qkv, int64_t rows, int64_t tokens, void *kcache, void *vcache, int hq, int hkv,
+                           int d, int max_pos, float theta, rptc_stream_t stream);
 /* Single-query attention of each row's q heads over cache positions [0, pos[row]]; d must be 128.
  * signs_in (fp16 [hq*128] or NULL): when given, each head's output is also put through the input-side
  * transform of the output projection with one 128-wide Hadamard block per head, H(s * o) / sqrt(128). */

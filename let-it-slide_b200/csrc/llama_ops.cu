@@ -87,6 +87,34 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     }
 }
 
+// The same for a whole prompt: one CTA per (position, row) takes all heads of its token, so the rotation angles of a
+// position are computed once per pair index instead of once per head.  Token t of row r sits in row r * T + t of qkv.
+__global__ void __launch_bounds__(256) rope_cache_prompt_kernel(__half *__restrict__ qkv, int64_t ld_qkv, __half *__restrict__ kcache,
+                                                               __half *__restrict__ vcache, int hq, int hkv, int d, int max_pos,
+                                                               float theta) {
+    const int p = blockIdx.x, row = blockIdx.y, T = gridDim.x;
+    const int half_d = d / 2, i = threadIdx.x % 64, grp = threadIdx.x / 64;      // pair index, head group (4 groups)
+    if (i >= half_d) return;
+    float sn, cs;
+    sincosf(p * __powf(theta, -2.f * i / d), &sn, &cs);
+    __half *tok = qkv + ((int64_t)row * T + p) * ld_qkv;
+    for (int head = grp; head < hq + 2 * hkv; head += 4) {
+        __half *src = tok + (int64_t)head * d;
+        const __half ra = src[i], rb = src[i + half_d];
+        if (head < hq + hkv) {
+            const float a = __half2float(ra), b = __half2float(rb);
+            const __half lo = __float2half_rn(a * cs - b * sn), hi = __float2half_rn(b * cs + a * sn);
+            __half *dst = head < hq ? src : kcache + (((int64_t)row * max_pos + p) * hkv + (head - hq)) * d;
+            dst[i] = lo;
+            dst[i + half_d] = hi;
+        } else {
+            __half *dst = vcache + (((int64_t)row * max_pos + p) * hkv + (head - hq - hkv)) * d;
+            dst[i] = ra;
+            dst[i + half_d] = rb;
+        }
+    }
+}
+
 // Single-query attention over the cache: one CTA of 512 threads per (row, q head); d == 128.
 // One trip to memory: every warp fetches the K AND V rows of its positions (16 of each in flight, positions
 // interleaved over the 16 warps) before anything that depends on the kernel in front, then keeps a running
@@ -532,4 +560,17 @@ extern "C" int rptc_embed_mailbox(const void *table, const uint64_t *slots, uint
     return launch(embed_mailbox_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __half *>(table),
                   reinterpret_cast<const unsigned long long *>(slots), steps_done, ids, static_cast<__half *>(out), ld_out, (int)rows,
                   (int)n, vocab, (unsigned long long)timeout_ms * 1000000ull, status);
+}
+
+extern "C" int rptc_rope_cache_prompt(void *qkv, int64_t ld_qkv, int64_t rows, int64_t tokens, void *kcache, void *vcache, int hq,
+                                      int hkv, int d, int max_pos, float theta, rptc_stream_t stream) {
+    if (!qkv || !kcache || !vcache) return RPTC_ERR_ARG;
+    if (rows <= 0 || rows > 65535 || tokens <= 0 || tokens > 65535 || tokens > max_pos || hq <= 0 || hkv <= 0 || (hq % hkv) ||
+        d <= 0 || (d % 2) || d > 128)
+        return RPTC_ERR_SHAPE;
+    if (ld_qkv < (int64_t)(hq + 2 * hkv) * d) return RPTC_ERR_SHAPE;
+    if (int e = rptc_check_device()) return e;
+    return launch(rope_cache_prompt_kernel, dim3((unsigned)tokens, (unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                  static_cast<__half *>(qkv), ld_qkv, static_cast<__half *>(kcache), static_cast<__half *>(vcache), hq, hkv, d, max_pos,
+                  theta);
 }

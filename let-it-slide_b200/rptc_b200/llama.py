@@ -426,22 +426,16 @@ class RPTCLlama:
         """Pushes a whole prompt `tokens` [rows, T] through the network in one pass: every block linear runs as the
         fused dequant-GEMM on the tensor cores (rows x T tokens at once), the KV caches are filled for positions
         0..T-1, `pos` is set to T and `ids` to the greedy choice after the last prompt token.  Returns the logits of
-        the last position, fp16 [rows, vocab].  Attention over the prompt is torch's scaled_dot_product_attention
-        and the elementwise steps between the GEMMs are torch ops; decoding continues with `step`."""
+        the last position, fp16 [rows, vocab].  Attention over the prompt is torch's scaled_dot_product_attention;
+        norms, transforms, RoPE + cache writes, residual adds and the gated-MLP middle are this library's glue
+        kernels; decoding continues with `step`."""
         cfg = self.cfg
         R, T = tokens.shape
         if R != self.rows or T > cfg.max_pos:
             raise ValueError("tokens must be [rows, T] with T <= max_pos")
-        D, half = cfg.head_dim, cfg.head_dim // 2
-        q_dim, kv_dim = self.heads_l * D, self.kv_heads_l * D
+        D = cfg.head_dim
+        q_dim = self.heads_l * D
         h = self.embed[tokens.long()].reshape(R * T, cfg.hidden)                     # fp16 residual stream
-        inv = cfg.rope_theta ** (-torch.arange(half, device=self.device, dtype=torch.float32) * 2 / D)
-        ang = torch.arange(T, device=self.device, dtype=torch.float32)[:, None] * inv[None, :]
-        cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
-
-        def rope(x):                                                                # [R, T, heads, D], rotate-half pairs
-            a, b = x[..., :half].float(), x[..., half:].float()
-            return torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1).to(torch.float16)
 
         def reduce(y):
             if self.tp_world > 1:
@@ -452,12 +446,10 @@ class RPTCLlama:
         xn = torch.empty_like(h)
         for i, b in enumerate(self.blocks):
             ops.rmsnorm(h, b.norm1, xn, cfg.rms_eps)
-            qkv = b.qkv(xn).reshape(R, T, -1)
-            q = rope(qkv[..., :q_dim].reshape(R, T, self.heads_l, D))
-            k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(R, T, self.kv_heads_l, D))
-            v = qkv[..., q_dim + kv_dim:].reshape(R, T, self.kv_heads_l, D)
-            self.kcache[i][:, :T] = k
-            self.vcache[i][:, :T] = v
+            qkv = b.qkv(xn)
+            ops.rope_cache_prompt(qkv, R, T, self.kcache[i], self.vcache[i], self.heads_l, self.kv_heads_l, D, cfg.rope_theta)
+            q = qkv[:, :q_dim].reshape(R, T, self.heads_l, D)                        # rotated in place
+            k, v = self.kcache[i][:, :T], self.vcache[i][:, :T]
             att = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                                    is_causal=True, enable_gqa=self.heads_l != self.kv_heads_l)
             att = att.transpose(1, 2).reshape(R * T, q_dim)

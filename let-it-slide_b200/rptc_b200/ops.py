@@ -228,6 +228,15 @@ def rope_cache(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcach
                                     kcache.shape[1], theta, stream_ptr()), "rptc_rope_cache")
 
 
+def rope_cache_prompt(qkv: torch.Tensor, rows: int, tokens: int, kcache: torch.Tensor, vcache: torch.Tensor, hq: int, hkv: int, d: int,
+                      theta: float) -> None:
+    """RoPE of q (in place) and k, and the cache writes of k and v, for a whole prompt (rptc_rope_cache_prompt):
+    qkv fp16 [rows * tokens, (hq + 2 hkv) d]."""
+    with torch.cuda.device(qkv.device):
+        check(lib().rptc_rope_cache_prompt(ptr(qkv), _ld(qkv, qkv.shape[1]), rows, tokens, ptr(kcache), ptr(vcache), hq, hkv, d,
+                                           kcache.shape[1], theta, stream_ptr()), "rptc_rope_cache_prompt")
+
+
 def attn_decode(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, out: torch.Tensor, hq: int,
                 hkv: int, d: int, signs_in: torch.Tensor | None = None) -> torch.Tensor:
     rows = qkv.shape[0]
