@@ -42,7 +42,9 @@ __device__ __forceinline__ void store8_f16(__half *p, const float (&v)[8]) {
 
 // Unnormalised Walsh-Hadamard transform of `block`-sized blocks; thread t holds elements 8t..8t+7 of
 // the CTA's chunk.  `ex` is a shared exchange buffer of chunk floats (used when block > 256).
-__device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
+// `guard`: a barrier before the exchange buffer is written (needed unless every thread is known to have passed a
+// barrier since the buffer was last read).
+__device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex, bool guard = true) {
     const int t = threadIdx.x;
 #pragma unroll
     for (int h = 1; h < 8; h <<= 1) {
@@ -68,7 +70,7 @@ __device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex) {
         // shared memory each of the first chunk/16 threads takes the G = block/256 group values of one r,
         // transforms them in registers, and puts them back (two barriers instead of one per stride).
         const int G = block >> 8;                      // 2, 4, 8 or 16
-        __syncthreads();          // the buffer may still be read from an earlier transform
+        if (guard) __syncthreads();          // the buffer may still be read from an earlier transform
 #pragma unroll
         for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
         __syncthreads();
@@ -147,8 +149,9 @@ struct FinishNormParams {
 // One row; called by all n/8 threads of a CTA.  `owner`: this CTA is the one that clears the accumulator behind
 // its read and stores the updated residual.  When several CTAs compute the same row (each for its own use),
 // exactly one of them is the owner of the residual and nobody clears; the residual then needs h_out != h.
+// `ex_idle`: no thread can still be reading the exchange buffer when this call starts (first use in the kernel).
 __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64_t row, float *ex, float *red, bool clear_acc,
-                                                bool write_h) {
+                                                bool write_h, bool ex_idle = false) {
     const int t = threadIdx.x;
     const int col = 8 * t;
     const float hn = hadamard_norm_dev(p.block);
@@ -162,7 +165,7 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
     if (p.acc) {
         if (clear_acc) load8_f32(p.acc + row * p.ld_acc + col, v, true);
         else load8_f32_cg(p.acc + row * p.ld_acc + col, v);
-        fwht8(v, p.block, ex);
+        fwht8(v, p.block, ex, !ex_idle);
         unpack8(raw_so, sg);
         float r[8];
         unpack8(raw_h, r);
@@ -188,7 +191,7 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
         unpack8(raw_si, sg);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= sg[i];
-        fwht8(v, p.block, ex);
+        fwht8(v, p.block, ex, false);      // block_sum's barriers lie between the last reads of ex and this write
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= hn;
     }

@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 q.n = (int32_t)p.n;
                 q.block = (int32_t)p.n;
 #pragma unroll 1
-                for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
+                for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
             }
         } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
@@ -793,7 +793,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             q.n = (int32_t)p.n;
             q.block = (int32_t)p.n;
 #pragma unroll 1
-            for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0);
+            for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
         } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
             const int pairs = nu * PAIRS;

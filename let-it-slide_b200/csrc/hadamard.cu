@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(THREADS) finish_norm_hadamard_kernel(const Fin
     __shared__ float red[36];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
-    finish_norm_row(p, blockIdx.x, ex, red, true, true);
+    finish_norm_row(p, blockIdx.x, ex, red, true, true, true);
 }
 
 // Output side of the fused qkv layer, rotary embedding and KV-cache append in one pass:
