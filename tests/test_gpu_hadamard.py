@@ -108,15 +108,18 @@ def test_gemv_computing_its_own_input_matches_glue_then_gemv(batch, m, with_acc)
 
 
 @pytest.mark.parametrize("batch", [1, 2])
-@pytest.mark.parametrize("m,n,block", [(4096, 11008, 256), (4096, 1792, 256), (64, 512, 128), (1056, 2048, 64)])
-def test_down_projection_making_its_own_swiglu_input(batch, m, n, block):
+@pytest.mark.parametrize("m,n,block,code,K,S", [(4096, 11008, 256, o.CODE_B, 2, 8), (4096, 1792, 256, o.CODE_B, 2, 8),
+                                                (64, 512, 128, o.CODE_B, 2, 8), (1056, 2048, 64, o.CODE_B, 2, 8),
+                                                (1056, 2048, 256, o.CODE_A, 4, 0), (352, 1024, 256, o.CODE_C, 2, 9),
+                                                (352, 1024, 32, o.CODE_C, 4, 9), (128, 768, 256, o.CODE_A, 2, 0)])
+def test_down_projection_making_its_own_swiglu_input(batch, m, n, block, code, K, S):
     """rptc_gemv_swiglu against rptc_swiglu_hadamard followed by rptc_gemv, several calls in a row."""
     from gpu_util import rand_lut, rand_words
     from rptc_b200 import Format, ops
-    rng = np.random.default_rng(batch * 11 + m + n)
-    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
-    codes = to_dev(o.from_rowmajor(rand_words(rng, m, n, 2), o.LAYOUT_TILED))
-    lut = to_dev(rand_lut(rng, o.CODE_B, S=8))
+    rng = np.random.default_rng(batch * 11 + m + n + K)
+    fmt = Format(code, K, 16, S, o.LAYOUT_TILED)
+    codes = to_dev(o.from_rowmajor(rand_words(rng, m, n, K), o.LAYOUT_TILED))
+    lut = to_dev(rand_lut(rng, code, 16, S))
     s_out, s_in = to_dev(o.signs_from_seed(3, 2 * n).astype(np.float16)), to_dev(o.signs_from_seed(4, n).astype(np.float16))
     dirty = torch.ones(2048, dtype=torch.float32, device="cuda")
     for rep in range(3):
