@@ -143,11 +143,11 @@ class RPTCLlama:
                 and self.cfg.head_dim == 128)
 
     def _glueable(self) -> bool:
-        """The shortest chain (6 launches per block) additionally needs hidden == 4096 (eight values a thread of the
-        512-thread matvec CTA), at most two rows and multi-head attention."""
+        """The short chain (5 launches per block with multi-head attention, 6 with grouped-query attention)
+        additionally needs hidden == 4096 (eight values a thread of the 512-thread matvec CTA) and at most two rows."""
         b = self.blocks[0]
-        return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and self.heads_l == self.kv_heads_l
-                and b.qkv.block_out == 128 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
+        return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and b.qkv.block_out >= 128
+                and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
 
     def _mlp_glueable(self) -> bool:
         """The down projection can make its own activations (five launches per block) when the MLP width is a whole
@@ -230,6 +230,7 @@ class RPTCLlama:
         cfg, r = self.cfg, self.rows
         self._embed_ids()
         mlp_glued = self._mlp_glueable()
+        mha = self.heads_l == self.kv_heads_l and self.blocks[0].qkv.block_out == 128
         # the launch that opens a block zeroes what the block before it left: acc_o always, acc_gu too when the down
         # projection reads it in every CTA
         stale = self._acc_pool if mlp_glued else self.acc_o
@@ -238,8 +239,14 @@ class RPTCLlama:
             ops.gemv_norm_input(b.qkv.codes, b.qkv.lut, self.acc_qkv, b.qkv.out_features, cfg.hidden, self.fmt, r,
                                 self.acc_h if prev else None, prev.signs_out if prev else None, prev.scale if prev else 1.0,
                                 self.h, self.h2, b.norm1, cfg.rms_eps, b.qkv.signs_in, clear=stale)
-            ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
-                                self.heads_l, cfg.rope_theta, b.o.signs_in)
+            if mha:
+                ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
+                                    self.heads_l, cfg.rope_theta, b.o.signs_in)
+            else:
+                ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                               self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+                ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                                cfg.head_dim, signs_in=b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_o)
             ops.gemv_norm_input(b.gate_up.codes, b.gate_up.lut, self.acc_gu, b.gate_up.out_features, cfg.hidden, self.fmt, r,
                                 self.acc_o, b.o.signs_out, b.o.scale, self.h2, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in,
@@ -256,7 +263,7 @@ class RPTCLlama:
         ops.finish_norm_hadamard(self.acc_h, last.signs_out, last.scale, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = (5 if mlp_glued else 6) * len(self.blocks) + 4
+        self.launches_per_step = ((5 if mlp_glued else 6) + (0 if mha else 1)) * len(self.blocks) + 4
 
     def _step_fused_tp(self) -> None:
         """Tensor-parallel decode step with the glue fused as far as the all-reduce allows: RMSNorm + input transform in

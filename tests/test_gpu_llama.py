@@ -71,21 +71,23 @@ def test_decode_engine_logits_match_fp32_reference(incoherent, hidden, ffn, kv_h
     ops.device_status()
 
 
+@pytest.mark.parametrize("kv_heads", [32, 8])
 @pytest.mark.parametrize("rows", [1, 2])
-def test_short_chains_match_reference_and_separate_glue(rows):
+def test_short_chains_match_reference_and_separate_glue(rows, kv_heads):
     """hidden 4096, multi-head: the qkv and gate-up matvecs compute their activations from the previous accumulator
     (six launches per block), and the down projection makes its SwiGLU input itself (five)."""
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
-    cfg = LlamaConfig(hidden=4096, layers=3, heads=32, kv_heads=32, ffn=1792, vocab=512, max_pos=16, weight_scale=0.02)
+    cfg = LlamaConfig(hidden=4096, layers=3, heads=32, kv_heads=kv_heads, ffn=1792, vocab=512, max_pos=16, weight_scale=0.02)
     T = 6
     model = RPTCLlama(cfg, rows=rows, seed=3)
     assert model._glueable() and model._mlp_glueable()
+    gqa = 0 if kv_heads == 32 else 1           # grouped-query attention keeps the q/k/v finish in a launch of its own
     g = torch.Generator(device="cuda").manual_seed(5)
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
     logits = {}
-    for launches, glued, glued_mlp in ((8, False, False), (6, True, False), (5, True, True)):
+    for launches, glued, glued_mlp in ((8 + gqa, False, False), (6 + gqa, True, False), (5 + gqa, True, True)):
         model.glued, model.glued_mlp = glued, glued_mlp
         for use_graph in (False, True):
             model.reset()
@@ -107,11 +109,11 @@ def test_short_chains_match_reference_and_separate_glue(rows):
             ops.embed(model.embed, model.ids, model.h)        # any launch after the step: orders the check below
             torch.cuda.synchronize()
             assert not model.acc_qkv.any() and not model.acc_h.any()
-            assert launches == 5 or not model.acc_gu.any()    # five launches: left to the next token's first launch
+            assert glued_mlp or not model.acc_gu.any()        # otherwise left to the next token's first launch
     for t in range(T):
         scale = ref[:, t].abs().max().item()
-        for launches in (6, 5):
-            assert (logits[launches, True, t] - logits[8, True, t]).abs().max().item() <= 4e-3 * scale
+        for launches in (6 + gqa, 5 + gqa):
+            assert (logits[launches, True, t] - logits[8 + gqa, True, t]).abs().max().item() <= 4e-3 * scale
 
 
 def test_next_token_kernel_matches_argmax():
