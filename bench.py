@@ -306,7 +306,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
 
 WORKLOADS = {
     "llama2-7b-decode-bs1": (dict(), dict(hidden=4096, ffn=11008, layers=32, heads=32, kv_heads=32)),
-    # the partitioned shape: tensor-parallel over all ranks (strong scaling), NCCL all-reduce after o and down
+    # the partitioned shape: tensor-parallel over all ranks (strong scaling), one all-reduce after o and down (--allreduce)
     "llama2-70b-tp": (dict(hidden=8192, layers=80, heads=64, kv_heads=8, ffn=28672),
                       dict(hidden=8192, ffn=28672, layers=80, heads=64, kv_heads=8)),
 }

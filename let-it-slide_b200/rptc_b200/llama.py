@@ -136,7 +136,7 @@ class RPTCLlama:
 
     # -- one token for every row ---------------------------------------------------------------------
     def _fusable(self) -> bool:
-        """The short chain (9 launches per block) needs incoherent layers, no tensor parallelism, and a
+        """The fused chain (8 launches per block) needs incoherent layers, no tensor parallelism, and a
         hidden size that is a single Hadamard block."""
         n = self.cfg.hidden
         return (self.tp_world == 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 4096
