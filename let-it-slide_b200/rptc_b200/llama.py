@@ -119,7 +119,7 @@ class RPTCLlama:
         self._acc_pool = torch.zeros(rows * (cfg.hidden + 2 * self.ffn_l), **f32)
         self.acc_o = self._acc_pool[: rows * cfg.hidden].view(rows, cfg.hidden)
         self.acc_gu = self._acc_pool[rows * cfg.hidden:].view(rows, 2 * self.ffn_l)
-        self.acc_gu2 = torch.zeros_like(self.acc_gu) if tp_world > 1 else None     # see _step_fused_tp
+        self.acc_gu2 = torch.zeros_like(self.acc_gu)     # second gate-up accumulator of the chains that alternate two
         self.peer = None
         if tp_world > 1 and peer_allreduce and incoherent:
             # the fused transform + all-reduce + residual kernel over NVLink peer memory instead of NCCL
@@ -137,9 +137,9 @@ class RPTCLlama:
     # -- one token for every row ---------------------------------------------------------------------
     def _fusable(self) -> bool:
         """The fused chain (8 launches per block) needs incoherent layers, no tensor parallelism, and a
-        hidden size that is a single Hadamard block."""
+        hidden size that is a single Hadamard block (or two of 4096)."""
         n = self.cfg.hidden
-        return (self.tp_world == 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 4096
+        return (self.tp_world == 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 8192
                 and self.cfg.head_dim == 128)
 
     def _glueable(self) -> bool:
@@ -193,6 +193,8 @@ class RPTCLlama:
         xt = self.xt[:, : cfg.hidden]
         ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
         n_launch = 2
+        mlp_glued = (self._mlp_glueable() and self.rows <= 2 and len(self.blocks) % 2 == 0 and self.fmt.layout == LAYOUT_TILED
+                     and self.fmt.K in (2, 4))
         for i, b in enumerate(self.blocks):
             b.qkv.matvec_acc(xt, self.acc_qkv)
             if self.heads_l == self.kv_heads_l and b.qkv.block_out == 128:
@@ -206,10 +208,20 @@ class RPTCLlama:
                                 cfg.head_dim, signs_in=b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_h)
             ops.finish_norm_hadamard(self.acc_h, b.o.signs_out, b.o.scale, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in, True, xt)
-            b.gate_up.matvec_acc(xt, self.acc_gu)
-            ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
-                                b.gate_up.scale, 1.0, clear=True)
-            b.down.matvec_acc(self.mlp, self.acc_h)
+            if mlp_glued:
+                # the down projection makes its SwiGLU input itself; two gate-up accumulators alternate from block to
+                # block and each down projection zeroes the one the block before it used
+                gu, other = (self.acc_gu, self.acc_gu2) if i % 2 == 0 else (self.acc_gu2, self.acc_gu)
+                b.gate_up.matvec_acc(xt, gu)
+                ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, self.rows, gu,
+                                      b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in, clear=other,
+                                      carry_in=b.down.carry_in)
+                n_launch -= 1
+            else:
+                b.gate_up.matvec_acc(xt, self.acc_gu)
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                    b.gate_up.scale, 1.0, clear=True)
+                b.down.matvec_acc(self.mlp, self.acc_h)
             if i + 1 < len(self.blocks):
                 nb = self.blocks[i + 1]
                 ops.finish_norm_hadamard(self.acc_h, b.down.signs_out, b.down.scale, self.h, nb.norm1, cfg.rms_eps,
@@ -415,8 +427,7 @@ class RPTCLlama:
     def reset(self, ids: torch.Tensor | None = None) -> None:
         self.pos.zero_()
         self._acc_pool.zero_()      # the short chain leaves acc_o / acc_gu to the next token's first launch
-        if self.acc_gu2 is not None:
-            self.acc_gu2.zero_()
+        self.acc_gu2.zero_()
         if ids is not None:
             self.ids.copy_(ids.to(torch.int32))
 
