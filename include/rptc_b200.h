@@ -116,7 +116,7 @@ int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, cons
 /* rptc_gemv whose activations are not read from memory but computed, by every CTA for itself, from what the
  * previous layer of a decoder block left behind: the glue between the two layers then costs no launch of its own.
  *   h' = h_in + s_out * H(acc) * scale_out;   x = H(s_in * rmsnorm(h') * w_norm)
- * (what rptc_finish_norm_hadamard computes; n must be 4096, one Hadamard block).  CTA 0 stores h' to h_out,
+ * (what rptc_finish_norm_hadamard computes; n must be 4096 or 8192: one or two 4096-point Hadamard blocks).  CTA 0 stores h' to h_out,
  * which must not alias h_in (other CTAs still read h_in).  `acc` is read by every CTA and therefore not cleared
  * here: name it as `clear` in a LATER launch of the same stream (a launch zeroes its own `clear` range once the
  * launches before it have completed).  TILED layout, no quirk, batch 1-2.  No reference counterpart (the

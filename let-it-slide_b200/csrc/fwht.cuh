@@ -198,6 +198,59 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
     store8_f16(p.out + row * p.ld_out + col, v);
 }
 
+// The same for a row of NH x 4096 elements handled by 512 threads (thread t holds elements 8t..8t+7 of every 4096-wide
+// piece; each piece is one Hadamard block): the form used inside a 512-thread matvec CTA for 8192-wide models.  Never
+// clears the accumulator (several CTAs read it); p.block must be 4096.
+template <int NH>
+__device__ __forceinline__ void finish_norm_row_wide(const FinishNormParams &p, int64_t row, float *ex, float *red, bool write_h,
+                                                     bool ex_idle) {
+    const int t = threadIdx.x;
+    const float hn = hadamard_norm_dev(4096);
+    float v[NH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+        const int col = hf * 4096 + 8 * t;
+        const uint4 raw_h = __ldcg(reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col));
+        if (p.acc) {
+            const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
+            load8_f32_cg(p.acc + row * p.ld_acc + col, v[hf]);
+            fwht8(v[hf], 4096, ex, !(ex_idle && hf == 0));
+            float sg[8], r[8];
+            unpack8(raw_so, sg);
+            unpack8(raw_h, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[hf][i] = r[i] + v[hf][i] * (p.scale_out * hn) * sg[i];
+            if (write_h) store8_f16((p.h_out ? p.h_out : p.h) + row * p.ld_h + col, v[hf]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[hf][i] = __half2float(__float2half_rn(v[hf][i]));
+        } else {
+            if (write_h && p.h_out) *reinterpret_cast<uint4 *>(p.h_out + row * p.ld_h + col) = raw_h;
+            unpack8(raw_h, v[hf]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[hf][i] * v[hf][i];
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / p.n + p.eps);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+        const int col = hf * 4096 + 8 * t;
+        float w[8], sg[8];
+        unpack8(*reinterpret_cast<const uint4 *>(p.w_norm + col), w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[hf][i] = __half2float(__float2half_rn(v[hf][i] * inv * w[i]));
+        if (p.transform_in) {
+            unpack8(raw8_or_ones(p.signs_in ? p.signs_in + col : nullptr), sg);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[hf][i] *= sg[i];
+            fwht8(v[hf], 4096, ex, hf != 0);      // before piece 0: block_sum's barriers; later pieces: the transform before
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[hf][i] *= hn;
+        }
+        store8_f16(p.out + row * p.ld_out + col, v[hf]);
+    }
+}
+
 // Fused MLP middle: gate/up pre-activations arrive as the fp32 accumulator of the fused gate-up
 // layer (gate in columns [0, n), up in [n, 2n)).  out = H (s_in * (silu(g) * u)) * scale_in with
 // g, u = s_out * (H acc) * scale_out.  Both transforms use the same block size, so one CTA owns

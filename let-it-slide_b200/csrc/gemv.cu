@@ -312,9 +312,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 q.out = x_sm;
                 q.ld_out = x_batch_stride >> 1;
                 q.n = (int32_t)p.n;
-                q.block = (int32_t)p.n;
+                q.block = 4096;
 #pragma unroll 1
-                for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+                for (int b = 0; b < BATCH; ++b) {
+                    if (p.n == 4096) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+                    else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
+                }
             }
         } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
@@ -791,9 +794,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             q.out = reinterpret_cast<__half *>(smem_raw + (xs - s0));
             q.ld_out = x_batch_stride >> 1;
             q.n = (int32_t)p.n;
-            q.block = (int32_t)p.n;
+            q.block = 4096;
 #pragma unroll 1
-            for (int b = 0; b < BATCH; ++b) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+            for (int b = 0; b < BATCH; ++b) {
+                    if (p.n == 4096) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+                    else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
+                }
         } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
             const int pairs = nu * PAIRS;
@@ -1186,7 +1192,7 @@ extern "C" int rptc_gemv_glued(const void *codes, const void *lut, const uint32_
         misaligned(in->clear) || (in->ld_acc % 4) || (in->clear_count % 4))
         return RPTC_ERR_ALIGN;
     if (in->clear_count < 0 || (in->clear_count && !in->clear)) return RPTC_ERR_ARG;
-    if (n != 8 * kGemvThreads) return RPTC_ERR_UNSUPPORTED;                     // one 4096-point block, eight values a thread
+    if (n != 4096 && n != 8192) return RPTC_ERR_UNSUPPORTED;                    // one or two 4096-point blocks, eight values a thread each
     if (!in->h_in || !in->h_out || in->h_in == in->h_out || !in->w_norm) return RPTC_ERR_ARG;
     if (in->ld_h < n || (in->acc && in->ld_acc < n)) return RPTC_ERR_SHAPE;
     if (misaligned(in->h_in) || misaligned(in->h_out) || misaligned(in->w_norm) || (in->ld_h % 8)) return RPTC_ERR_ALIGN;

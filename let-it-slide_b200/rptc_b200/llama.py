@@ -144,9 +144,10 @@ class RPTCLlama:
 
     def _glueable(self) -> bool:
         """The short chain (5 launches per block with multi-head attention, 6 with grouped-query attention)
-        additionally needs hidden == 4096 (eight values a thread of the 512-thread matvec CTA) and at most two rows."""
+        additionally needs hidden 4096 or 8192 (one or two 4096-point blocks, eight values a thread of the 512-thread
+        matvec CTA each) and at most two rows."""
         b = self.blocks[0]
-        return (self._fusable() and self.cfg.hidden == 4096 and self.rows <= 2 and b.qkv.block_out >= 128
+        return (self._fusable() and self.cfg.hidden in (4096, 8192) and self.rows <= 2 and b.qkv.block_out >= 128
                 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4) and self.glued)
 
     def _mlp_glueable(self) -> bool:

@@ -139,3 +139,34 @@ def test_down_projection_making_its_own_swiglu_input(batch, m, n, block, code, K
         # tensor-core kernel on the other side
         scale = acc_a.abs().max().item()
         assert (acc_b - acc_a).abs().max().item() <= (1e-4 if batch == 1 else 2e-3) * scale
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("with_acc", [True, False])
+def test_gemv_computing_its_own_input_from_8192_wide_rows(batch, with_acc):
+    """rptc_gemv_glued with n = 8192 (two 4096-point blocks per row) against the separate glue kernel + rptc_gemv."""
+    from gpu_util import rand_lut, rand_words
+    from rptc_b200 import Format, ops
+    rng = np.random.default_rng(batch * 5 + with_acc)
+    m, n = 1280, 8192
+    fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
+    codes = to_dev(o.from_rowmajor(rand_words(rng, m, n, 2), o.LAYOUT_TILED))
+    lut = to_dev(rand_lut(rng, o.CODE_B, S=8))
+    w_norm = to_dev((1 + 0.1 * rng.standard_normal(n)).astype(np.float16))
+    s_out, s_in = to_dev(o.signs_from_seed(7, n).astype(np.float16)), to_dev(o.signs_from_seed(8, n).astype(np.float16))
+    for rep in range(2):
+        prev = to_dev(rng.standard_normal((batch, n)).astype(np.float32)) if with_acc else None
+        h0 = to_dev(rng.standard_normal((batch, n)).astype(np.float16))
+        h_a, x_a = h0.clone(), torch.empty_like(h0)
+        acc_a = torch.zeros(batch, m, dtype=torch.float32, device="cuda")
+        ops.finish_norm_hadamard(prev.clone() if with_acc else None, s_out, 0.3, h_a, w_norm, 1e-5, s_in, True, x_a)
+        ops.gemv_acc(codes, lut, x_a, acc_a, m, n, fmt)
+        h_b, acc_b = torch.full_like(h0, float("nan")), torch.zeros_like(acc_a)
+        ops.gemv_norm_input(codes, lut, acc_b, m, n, fmt, batch, prev, s_out, 0.3, h0, h_b, w_norm, 1e-5, s_in)
+        torch.cuda.synchronize()
+        ops.device_status()
+        assert torch.equal(h_b, h_a)
+        scale = acc_a.abs().max().item()
+        # the sum of squares is accumulated in a different order (16 values a thread instead of 8), so activations can
+        # differ by an fp16 ulp
+        assert (acc_b - acc_a).abs().max().item() <= 2e-3 * scale

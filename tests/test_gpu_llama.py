@@ -74,18 +74,20 @@ def test_decode_engine_logits_match_fp32_reference(incoherent, hidden, ffn, kv_h
     ops.device_status()
 
 
-@pytest.mark.parametrize("kv_heads", [32, 8])
+@pytest.mark.parametrize("hidden,kv_heads", [(4096, 32), (4096, 8), (8192, 8)])
 @pytest.mark.parametrize("rows", [1, 2])
-def test_short_chains_match_reference_and_separate_glue(rows, kv_heads):
-    """hidden 4096, multi-head: the qkv and gate-up matvecs compute their activations from the previous accumulator
-    (six launches per block), and the down projection makes its SwiGLU input itself (five)."""
+def test_short_chains_match_reference_and_separate_glue(rows, hidden, kv_heads):
+    """hidden 4096 / 8192: the qkv and gate-up matvecs compute their activations from the previous accumulator (six
+    launches per block), and the down projection makes its SwiGLU input itself (five); one more with grouped-query
+    attention."""
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
-    cfg = LlamaConfig(hidden=4096, layers=4, heads=32, kv_heads=kv_heads, ffn=1792, vocab=512, max_pos=16, weight_scale=0.02)
+    cfg = LlamaConfig(hidden=hidden, layers=4, heads=hidden // 128, kv_heads=kv_heads, ffn=1792, vocab=512, max_pos=16,
+                      weight_scale=0.02 if hidden == 4096 else 0.014)
     T = 6
     model = RPTCLlama(cfg, rows=rows, seed=3)
     assert model._glueable() and model._mlp_glueable()
-    gqa = 0 if kv_heads == 32 else 1           # grouped-query attention keeps the q/k/v finish in a launch of its own
+    gqa = 0 if kv_heads == hidden // 128 else 1           # grouped-query attention keeps the q/k/v finish in a launch of its own
     g = torch.Generator(device="cuda").manual_seed(5)
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
