@@ -128,6 +128,7 @@ class RPTCLlama:
         self.glued = True           # False keeps the glue in launches of its own (the 8-launch chain)
         self.fused_tp = True        # False: the 15-launch chain under tensor parallelism
         self.glued_mlp = True       # False: SwiGLU in a launch of its own inside the short chain
+        self.glued_tp = True        # False: RMSNorm + input transform of the tensor-parallel chain in launches of their own
         self.host_ids: torch.Tensor | None = None      # see bind_host_io
         self.host_next: torch.Tensor | None = None
         self.mailbox = None                            # see bind_mailbox
@@ -286,10 +287,19 @@ class RPTCLlama:
         xt = self.xt[:, : cfg.hidden]
         self._embed_ids()
         b0 = self.blocks[0]
-        ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
         per_reduce = 1 if self.peer is not None else 3
-        mlp_glued = (self._mlp_glueable() and self.rows <= 2 and len(self.blocks) % 2 == 0 and self.fmt.layout == LAYOUT_TILED
-                     and self.fmt.K in (2, 4))
+        native = self.rows <= 2 and self.fmt.layout == LAYOUT_TILED and self.fmt.K in (2, 4)
+        mlp_glued = self._mlp_glueable() and native and len(self.blocks) % 2 == 0
+        # RMSNorm + input transform inside the matvec that consumes them (the all-reduce has already updated h)
+        norm_glued = self.glued_tp and native and cfg.hidden in (4096, 8192)
+
+        def normed_matvec(lin, w_norm, acc):
+            ops.gemv_norm_input(lin.codes, lin.lut, acc, lin.out_features, cfg.hidden, self.fmt, self.rows, None, None, 1.0,
+                                self.h, self.h2, w_norm, cfg.rms_eps, lin.signs_in, carry_in=lin.carry_in)
+
+        if norm_glued:
+            return self._step_fused_tp_glued(normed_matvec, mlp_glued, per_reduce)
+        ops.finish_norm_hadamard(None, None, 1.0, self.h, b0.norm1, cfg.rms_eps, b0.qkv.signs_in, True, xt)
         for i, b in enumerate(self.blocks):
             b.qkv.matvec_acc(xt, self.acc_qkv)
             ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
@@ -322,6 +332,35 @@ class RPTCLlama:
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
         self.launches_per_step = ((8 if mlp_glued else 9) + 2 * per_reduce) * len(self.blocks) + 4
+
+    def _step_fused_tp_glued(self, normed_matvec, mlp_glued: bool, per_reduce: int) -> None:
+        """The tensor-parallel chain with the norms inside the matvecs: qkv* -> q/k/v finish -> attention -> o ->
+        all-reduce -> gate-up* -> down (SwiGLU inside or in front) -> all-reduce."""
+        cfg = self.cfg
+        for i, b in enumerate(self.blocks):
+            normed_matvec(b.qkv, b.norm1, self.acc_qkv)
+            ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                           self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                            cfg.head_dim, signs_in=b.o.signs_in)
+            b.o.matvec_acc(self.attn, self.acc_h)
+            self._finish_row_parallel(b.o)
+            if mlp_glued:
+                gu, other = (self.acc_gu, self.acc_gu2) if i % 2 == 0 else (self.acc_gu2, self.acc_gu)
+                normed_matvec(b.gate_up, b.norm2, gu)
+                ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, self.rows, gu,
+                                      b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in, clear=other,
+                                      carry_in=b.down.carry_in)
+            else:
+                normed_matvec(b.gate_up, b.norm2, self.acc_gu)
+                ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
+                                    b.gate_up.scale, 1.0, clear=True)
+                b.down.matvec_acc(self.mlp, self.acc_h)
+            self._finish_row_parallel(b.down)
+        ops.finish_norm_hadamard(None, None, 1.0, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
+        ops.dense_gemv(self.head, self.xn, out=self.logits)
+        self._next_token()
+        self.launches_per_step = ((6 if mlp_glued else 7) + 2 * per_reduce) * len(self.blocks) + 4
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows
