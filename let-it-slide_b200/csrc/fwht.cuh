@@ -150,8 +150,14 @@ struct FinishNormParams {
 // its read and stores the updated residual.  When several CTAs compute the same row (each for its own use),
 // exactly one of them is the owner of the residual and nobody clears; the residual then needs h_out != h.
 // `ex_idle`: no thread can still be reading the exchange buffer when this call starts (first use in the kernel).
+struct NoHook {
+    __device__ __forceinline__ void operator()() const {}
+};
+// `after_loads`: called once the row's global loads have been issued and before their values are used -- a place for
+// work that should overlap the loads' trip through L2 (e.g. writing a lookup table to shared memory).
+template <typename Hook = NoHook>
 __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64_t row, float *ex, float *red, bool clear_acc,
-                                                bool write_h, bool ex_idle = false) {
+                                                bool write_h, bool ex_idle = false, Hook after_loads = Hook()) {
     const int t = threadIdx.x;
     const int col = 8 * t;
     const float hn = hadamard_norm_dev(p.block);
@@ -165,6 +171,9 @@ __device__ __forceinline__ void finish_norm_row(const FinishNormParams &p, int64
     if (p.acc) {
         if (clear_acc) load8_f32(p.acc + row * p.ld_acc + col, v, true);
         else load8_f32_cg(p.acc + row * p.ld_acc + col, v);
+    }
+    after_loads();
+    if (p.acc) {
         fwht8(v, p.block, ex, !ex_idle);
         unpack8(raw_so, sg);
         float r[8];

@@ -283,7 +283,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
-            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);      // the codebook loads were issued before the wait
+            // the codebook loads were issued before the wait; with computed activations the table is written while the
+            // glue's own loads are in flight (below)
+            if (INPUT == 0 || p.n != 4096) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
         }
         if (useg0 > 0) __syncthreads();
         if (INPUT != 0) {
@@ -315,7 +317,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 q.block = 4096;
 #pragma unroll 1
                 for (int b = 0; b < BATCH; ++b) {
-                    if (p.n == 4096) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+                    if (p.n == 4096)
+                        finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, [&]() {
+                            if (b == 0) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                        });
                     else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
                 }
             }
@@ -767,7 +772,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
-            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);      // the codebook loads were issued before the wait
+            // the codebook loads were issued before the wait; with computed activations the table is written while the
+            // glue's own loads are in flight (below)
+            if (INPUT == 0 || p.n != 4096) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
         }
         if (useg0 > 0) __syncthreads();
         if (INPUT != 0) {
@@ -797,7 +804,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             q.block = 4096;
 #pragma unroll 1
             for (int b = 0; b < BATCH; ++b) {
-                    if (p.n == 4096) finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0);
+                    if (p.n == 4096)
+                        finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, [&]() {
+                            if (b == 0) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                        });
                     else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
                 }
         } else {
