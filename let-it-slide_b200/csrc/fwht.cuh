@@ -4,6 +4,10 @@
 
 namespace rptc {
 
+struct NoHook {      // default of the `after_loads` hooks below
+    __device__ __forceinline__ void operator()() const {}
+};
+
 __device__ __forceinline__ void load8_f16(const __half *p, float (&v)[8]) {
     const uint4 a = *reinterpret_cast<const uint4 *>(p);
     const uint32_t w[4] = {a.x, a.y, a.z, a.w};
@@ -150,9 +154,6 @@ struct FinishNormParams {
 // its read and stores the updated residual.  When several CTAs compute the same row (each for its own use),
 // exactly one of them is the owner of the residual and nobody clears; the residual then needs h_out != h.
 // `ex_idle`: no thread can still be reading the exchange buffer when this call starts (first use in the kernel).
-struct NoHook {
-    __device__ __forceinline__ void operator()() const {}
-};
 // `after_loads`: called once the row's global loads have been issued and before their values are used -- a place for
 // work that should overlap the loads' trip through L2 (e.g. writing a lookup table to shared memory).
 template <typename Hook = NoHook>
@@ -278,7 +279,9 @@ struct SwigluParams {
 };
 
 // Columns col .. col+7 of one row (thread t of the chunk holds 8t..8t+7); result to dst[0..7].
-__device__ __forceinline__ void swiglu_chunk(const SwigluParams &p, int64_t row, int64_t col, float *ex, bool clear, __half *dst) {
+template <typename Hook = NoHook>
+__device__ __forceinline__ void swiglu_chunk(const SwigluParams &p, int64_t row, int64_t col, float *ex, bool clear, __half *dst,
+                                             Hook after_loads = Hook()) {
     float g[8], u[8], sg[8];
     const uint4 raw_sg = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
     const uint4 raw_su = raw8_or_ones(p.signs_out ? p.signs_out + p.n + col : nullptr);
@@ -293,6 +296,7 @@ __device__ __forceinline__ void swiglu_chunk(const SwigluParams &p, int64_t row,
         load8_f32_cg(p.acc + row * p.ld_acc + col, g);
         load8_f32_cg(p.acc + row * p.ld_acc + p.n + col, u);
     }
+    after_loads();
     fwht8(g, p.block, ex);
     fwht8(u, p.block, ex);
     unpack8(raw_sg, sg);

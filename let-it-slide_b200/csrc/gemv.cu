@@ -552,7 +552,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
     }
 
     pdl_wait_prior_grids();
-    lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
     if (p.clear) {
         float4 *z = reinterpret_cast<float4 *>(p.clear);
         for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.clear_count; i += (int64_t)gridDim.x * kGemvThreads)
@@ -561,11 +560,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
     // ---- activations of this CTA's column blocks: one warp per block and row ----
     {
         __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+        bool table_written = false;      // the table goes to shared memory while a warp's SwiGLU loads are in flight
         for (uint32_t b = cb_first + warp; b <= cb_last; b += kGemvWarps)
 #pragma unroll 1
             for (int r = 0; r < BATCH; ++r)
                 swiglu_chunk(p.sw, r, (int64_t)b * 256 + 8 * lane, nullptr, false,
-                             x_sm + (size_t)r * (x_batch_stride >> 1) + (size_t)(b - cb_first) * 256 + 8 * lane);
+                             x_sm + (size_t)r * (x_batch_stride >> 1) + (size_t)(b - cb_first) * 256 + 8 * lane, [&]() {
+                                 if (!table_written) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                                 table_written = true;
+                             });
+        if (!table_written) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
     }
     __syncthreads();
 
