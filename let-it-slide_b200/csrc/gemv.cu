@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
     const int64_t rb_stride = (int64_t)p.n_units << 5;        // 128-bit units between row blocks of the TILED layout
     uint32_t slot = 0, phase = 0;
     bool ok = true, waited_prior = false;
+    bool table_pending = false;      // the table's values are in registers; they go to shared memory under the first loads
 
     for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
         const int32_t nu = min(p.seg_units, p.n_units - useg0);
@@ -285,7 +286,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
             waited_prior = true;
             // the codebook loads were issued before the wait; with computed activations the table is written while the
             // glue's own loads are in flight (below)
-            if (INPUT == 0 || p.n != 4096) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+            table_pending = true;
+            if (INPUT != 0 && p.n != 4096) {
+                lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                table_pending = false;
+            }
         }
         if (useg0 > 0) __syncthreads();
         if (INPUT != 0) {
@@ -319,7 +324,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 for (int b = 0; b < BATCH; ++b) {
                     if (p.n == 4096)
                         finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, [&]() {
-                            if (b == 0) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                            if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+                            table_pending = false;
                         });
                     else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
                 }
@@ -338,6 +344,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
+                        if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);       // under the loads above
+                        table_pending = false;
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs)
@@ -356,6 +364,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 }
             }
         }
+        if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);       // threads that loaded nothing, other paths
+        table_pending = false;
         __syncthreads();
 
         // ---- main loop: runs of consecutive units inside one pair of row blocks ----
