@@ -280,6 +280,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
             to_issue -= ahead;
         }
 
+        // The 16 stream bits in front of this warp's first unit: part of the weights, so they can be fetched before
+        // anything that depends on the grid in front (later runs start at a row's first unit and need no fetch).
+        uint32_t first_prev_a = 0u, first_prev_b = 0u;
+        if (count) {
+            const int64_t row_a = ((int64_t)rbp0 << 6) + lane;
+            const bool has_b = 2 * rbp0 + 1 < n_rb;
+            const int32_t ug = useg0 + u0;
+            if (ug == 0) {
+                first_prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
+                first_prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
+            } else {
+                const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp0) * rb_stride +
+                                                                           ((int64_t)(ug - 1) << 5) + lane) + 3;
+                first_prev_a = __ldg(last);
+                first_prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+            }
+        }
         // ---- activations of this column segment -> shared memory ----
         if (!waited_prior) {
             pdl_wait_prior_grids();
@@ -377,7 +394,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
             const int64_t row_a = ((int64_t)rbp << 6) + lane;
             const bool has_b = 2 * rbp + 1 < n_rb;
             uint32_t prev_a, prev_b;
-            {
+            if (k == 0) {
+                prev_a = first_prev_a;
+                prev_b = first_prev_b;
+            } else {
                 const int32_t ug = useg0 + u;
                 if (ug == 0) {
                     prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
@@ -561,6 +581,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
         to_issue -= ahead;
     }
 
+    // The 16 stream bits in front of a run's first unit are part of the weights: those of the first run are fetched here,
+    // before the wait, those of every later run while the run before it is being decoded.
+    auto load_history = [&](uint32_t cbx, uint32_t rbpx, uint32_t u4x, uint32_t &pa, uint32_t &pb) {
+        const int64_t row_a = ((int64_t)rbpx << 6) + lane;
+        const bool has_b = 2 * rbpx + 1 < n_rb;
+        const int32_t ug = (int32_t)(cbx * UPB + u4x);
+        if (ug == 0) {
+            pa = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
+            pb = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
+        } else {
+            const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbpx) * rb_stride + ((int64_t)(ug - 1) << 5) + lane) + 3;
+            pa = __ldg(last);
+            pb = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+        }
+    };
+    uint32_t next_prev_a = 0u, next_prev_b = 0u;
+    if (count) load_history(cb0, rbp0, u40, next_prev_a, next_prev_b);
+
     pdl_wait_prior_grids();
     if (p.clear) {
         float4 *z = reinterpret_cast<float4 *>(p.clear);
@@ -589,16 +627,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
         const uint32_t run = min(count - k, UPB - u4);
         const int64_t row_a = ((int64_t)rbp << 6) + lane;
         const bool has_b = 2 * rbp + 1 < n_rb;
-        const int32_t ug = (int32_t)(cb * UPB + u4);
-        uint32_t prev_a, prev_b;
-        if (ug == 0) {
-            prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
-            prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
-        } else {
-            const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride + ((int64_t)(ug - 1) << 5) + lane) + 3;
-            prev_a = __ldg(last);
-            prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+        uint32_t prev_a = next_prev_a, prev_b = next_prev_b;
+        // where the run after this one starts; its history words travel while this run is decoded
+        uint32_t cb_n = cb, rbp_n = rbp, u4_n = u4 + run;
+        if (u4_n == UPB) {
+            u4_n = 0;
+            if (++rbp_n == n_rbp) {
+                rbp_n = 0;
+                ++cb_n;
+            }
         }
+        if (k + run < count) load_history(cb_n, rbp_n, u4_n, next_prev_a, next_prev_b);
         float facc_a[BATCH], facc_b[BATCH];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
@@ -660,14 +699,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
             if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
         }
         k += run;
-        u4 += run;
-        if (u4 == UPB) {
-            u4 = 0;
-            if (++rbp == n_rbp) {
-                rbp = 0;
-                ++cb;
-            }
-        }
+        cb = cb_n, rbp = rbp_n, u4 = u4_n;
     }
     if (!ok) {
         for (int s = 0; s < kStages; ++s) {      // bounded chance for the copies in flight to land
