@@ -814,6 +814,28 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             to_issue -= ahead;
         }
 
+        // Word 3 of the unit in front of a run, rows g + 8j of both blocks: part of the weights, so the first run's are
+        // fetched here, before anything that depends on the grid in front.
+        auto load_history = [&](uint32_t rbpx, int32_t ug, uint32_t (&pa)[4], uint32_t (&pb)[4]) {
+            const int64_t row0 = (int64_t)rbpx << 6;
+            const bool has_b = 2 * rbpx + 1 < n_rb;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t r = row0 + g + 8 * j;
+                if (ug == 0) {
+                    pa[j] = p.carry_in ? __ldg(p.carry_in + r) : 0u;
+                    pb[j] = (p.carry_in && has_b) ? __ldg(p.carry_in + r + 32) : 0u;
+                } else {
+                    const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbpx) * rb_stride +
+                                                                               ((int64_t)(ug - 1) << 5) + (g + 8 * j)) + 3;
+                    pa[j] = __ldg(last);
+                    pb[j] = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+                }
+            }
+        };
+        uint32_t first_pa[4] = {0u, 0u, 0u, 0u}, first_pb[4] = {0u, 0u, 0u, 0u};
+        if (count) load_history(rbp0, useg0 + u0, first_pa, first_pb);
+
         // ---- activations of this column segment -> shared memory ----
         if (!waited_prior) {
             pdl_wait_prior_grids();
@@ -902,21 +924,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
             const bool has_b = 2 * rbp + 1 < n_rb;
             // word 3 of the unit before the run, rows g + 8j of both blocks (lanes t == 3 hand it to lanes t == 0)
             uint32_t pa[4], pb[4];
-            {
-                const int32_t ug = useg0 + u;
+            if (k == 0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int64_t r = row0 + g + 8 * j;
-                    if (ug == 0) {
-                        pa[j] = p.carry_in ? __ldg(p.carry_in + r) : 0u;
-                        pb[j] = (p.carry_in && has_b) ? __ldg(p.carry_in + r + 32) : 0u;
-                    } else {
-                        const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride +
-                                                                                   ((int64_t)(ug - 1) << 5) + (g + 8 * j)) + 3;
-                        pa[j] = __ldg(last);
-                        pb[j] = has_b ? __ldg(last + 4 * rb_stride) : 0u;
-                    }
-                }
+                for (int j = 0; j < 4; ++j) pa[j] = first_pa[j], pb[j] = first_pb[j];
+            } else {
+                load_history(rbp, useg0 + u, pa, pb);
             }
             float ca[2][4], cb[2][4];
 #pragma unroll
