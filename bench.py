@@ -98,6 +98,8 @@ def cpu_block_seconds(cfg_dims: dict, reps: int) -> tuple[float, int, str]:
     import numpy as np
 
     import c_oracle
+    # all the host cores this process may run on, whatever a launcher exported as OMP_NUM_THREADS for its children
+    c_oracle.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     hidden, ffn, layers = cfg_dims["hidden"], cfg_dims["ffn"], cfg_dims["layers"]
     q = cfg_dims["heads"] * 128
     kv = cfg_dims["kv_heads"] * 128

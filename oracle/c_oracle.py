@@ -40,6 +40,10 @@ def threads() -> int:
     return lib().rptc_oracle_threads()
 
 
+def set_threads(n: int) -> None:
+    lib().rptc_oracle_set_threads(int(n))
+
+
 def _ptr(a):
     return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
 

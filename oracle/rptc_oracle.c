@@ -57,6 +57,15 @@ static void h2f_init(void) {
 enum { CODE_A = 0, CODE_B = 1, CODE_C = 2 };
 enum { LAYOUT_ROWMAJOR = 0, LAYOUT_UNITMAJOR = 2 };
 
+/* Worker threads for the calls that follow (a launcher may have exported OMP_NUM_THREADS=1 for its children). */
+void rptc_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int rptc_oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
