@@ -246,6 +246,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     first = int(model.ids.item())
     torch.cuda.synchronize()
     model.pos.copy_(pos_timed - 3)         # three untimed steps, then the positions of the device-resident leg
+    model.sync_positions()
     if not tp:
         loop = model.host_loop()
         first = loop.run([first], 3)[-1][0]

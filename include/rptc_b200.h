@@ -32,7 +32,10 @@ typedef enum {
     RPTC_ERR_CUDA = -5,        /* a CUDA runtime call failed; see rptc_last_cuda_error() */
     RPTC_ERR_TIMEOUT = -6,     /* a bounded device-side wait ran out (see rptc_device_status) */
     RPTC_ERR_TOO_LARGE = -7,   /* size beyond a documented maximum */
-    RPTC_ERR_DEVICE = -8       /* the current device is not compute capability 10.x */
+    RPTC_ERR_DEVICE = -8,      /* the current device is not compute capability 10.x */
+    RPTC_ERR_INTERNAL = -9,    /* a kernel found its shared-memory layout violated and did nothing (rptc_device_status) */
+    RPTC_ERR_RANGE = -10       /* a sequence position lay outside [0, max_pos): the cache access was skipped
+                                  (rptc_device_status) */
 } rptc_status;
 
 /* Trellis codes.
@@ -85,10 +88,13 @@ int rptc_version(void);
 int rptc_last_cuda_error(void);
 /* RPTC_OK when the current device is a compute-capability 10.x GPU, else RPTC_ERR_DEVICE. */
 int rptc_check_device(void);
-/* Reads (and clears) the device-side status word: 0, or RPTC_ERR_TIMEOUT when a kernel gave up a
- * bounded wait on one of its own asynchronous copies.  Synchronises the device. */
+/* Reads (and clears) the device-side status word.  0, or what a kernel reported since the last call:
+ * RPTC_ERR_TIMEOUT (a bounded wait on one of its own asynchronous copies, on a peer or on the host ran out),
+ * RPTC_ERR_RANGE (a position outside the KV cache: the access was skipped, nothing was written out of bounds),
+ * RPTC_ERR_INTERNAL (shared-memory plan mismatch).  Synchronises the device. */
 int rptc_device_status(void);
-/* Launch kernels with programmatic dependent launch (1) or plainly (0, default). */
+/* Launch kernels with programmatic dependent launch (1) or plainly (0, default).  The setting belongs to the
+ * calling thread: launches made by other threads are not affected. */
 void rptc_set_pdl(int enable);
 
 /* Re-tiles packed codes between layouts (a pure permutation of 128-bit units).

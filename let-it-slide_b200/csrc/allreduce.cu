@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams
         while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
             if (global_ns() - t0 > p.timeout_ns) {
                 timed_out = 1;
-                atomicExch(p.status, 1u);
+                atomicExch(p.status, kStatusWaitExpired);
                 break;
             }
         }

@@ -4,7 +4,7 @@
 namespace rptc {
 
 thread_local int g_last_cuda_error = 0;
-static bool g_pdl = false;
+static thread_local bool g_pdl = false;      // per calling thread: two threads that launch with different settings do not race
 
 int cuda_fail(cudaError_t e) {
     g_last_cuda_error = (int)e;
@@ -14,11 +14,10 @@ int cuda_fail(cudaError_t e) {
 
 bool pdl_enabled() { return g_pdl; }
 
-constexpr int kMaxDevices = 64;
 static int g_sms[kMaxDevices];
 static int g_cc[kMaxDevices];
 
-static int current_device() {
+int current_device() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
     return dev;
@@ -93,6 +92,8 @@ extern "C" const char *rptc_strerror(int status) {
         case RPTC_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case RPTC_ERR_TOO_LARGE: return "size beyond a documented maximum";
         case RPTC_ERR_DEVICE: return "current device is not a compute-capability 10.x GPU";
+        case RPTC_ERR_INTERNAL: return "a kernel found its shared-memory plan violated and did nothing";
+        case RPTC_ERR_RANGE: return "a sequence position lay outside the KV cache; the access was skipped";
     }
     return "unknown status";
 }
@@ -123,6 +124,8 @@ extern "C" int rptc_device_status(void) {
     if (v) {
         const unsigned int zero = 0;
         RPTC_CUDA(cudaMemcpy(w, &zero, sizeof(zero), cudaMemcpyHostToDevice));
+        if (v == kStatusSmemPlan) return RPTC_ERR_INTERNAL;
+        if (v == kStatusPosition) return RPTC_ERR_RANGE;
         return RPTC_ERR_TIMEOUT;
     }
     return RPTC_OK;

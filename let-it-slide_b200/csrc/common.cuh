@@ -17,14 +17,38 @@ constexpr uint32_t kSpinLimit = 1u << 22;   // bounded wait: try_wait attempts b
 extern thread_local int g_last_cuda_error;
 int cuda_fail(cudaError_t e);                 // records e, returns RPTC_ERR_CUDA
 int num_sms();                                // SM count of the current device (cached per device)
-bool pdl_enabled();
+int current_device();                         // index of the current device, or -1 (beyond kMaxDevices, or no device)
+bool pdl_enabled();                           // the calling thread's rptc_set_pdl setting
 unsigned int *device_status_word();           // device address of the status word (per device)
+constexpr int kMaxDevices = 64;
+
+// What a kernel leaves in the device status word (rptc_device_status maps them to rptc_status values).
+constexpr unsigned int kStatusWaitExpired = 1u;      // a bounded wait on an own copy or on a peer ran out
+constexpr unsigned int kStatusSmemPlan = 2u;         // the kernel's shared-memory layout does not fit where it was placed
+constexpr unsigned int kStatusMailboxExpired = 3u;   // the host never posted the step's token ids
+constexpr unsigned int kStatusPosition = 4u;         // a sequence position outside [0, max_pos): the access was skipped
 
 #define RPTC_CUDA(call)                                      \
     do {                                                     \
         cudaError_t e__ = (call);                            \
         if (e__ != cudaSuccess) return ::rptc::cuda_fail(e__); \
     } while (0)
+
+// The opt-in to more than 48 KiB of dynamic shared memory is an attribute of a kernel ON ONE DEVICE: it is set the
+// first time a kernel is launched on each device of the process, and remembered per device.
+struct SmemOptIn {
+    bool done[kMaxDevices] = {};
+};
+template <typename Kernel>
+inline int allow_max_smem(Kernel kern, SmemOptIn &seen) {
+    const int dev = current_device();
+    if (dev < 0) return cuda_fail(cudaErrorInvalidDevice);
+    if (!seen.done[dev]) {
+        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        seen.done[dev] = true;
+    }
+    return RPTC_OK;
+}
 
 // Launches `kernel` with or without the programmatic-dependent-launch attribute.
 template <typename... KArgs, typename... Args>
@@ -87,7 +111,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 #pragma unroll 1
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
-    atomicExch(status, 1u);
+    atomicExch(status, kStatusWaitExpired);
     return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int *status) {

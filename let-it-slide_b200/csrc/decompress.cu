@@ -180,12 +180,9 @@ static int launch_dec(const DecParams &p, size_t smem, cudaStream_t stream) {
     int threads = kDecThreads;
     while (threads > 64 && smem + size_t(threads / 32) * DecTile<K>::kBytes > 226 * 1024) threads >>= 1;
     smem += size_t(threads / 32) * DecTile<K>::kBytes;
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = decompress_kernel<CODE, K, ROWLANES>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(threads), smem, stream, p);
 }
 

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s0 = smem_addr(smem_raw);
     if (s0 > p.bar_addr) {                     // the dynamic area starts later than the host planned for
-        if (tid == 0) atomicExch(p.status, 2u);
+        if (tid == 0) atomicExch(p.status, kStatusSmemPlan);
         return;
     }
     // barriers: full_w[s] (128 producer arrivals), full_x[s] (TMA bytes), empty[s] (MMA commit), accum, tmem slot
@@ -273,12 +273,9 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_tiled_fn() {
 
 template <int CODE, int K, int NROWS>
 static int launch_gemm(const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = gemm_kernel<CODE, K, NROWS>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, grid, dim3(kGemmThreads), smem, stream, p, map);
 }
 

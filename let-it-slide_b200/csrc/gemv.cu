@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
         xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
     }
     if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
-        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemPlan);
         return;
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
         xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
     }
     if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
-        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemPlan);
         return;
     }
     const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
@@ -753,7 +753,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
     }
     if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
-        if (threadIdx.x == 0) atomicExch(p.status, 2u);
+        if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemPlan);
         return;
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
@@ -1046,12 +1046,9 @@ __global__ void gemv_finish_kernel(float *__restrict__ acc, int64_t ld_acc, __ha
 
 template <int CODE, int K>
 static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = gemv_kernel<CODE, K>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
@@ -1063,24 +1060,18 @@ static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
 
 template <int CODE, int K, int BATCH, int INPUT = 0>
 static int launch_gemv_mma(const GemvParams &p, size_t smem, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = gemv_mma_kernel<CODE, K, BATCH, INPUT>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
 template <int CODE, int K, int BATCH, int INPUT = 0>
 static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t stream) {
     if (BATCH >= RPTC_GEMV_MMA_MIN_BATCH) return launch_gemv_mma<CODE, K, BATCH, INPUT>(p, smem, stream);
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = gemv_pair_kernel<CODE, K, BATCH, INPUT>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
@@ -1170,11 +1161,11 @@ int check_format(const rptc_format *f);   // api.cu
 
 using namespace rptc;
 
-extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
-                         float *acc, int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
-                         rptc_stream_t stream) {
+// Every check of rptc_gemv's arguments that needs no device work, in the order the entry point reports them.
+static int validate_gemv_args(const void *codes, const void *lut, const void *x, int64_t ld_x, const float *acc, int64_t ld_acc,
+                              int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt) {
     if (!codes || !lut || !x || !acc || !fmt) return RPTC_ERR_ARG;
-    if (int e = check_format(fmt)) return e;
+    if (int e = rptc::check_format(fmt)) return e;
     if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
     if (batch < 1 || batch > 8) return RPTC_ERR_ARG;
     if (x_order != RPTC_XORDER_NATURAL && x_order != RPTC_XORDER_K2_LEGACY) return RPTC_ERR_ARG;
@@ -1187,6 +1178,13 @@ extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *car
         (reinterpret_cast<uintptr_t>(x) & 3) || (ld_x & 1))
         return RPTC_ERR_ALIGN;
     if (ld_x < n || ld_acc < m) return RPTC_ERR_SHAPE;
+    return RPTC_OK;
+}
+
+extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
+                         float *acc, int64_t ld_acc, int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt,
+                         rptc_stream_t stream) {
+    if (int e = validate_gemv_args(codes, lut, x, ld_x, acc, ld_acc, m, n, batch, x_order, fmt)) return e;
     if (int e = rptc_check_device()) return e;
     // batches that are not a power of two run as a short sequence of launches
     int done = 0;
@@ -1219,7 +1217,7 @@ extern "C" int rptc_gemv_finish(float *acc, int64_t ld_acc, void *y, int64_t ld_
 namespace rptc {
 constexpr int64_t kStaticAccFloats = 262144;                      // 1 MiB: batch * m may not exceed this
 static __device__ __align__(256) float g_static_acc[kStaticAccFloats];
-static float *g_static_acc_ptr[64];                               // device address of the array, per device
+static float *g_static_acc_ptr[kMaxDevices];                               // device address of the array, per device
 }  // namespace rptc
 
 extern "C" int rptc_gemv_f16_static(const void *codes, const void *lut, const uint32_t *carry_in, const void *x, int64_t ld_x,
@@ -1229,9 +1227,13 @@ extern "C" int rptc_gemv_f16_static(const void *codes, const void *lut, const ui
     if (batch < 1 || batch > 8 || m <= 0) return RPTC_ERR_ARG;
     if ((int64_t)batch * m > kStaticAccFloats) return RPTC_ERR_TOO_LARGE;      // the fixed accumulator cannot hold it
     if (ld_y < m) return RPTC_ERR_SHAPE;
-    int dev = 0;
-    RPTC_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return RPTC_ERR_ARG;
+    // Everything that can refuse the call is checked before the shared array is touched: a rejected call must not put a
+    // clearing of the array on the caller's stream (it could land in the middle of a valid call on another stream).
+    // The non-null placeholder stands for the accumulator, whose address is not known yet.
+    if (int e = validate_gemv_args(codes, lut, x, ld_x, reinterpret_cast<const float *>(codes), m, m, n, batch, x_order, fmt)) return e;
+    if (int e = rptc_check_device()) return e;
+    const int dev = current_device();
+    if (dev < 0) return RPTC_ERR_ARG;
     if (!g_static_acc_ptr[dev]) {
         // Set-up, once per device, with that device current: in host code the array's name is only a handle,
         // the address a kernel can use has to be asked for.
@@ -1271,12 +1273,9 @@ extern "C" int rptc_gemv_glued(const void *codes, const void *lut, const uint32_
 
 template <int CODE, int K, int BATCH>
 static int launch_gemv_colblock(const GemvParams &p, size_t smem, cudaStream_t stream) {
-    static bool configured = false;
+    static SmemOptIn opted;
     auto kern = gemv_colblock_kernel<CODE, K, BATCH>;
-    if (!configured) {
-        RPTC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
-    }
+    if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 

@@ -93,6 +93,7 @@ struct QkvFinishParams {
     const int32_t *pos;
     int32_t hq, hkv, max_pos, block, chunk;
     float theta;
+    unsigned int *status;
 };
 
 __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p) {
@@ -105,6 +106,9 @@ __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p
     float v[8], sg[8];
     const uint4 raw_so = raw8_or_ones(p.signs_out ? p.signs_out + col : nullptr);
     const int ps = p.pos[row];
+    // a position outside [0, max_pos) has no row in the cache: q is still finished, k and v are dropped, the host is told
+    const bool in_cache = ps >= 0 && ps < p.max_pos;
+    if (!in_cache && t == 0 && blockIdx.x == 0) atomicExch(p.status, kStatusPosition);
     load8_f32(p.acc + row * p.ld_acc + col, v, true);
     fwht8(v, p.block, ex);
     unpack8(raw_so, sg);
@@ -123,10 +127,9 @@ __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p
             sincosf(ps * __powf(p.theta, -2.f * j / 128.f), &sn, &cs);
             o[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
         }
-        __half *dst = head < p.hq ? p.q_out + row * p.ld_q + col
-                                  : p.kcache + ((row * p.max_pos + ps) * p.hkv + (head - p.hq)) * 128 + idx;
-        store8_f16(dst, o);
-    } else {
+        if (head < p.hq) store8_f16(p.q_out + row * p.ld_q + col, o);
+        else if (in_cache) store8_f16(p.kcache + ((row * p.max_pos + ps) * p.hkv + (head - p.hq)) * 128 + idx, o);
+    } else if (in_cache) {
         store8_f16(p.vcache + ((row * p.max_pos + ps) * p.hkv + (head - p.hq - p.hkv)) * 128 + idx, v);
     }
 }
@@ -294,5 +297,7 @@ extern "C" int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out
     p.block = block;
     p.chunk = chunk;
     p.theta = theta;
+    p.status = device_status_word();
+    if (!p.status) return RPTC_ERR_CUDA;
     return launch(qkv_finish_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0, static_cast<cudaStream_t>(stream), p);
 }

@@ -52,11 +52,15 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__
 // at positions pos[row].  Caches: [rows][max_pos][hkv][d].  One CTA per (row, head of q|k|v).
 __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv, int64_t ld_qkv, const int32_t *__restrict__ pos,
                                                         __half *__restrict__ kcache, __half *__restrict__ vcache, int hq, int hkv,
-                                                        int d, int max_pos, float theta) {
+                                                        int d, int max_pos, float theta, unsigned int *__restrict__ status) {
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     const int row = blockIdx.y, head = blockIdx.x, t = threadIdx.x;      // t < d/2
     const int p = pos[row];
+    if (p < 0 || p >= max_pos) {       // no room in the cache for this position: report it and touch nothing
+        if (t == 0 && head == 0) atomicExch(status, kStatusPosition);
+        return;
+    }
     __half *src = qkv + (int64_t)row * ld_qkv + (int64_t)head * d;
     if (head < hq + hkv) {
         float lo = 0.f, hi = 0.f;
@@ -128,7 +132,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                                                                   const __half *__restrict__ signs_in, float *__restrict__ acc,
                                                                   int64_t ld_acc, const __half *__restrict__ signs_out,
                                                                   float scale_out, float theta, __half *__restrict__ kcache_w,
-                                                                  __half *__restrict__ vcache_w) {
+                                                                  __half *__restrict__ vcache_w, unsigned int *__restrict__ status) {
     __shared__ float part[kAttnWarps][128];
     __shared__ float pm[kAttnWarps], pl[kAttnWarps];
     __shared__ float tr[128];
@@ -141,7 +145,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     if (!fused) pdl_wait_prior_grids();
     const int row = blockIdx.y, head = blockIdx.x, kvh = head / (hq / hkv);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int ctx = (int)ld_ordered_u32(pos + row) + 1;
+    // A position outside [0, max_pos) has no row in the cache: it is reported, nothing is appended, and attention runs
+    // over the rows that exist (the result is meaningless, the accesses stay in bounds).
+    const int pos_raw = (int)ld_ordered_u32(pos + row);
+    const bool pos_ok = pos_raw >= 0 && pos_raw < max_pos;
+    if (!pos_ok && t == 0 && head == 0) atomicExch(status, kStatusPosition);
+    const int ctx = min(max(pos_raw, 0), max_pos - 1) + 1;
     const int n_old = fused ? ctx - 1 : ctx;                     // rows to read from the cache
     const int64_t stride = (int64_t)hkv * D;
     const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
@@ -199,10 +208,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                 store8_f16(qs + i8, o);
             } else if (grp == 1) {
                 store8_f16(ks + i8, o);
-                store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+                if (pos_ok) store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
             } else if (grp == 2) {
                 store8_f16(vs + i8, o);
-                store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+                if (pos_ok) store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
             }
         }
         __syncthreads();
@@ -367,7 +376,7 @@ __global__ void __launch_bounds__(256) embed_mailbox_kernel(const __half *__rest
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
                 if (now - t0 > timeout_ns) {
-                    atomicExch(status, 3u);
+                    atomicExch(status, kStatusMailboxExpired);
                     break;
                 }
                 __nanosleep(100);
@@ -429,7 +438,7 @@ __global__ void __launch_bounds__(1024) next_token_kernel(const __half *__restri
             if (at == 0x7FFFFFFF) at = 0;           // a row of NaNs
             next[r] = at;
             if (ids) ids[r] = at;
-            if (pos) pos[r] += 1;
+            if (pos && pos[r] < 0x7FFFFFFF) pos[r] += 1;      // consumers check the position against their cache
             if (mirror) {
                 // with a step counter the slot is a mailbox entry: (sequence << 32) | id, one store, pushed to the host
                 mirror[r] = steps_done ? (int64_t)(((unsigned long long)*steps_done << 32) | (unsigned)at) : (int64_t)at;
@@ -459,9 +468,11 @@ extern "C" int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, vo
     if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || d <= 0 || (d % 2) || d > 128 || max_pos <= 0) return RPTC_ERR_SHAPE;
     if (ld_qkv < (int64_t)(hq + 2 * hkv) * d) return RPTC_ERR_SHAPE;
     if (int e = rptc_check_device()) return e;
+    unsigned int *status = device_status_word();
+    if (!status) return RPTC_ERR_CUDA;
     return launch(rope_cache_kernel, dim3((unsigned)(hq + 2 * hkv), (unsigned)rows), dim3(64), 0, static_cast<cudaStream_t>(stream),
                   static_cast<__half *>(qkv), ld_qkv, pos, static_cast<__half *>(kcache), static_cast<__half *>(vcache), hq, hkv, d,
-                  max_pos, theta);
+                  max_pos, theta, status);
 }
 
 extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
@@ -472,11 +483,13 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
     if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || max_pos <= 0 || max_pos > 32768) return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(kcache) & 7) || (ld_qkv & 3)) return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
+    unsigned int *status = device_status_word();
+    if (!status) return RPTC_ERR_CUDA;
     return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
                   static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in),
                   static_cast<float *>(nullptr), (int64_t)0, static_cast<const __half *>(nullptr), 0.f, 0.f,
-                  static_cast<__half *>(nullptr), static_cast<__half *>(nullptr));
+                  static_cast<__half *>(nullptr), static_cast<__half *>(nullptr), status);
 }
 
 extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, const int32_t *pos,
@@ -490,11 +503,13 @@ extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *sign
         (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (ld_acc % 4))
         return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
+    unsigned int *status = device_status_word();
+    if (!status) return RPTC_ERR_CUDA;
     return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(nullptr), (int64_t)0, pos, static_cast<const __half *>(kcache),
                   static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, heads, max_pos, 0.08838834764831845f,
                   static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, theta,
-                  static_cast<__half *>(kcache), static_cast<__half *>(vcache));
+                  static_cast<__half *>(kcache), static_cast<__half *>(vcache), status);
 }
 
 extern "C" int rptc_dense_gemv(const void *W, int64_t ld_w, const void *x, int64_t ld_x, void *y, int64_t ld_y, int64_t m, int64_t n,

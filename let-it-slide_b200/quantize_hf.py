@@ -120,17 +120,25 @@ def evaluate_layer(H: torch.Tensor, W: torch.Tensor, recon: torch.Tensor):
 
 
 class FactorizedRPTCLinear(nn.Module):
-    """A linear layer stored as code-A trellis codes plus the factorisation's biases and scales."""
+    """A linear layer stored as code-A trellis codes plus the factorisation's biases and scales.
+
+    Rows are split into `num_banks` banks of out_features / num_banks rows with one alphabet each, as the reference's
+    round_weights does (quantize_hf.py:120-156; it needs out_features % (num_banks * batch_size) == 0 only).  The
+    kernels decode 32 rows at a time, so each bank is stored padded up to a whole number of 32-row blocks with all-zero
+    code rows whose outputs are dropped: Llama-2-7B's gate/up projections (11008 rows, 344 per bank at 32 banks) take 11
+    blocks per bank."""
 
     def __init__(self, out_features: int, in_features: int, shift_register_size: int, num_banks: int, bias: bool = False,
                  device=None):
         super().__init__()
-        if in_features % 64 or out_features % (32 * num_banks):
-            raise ValueError("in_features must be a multiple of 64 and every bank a whole number of 32-row blocks")
+        if in_features % 64 or out_features % num_banks:
+            raise ValueError("in_features must be a multiple of 64 and out_features a multiple of num_banks")
         self.out_features, self.in_features, self.L, self.num_banks = out_features, in_features, shift_register_size, num_banks
+        self.bank_rows = out_features // num_banks                 # rows of W per bank
+        self.bank_blocks = -(-self.bank_rows // 32)                # 32-row blocks per bank as stored (last one zero-padded)
         self.fmt = Format(CODE_LUT, 2, shift_register_size, 0, LAYOUT_TILED)
         dev = device
-        self.register_buffer("codes", torch.zeros((out_features // 32, in_features // 64, 32, 4), dtype=torch.int32, device=dev))
+        self.register_buffer("codes", torch.zeros((num_banks * self.bank_blocks, in_features // 64, 32, 4), dtype=torch.int32, device=dev))
         self.register_buffer("alphabets", torch.zeros((num_banks, 1 << shift_register_size), dtype=torch.float16, device=dev))
         self.register_buffer("biases_out", torch.zeros(out_features, dtype=torch.float32, device=dev))
         self.register_buffer("biases_in", torch.zeros(in_features, dtype=torch.float32, device=dev))
@@ -145,8 +153,10 @@ class FactorizedRPTCLinear(nn.Module):
         L = alphabets.shape[1].bit_length() - 1
         dev = torch.device("cuda", torch.cuda.current_device())
         self = cls(m, n, L, alphabets.shape[0], bias is not None, device=dev)
-        words = pack_symbols(symbols.to(dev), bits=2)                       # ROWMAJOR, MSB first
-        self.codes.copy_(ops.repack(words.contiguous(), LAYOUT_ROWMAJOR, LAYOUT_TILED, m, n // 64))
+        padded = torch.zeros((self.num_banks, self.bank_blocks * 32, n), dtype=symbols.dtype, device=dev)
+        padded[:, : self.bank_rows] = symbols.to(dev).reshape(self.num_banks, self.bank_rows, n)
+        words = pack_symbols(padded.reshape(-1, n), bits=2)                 # ROWMAJOR, MSB first
+        self.codes.copy_(ops.repack(words.contiguous(), LAYOUT_ROWMAJOR, LAYOUT_TILED, padded.shape[0] * padded.shape[1], n // 64))
         self.alphabets.copy_(alphabets.to(dev))
         for name, v in (("biases_out", biases_out), ("biases_in", biases_in), ("scales_out", scales_out), ("scales_in", scales_in)):
             getattr(self, name).copy_(v.reshape(-1).to(dev))
@@ -155,15 +165,16 @@ class FactorizedRPTCLinear(nn.Module):
         return self
 
     def _bank(self, b: int):
-        rb = self.out_features // 32 // self.num_banks
-        return self.codes[b * rb:(b + 1) * rb], self.alphabets[b], rb * 32
+        """(codes of the bank, its alphabet, rows as stored = a multiple of 32, slice of W's rows the bank holds)."""
+        rb = self.bank_blocks
+        return self.codes[b * rb:(b + 1) * rb], self.alphabets[b], rb * 32, slice(b * self.bank_rows, (b + 1) * self.bank_rows)
 
     def decoded(self) -> torch.Tensor:
         """W_hat [m, n] fp16: the alphabet entries the codes select."""
         out = torch.empty((self.out_features, self.in_features), dtype=torch.float16, device=self.codes.device)
         for b in range(self.num_banks):
-            codes, lut, rows = self._bank(b)
-            out[b * rows:(b + 1) * rows] = ops.decompress(codes, lut, rows, self.in_features, self.fmt)
+            codes, lut, stored, sl = self._bank(b)
+            out[sl] = ops.decompress(codes, lut, stored, self.in_features, self.fmt)[: self.bank_rows]
         return out
 
     def reconstruct(self) -> torch.Tensor:
@@ -178,13 +189,12 @@ class FactorizedRPTCLinear(nn.Module):
         t = xs.shape[0]
         y = torch.empty((t, self.out_features), dtype=torch.float32, device=x.device)
         for b in range(self.num_banks):
-            codes, lut, rows = self._bank(b)
-            sl = slice(b * rows, (b + 1) * rows)
-            if t > 8 and rows % 128 == 0:           # the tensor-core GEMM works on 128-row tiles
-                y[:, sl] = ops.gemm(codes, lut, xs, rows, self.in_features, self.fmt).float()
+            codes, lut, stored, sl = self._bank(b)
+            if t > 8 and stored % 128 == 0:         # the tensor-core GEMM works on 128-row tiles
+                y[:, sl] = ops.gemm(codes, lut, xs, stored, self.in_features, self.fmt)[:, : self.bank_rows].float()
             else:
                 for t0 in range(0, t, 8):
-                    y[t0:t0 + 8, sl] = ops.gemv(codes, lut, xs[t0:t0 + 8], rows, self.in_features, self.fmt).float()
+                    y[t0:t0 + 8, sl] = ops.gemv(codes, lut, xs[t0:t0 + 8], stored, self.in_features, self.fmt)[:, : self.bank_rows].float()
         y = y * self.scales_out + x32.sum(dim=1, keepdim=True) * self.biases_out + (x32 @ self.biases_in)[:, None]
         if self.bias is not None:
             y = y + self.bias

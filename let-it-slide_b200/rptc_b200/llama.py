@@ -134,6 +134,7 @@ class RPTCLlama:
         self.mailbox = None                            # see bind_mailbox
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
+        self._pos_hi = 0            # host-side upper bound of the positions on the device (see step)
 
     # -- one token for every row ---------------------------------------------------------------------
     def _fusable(self) -> bool:
@@ -458,7 +459,21 @@ class RPTCLlama:
     def host_loop(self, timeout_ms: int = 2000) -> "HostTokenLoop":
         return HostTokenLoop(self, timeout_ms)
 
+    def sync_positions(self) -> None:
+        """Re-reads the device-side positions after they were edited directly (`model.pos.copy_(...)`)."""
+        self._pos_hi = int(self.pos.max().item())
+
+    def _claim_positions(self, n_steps: int) -> None:
+        """The positions live on the device and advance with every replay of the captured step; the host keeps an upper
+        bound and refuses a step that has no row left in the KV caches (the kernels would skip the access and raise the
+        device status word, but by then the token is lost)."""
+        if self._pos_hi + n_steps > self.cfg.max_pos:
+            raise RuntimeError(f"decode step at position {self._pos_hi + n_steps - 1} but the KV caches hold max_pos = "
+                               f"{self.cfg.max_pos} positions")
+        self._pos_hi += n_steps
+
     def step(self) -> None:
+        self._claim_positions(1)
         if self.graph is not None:
             self.graph.replay()
         else:
@@ -466,6 +481,7 @@ class RPTCLlama:
 
     def reset(self, ids: torch.Tensor | None = None) -> None:
         self.pos.zero_()
+        self._pos_hi = 0
         self._acc_pool.zero_()      # the short chain leaves acc_o / acc_gu to the next token's first launch
         self.acc_gu2.zero_()
         if ids is not None:
@@ -530,6 +546,7 @@ class RPTCLlama:
         ops.rmsnorm(last, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self.pos.fill_(T - 1)
+        self._pos_hi = T
         ops.next_token(self.logits, self.next_ids, self.ids, self.pos, None)        # pos -> T, ids -> greedy choice
         return self.logits
 
@@ -617,6 +634,7 @@ class HostTokenLoop:
         model, tokens = self.model, []
         if n_steps <= 0:
             return tokens
+        model._claim_positions(n_steps)
         self._post(self.seq + 1, first_ids)
         model.graph.replay()
         for i in range(n_steps):

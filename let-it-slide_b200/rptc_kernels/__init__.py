@@ -11,6 +11,9 @@ instead of the reference's kernels.  Differences, all deliberate:
     `set_reference_quirks(True)` reproduces those deviations bit for bit;
   * `decompress_matvec_t_*` computes the intended product; the reference kernel's inner loop does
     not advance its shift registers (inference_t.cu:125-134) and is not reproduced;
+  * the fused matvecs add partial sums into an fp32 accumulator that this module keeps per (device, stream, m): two
+    calls on the same stream are ordered by the stream; calls from two host threads that share one stream must be
+    serialised by the caller;
   * shape rules are relaxed: n needs to be a multiple of 64 only, except for the chunked layout of
     `decompress_matvec_*`, which is defined in steps of 2048 columns.
 """
@@ -22,7 +25,7 @@ from rptc_b200 import (CODE_HASH, CODE_LUT, LAYOUT_CHUNKED, LAYOUT_ROWMAJOR, LAY
                        QUIRK_K2_LANE0_CARRY, QUIRK_NONE, XORDER_K2_LEGACY, XORDER_NATURAL, Format, ops)
 
 _quirks = False
-_scratch: dict[tuple[int, int], torch.Tensor] = {}
+_scratch: dict[tuple[int, int, int], torch.Tensor] = {}
 
 
 def set_reference_quirks(enable: bool) -> None:
@@ -44,7 +47,9 @@ def _check(t: torch.Tensor, name: str, dtype: torch.dtype, dim: int | None = Non
 
 
 def _acc(device: torch.device, m: int) -> torch.Tensor:
-    key = (device.index or 0, m)
+    """fp32 accumulator of the fused matvecs, one per (device, stream, m): calls on different streams share nothing, like
+    the reference's functions, which write `out` directly (inference.cu:335-342)."""
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream, m)
     buf = _scratch.get(key)
     if buf is None:
         buf = torch.zeros((1, m), dtype=torch.float32, device=device)

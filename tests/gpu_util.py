@@ -30,3 +30,53 @@ def bits(a):
 
 def lut_for_oracle(lut, code, S):
     return lut.reshape(1 << S, 2) if code == o.CODE_C else lut
+
+
+# ---- tolerances derived from the kernels' arithmetic --------------------------------------------------------
+# |w|, |x| below are the Euclidean norms of a weight row and an activation row; y is the exact product.
+#  * batch 1 (HFMA2 kernels): four fp16 accumulators per 64-weight unit take eight fp16 products each, three fp16
+#    adds join them, everything after that is fp32.  Each fp16 rounding is 2^-11 of a partial sum of at most 64
+#    terms, and the roundings of the n/64 units add in quadrature: about 4e-5 |w||x| at the worst row of a
+#    4096 x 4096 layer (0.147 absolute measured).  Bound: 1.5e-4 |w||x|.
+#  * batch >= 2 (mma.sync kernel) and the tcgen05 GEMM: fp16 products summed in fp32.  Bound: 2e-5 |w||x|.
+#  * the fp16 rounding of the result itself: 2^-11 |y|.
+# One mis-decoded weight moves an output by |dw * x_c|, about 1 for N(0,1) weights and activations: at n = 4096 the
+# batch-1 bound is 0.6 absolute and the others 0.08, against 8.2 for the bound these tests used before.
+GEMV_HFMA2_TOL = 1.5e-4
+GEMV_FP32_TOL = 2e-5
+
+
+def check_product(y, exact, wnorm, xnorm, rel, what=""):
+    """y, exact: [b, m] float64 arrays; wnorm [m], xnorm [b].  Returns max err/tol (also printed)."""
+    err = np.abs(np.asarray(y, dtype=np.float64) - exact)
+    tol = rel * wnorm[None, :] * xnorm[:, None] + 2.0**-11 * np.abs(exact) + 1e-4
+    worst = float(np.max(err / tol))
+    print(f"{what} max err {err.max():.4g}, max err/tol {worst:.3f}")
+    assert worst <= 1.0, f"{what} max err/tol {worst:.3f}"
+    return worst
+
+
+def probe_columns(run, n, batch, m, cols=None):
+    """Exact-column probing: run(x) -> y for x fp16 [batch, n] whose rows are unit vectors.  Every product is then a
+    weight times one or zero and every partial sum a weight plus zeros, exact in fp16 and fp32, so the output row of
+    column c must equal column c of the decoded matrix bit for bit.  Returns Y [len(cols), m] fp16 (all columns when
+    `cols` is None)."""
+    cols = torch.arange(n, device="cuda") if cols is None else torch.as_tensor(cols, device="cuda", dtype=torch.long)
+    Y = torch.empty((len(cols), m), dtype=torch.float16, device="cuda")
+    x = torch.zeros((batch, n), dtype=torch.float16, device="cuda")
+    ar = torch.arange(batch, device="cuda")
+    for i0 in range(0, len(cols), batch):
+        c = cols[i0:i0 + batch]
+        k = len(c)
+        x.zero_()
+        x[ar[:k], c] = 1.0
+        Y[i0:i0 + k] = run(x)[:k]
+    return Y
+
+
+def assert_same_bits(a, b, what=""):
+    """Two fp16 CUDA tensors, compared as raw 16-bit patterns."""
+    a, b = a.contiguous().view(torch.int16), b.contiguous().view(torch.int16)
+    if not torch.equal(a, b):
+        bad = (a != b).nonzero()
+        raise AssertionError(f"{what}: {len(bad)} of {a.numel()} elements differ, first at {bad[0].tolist()}")

@@ -46,3 +46,33 @@ def test_argument_errors_need_no_gpu():
     assert lib().rptc_decompress(1 << 8, 1 << 8, None, 1 << 8, 64, 32, 64, ctypes.byref(bad), None) == -4
     assert lib().rptc_hadamard(1 << 8, 0, 256, 1 << 8, 256, None, None, 0, 1, 256, 100, 0, 1.0, 0, None) == -1
     assert lib().rptc_repack(1 << 8, 0, 1 << 9, 2, 33, 4, None) == -2
+
+
+def test_entry_point_without_scratch_rejects_bad_calls_before_it_touches_its_array():
+    """rptc_gemv_f16_static shares one array between all calls on a device: a call that is going to be refused must be
+    refused before anything is queued on the caller's stream.  All of these return without a CUDA call."""
+    from rptc_b200 import Format, lib
+    f = Format()
+    call = lib().rptc_gemv_f16_static
+    ok = dict(codes=1 << 8, lut=1 << 8, x=1 << 8, ld_x=64, y=1 << 8, ld_y=32, m=32, n=64, batch=1, x_order=0, fmt=f)
+
+    def status(**kw):
+        a = {**ok, **kw}
+        return call(a["codes"], a["lut"], None, a["x"], a["ld_x"], a["y"], a["ld_y"], a["m"], a["n"], a["batch"], a["x_order"],
+                    ctypes.byref(a["fmt"]), None)
+
+    assert status(codes=None) == -1                             # null codes
+    assert status(y=None) == -1
+    assert status(fmt=Format(code=7)) == -1                     # bad enum value
+    assert status(fmt=Format(code=1, K=4)) == -4                # HASH is 2 bits per weight
+    assert status(m=33) == -2                                   # m % 32
+    assert status(codes=(1 << 8) + 4) == -3                     # codes not 16-byte aligned
+    assert status(ld_x=32) == -2                                # ld_x < n
+    assert status(m=262144 // 8 + 32, ld_y=1 << 20, batch=8) == -7      # beyond the fixed accumulator
+    assert status(batch=9) == -1
+
+
+def test_status_strings_cover_every_code():
+    from rptc_b200 import lib
+    for code in range(-10, 1):
+        assert lib().rptc_strerror(code) != b"unknown status"

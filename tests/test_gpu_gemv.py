@@ -1,27 +1,28 @@
 """GPU parity: the fused dequant-GEMV against the CPU oracle (fp64 product of bit-exact weights).
 
-Tolerance.  The kernel multiplies in fp16 pairs and adds eight products per fp16 accumulator before
-widening to fp32, so an output carries an absolute error of a few fp16 ulps of its partial sums.
-The bound used is  |y - y_exact| <= 2e-3 * ||w_row|| * ||x||  (about 30 times tighter than a fully
-fp16-accumulated dot product such as the reference's, inference.cu:263,270-276), and the rounding
-of the fp16 result itself.
+Tolerance (derived in gpu_util.py from the kernels' arithmetic).  Batch 1 multiplies in fp16 pairs and adds eight
+products per fp16 accumulator before widening to fp32: |y - exact| <= 1.5e-4 ||w_row|| ||x|| + 2^-11 |exact|, which is
+0.6 absolute at n = 4096 with N(0,1) data -- below the ~1 that ONE mis-decoded weight moves an output by (the
+reference's fully fp16-accumulated product, inference.cu:263,270-276, is about 200 times looser).  Batch 2-8 runs on
+mma.sync with fp32 accumulation: 2e-5 ||w_row|| ||x||.  Wrong weights are hunted exactly, column by column, in
+test_gpu_probe.py; this file checks the arithmetic on random inputs.
 """
 import numpy as np
 import pytest
 import torch
 
 import rptc_oracle as o
-from gpu_util import bits, lut_for_oracle, rand_lut, rand_words, to_dev
+from gpu_util import GEMV_FP32_TOL, GEMV_HFMA2_TOL, bits, check_product, lut_for_oracle, rand_lut, rand_words, to_dev
 
 pytestmark = pytest.mark.gpu
 
 
-def _check(y, w16, x16):
+def _check(y, w16, x16, rel=None, what=""):
+    """rel defaults to the bound of the kernel that serves this batch size (1: HFMA2, 2-8: mma.sync)."""
+    if rel is None:
+        rel = GEMV_HFMA2_TOL if x16.shape[0] in (1, 3, 5, 7) else GEMV_FP32_TOL      # odd batches end in a batch-1 launch
     exact = o.matvec_exact(w16, x16)
-    scale = np.linalg.norm(w16.astype(np.float64), axis=1)[None, :] * np.linalg.norm(x16.astype(np.float64), axis=1)[:, None]
-    err = np.abs(y.astype(np.float64) - exact)
-    tol = 2e-3 * scale + 1e-3 * np.abs(exact) + 1e-3
-    assert (err <= tol).all(), f"max err/tol {np.max(err / tol):.3f}"
+    check_product(y, exact, np.linalg.norm(w16.astype(np.float64), axis=1), np.linalg.norm(x16.astype(np.float64), axis=1), rel, what)
 
 
 CASES = [(o.CODE_B, 2, 16, 8), (o.CODE_B, 2, 16, 6), (o.CODE_A, 2, 16, 0), (o.CODE_A, 4, 16, 0), (o.CODE_A, 2, 14, 0),
@@ -57,7 +58,7 @@ def test_gemv_legacy_layouts(layout):
     x = rng.standard_normal((1, n)).astype(np.float16)
     w16 = o.decode(w, lut, n, code=o.CODE_B, S=8)
     y = ops.gemv(to_dev(o.from_rowmajor(w, layout)), to_dev(lut), to_dev(x), m, n, Format(o.CODE_B, 2, 16, 8, layout))
-    _check(y.float().cpu().numpy(), w16, x)
+    _check(y.float().cpu().numpy(), w16, x, GEMV_HFMA2_TOL)      # the general kernel is an HFMA2 kernel
 
 
 def test_gemv_carry_in_and_column_sharding():
@@ -104,7 +105,7 @@ def test_gemv_all_ones_codebook_known_answer():
     y = ops.gemv(to_dev(o.from_rowmajor(w, o.LAYOUT_TILED)), to_dev(lut), to_dev(x), m, n,
                  Format(o.CODE_A, 2, 16, 0, o.LAYOUT_TILED))
     s = x.astype(np.float64).sum()
-    assert np.allclose(y.float().cpu().numpy(), s, atol=0.25)
+    assert np.allclose(y.float().cpu().numpy(), s, atol=2.0**-11 * abs(s) + 1.5e-4 * np.sqrt(n) * np.linalg.norm(x.astype(np.float64)))
 
 
 @pytest.mark.parametrize("m,n", [(4096, 4096), (11008, 4096), (4096, 11008), (28672, 8192)])
@@ -118,9 +119,16 @@ def test_gemv_full_size_linearity(m, n):
     x = torch.randn((2, n), dtype=torch.float16, device="cuda", generator=g)
     fmt = Format(o.CODE_B, 2, 16, 8, o.LAYOUT_TILED)
     y = ops.gemv(codes, lut, x, m, n, fmt).float()
-    ysum = ops.gemv(codes, lut, (x[0] + x[1]).unsqueeze(0), m, n, fmt).float()
+    ysum = ops.gemv(codes, lut, (x[0] + x[1]).unsqueeze(0), m, n, fmt).float()      # the fp16 sum is the input of both sides
     dense = ops.decompress(codes, lut, m, n, fmt)
     ref = (x.double() @ dense.double().T)
     scale = dense.double().norm(dim=1)[None, :] * x.double().norm(dim=1)[:, None]
-    assert bool(((y.double() - ref).abs() <= 2e-3 * scale + 1e-3 * ref.abs() + 1e-3).all())
-    assert bool(((ysum[0] - (y[0] + y[1])).abs() <= 4e-3 * scale.max().item()).all())
+    err = (y.double() - ref).abs()
+    tol = GEMV_FP32_TOL * scale + 2.0**-11 * ref.abs() + 1e-4                        # batch 2: the mma.sync kernel
+    assert bool((err <= tol).all()), f"max err/tol {(err / tol).max().item():.3f}"
+    # batch 1 (HFMA2 kernel) on the fp16 sum of the two rows, against the same product
+    xs = (x[0] + x[1]).unsqueeze(0)
+    ref_s = xs.double() @ dense.double().T
+    err_s = (ysum.double() - ref_s).abs()
+    tol_s = GEMV_HFMA2_TOL * dense.double().norm(dim=1)[None, :] * xs.double().norm() + 2.0**-11 * ref_s.abs() + 1e-4
+    assert bool((err_s <= tol_s).all()), f"batch 1 max err/tol {(err_s / tol_s).max().item():.3f}"

@@ -262,3 +262,77 @@ def test_decode_attention_beyond_one_chunk_of_positions(kv_heads):
             torch.cuda.synchronize()
             err = (model.logits.float() - ref[:, t]).abs().max().item()
             assert err <= 1.5e-2 * ref[:, t].abs().max().item(), (T, t, err)
+
+
+def test_a_step_beyond_the_cache_is_refused_on_the_host_and_skipped_on_the_device():
+    """max_pos = 8.  The host counts the steps and refuses the ninth; when the host guard is bypassed the kernels
+    themselves see the position, skip the cache write, raise the device status word, and a guard region behind the
+    caches stays untouched.  Nothing faults: the access is skipped, not attempted."""
+    from rptc_b200 import RPTCError, ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    for kv_heads in (4, 2):                                   # fused q/k/v finish + attention, and the separate kernels
+        cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=kv_heads, ffn=1024, vocab=512, max_pos=8, weight_scale=0.05)
+        model = RPTCLlama(cfg, rows=1, seed=2)
+        # caches re-seated inside larger buffers whose tails are the guard regions
+        guards = []
+        for name in ("kcache", "vcache"):
+            for i in range(cfg.layers):
+                big = torch.full((1, cfg.max_pos + 4, kv_heads, cfg.head_dim), 7.0, dtype=torch.float16, device="cuda")
+                getattr(model, name)[i] = big[:, : cfg.max_pos]
+                guards.append(big)
+        model.reset(torch.tensor([3]))
+        for _ in range(cfg.max_pos):
+            model.step()
+        torch.cuda.synchronize()
+        ops.device_status()                                   # eight steps fit
+        with pytest.raises(RuntimeError, match="max_pos"):
+            model.step()
+        model.step_eager()                                    # around the host guard: position 8 reaches the kernels
+        torch.cuda.synchronize()
+        with pytest.raises(RPTCError) as err:
+            ops.device_status()
+        assert err.value.status == -10                        # RPTC_ERR_RANGE
+        for big in guards:
+            assert bool((big[:, cfg.max_pos:] == 7.0).all()), "a kernel wrote behind the cache"
+        ops.device_status()                                   # the report cleared the word
+
+
+def test_rope_cache_kernel_skips_a_position_outside_the_cache():
+    from rptc_b200 import RPTCError, ops
+    hq, hkv, d, max_pos = 4, 2, 128, 8
+    qkv = torch.randn((1, (hq + 2 * hkv) * d), dtype=torch.float16, device="cuda")
+    before = qkv.clone()
+    big_k = torch.full((1, max_pos + 2, hkv, d), 7.0, dtype=torch.float16, device="cuda")
+    big_v = big_k.clone()
+    for bad in (8, -1, 2**31 - 1):
+        pos = torch.tensor([bad], dtype=torch.int32, device="cuda")
+        ops.rope_cache(qkv, pos, big_k[:, :max_pos], big_v[:, :max_pos], hq, hkv, d, 10000.0)
+        torch.cuda.synchronize()
+        with pytest.raises(RPTCError):
+            ops.device_status()
+        assert torch.equal(qkv, before) and bool((big_k == 7.0).all()) and bool((big_v == 7.0).all())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_two_devices_in_one_process():
+    """The opt-in to large dynamic shared memory is per device: the kernels must work on the second device a process
+    uses, not only on the first (plain local memory on each device, no peer operands)."""
+    from rptc_b200 import Format, ops
+    fmt = Format()
+    m, n = 256, 4096
+    results = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=f"cuda:{dev}").manual_seed(5)
+            codes = torch.randint(-2**31, 2**31 - 1, (m // 32, n // 64, 32, 4), dtype=torch.int32, device=f"cuda:{dev}", generator=g)
+            lut = torch.randn(512, dtype=torch.float16, device=f"cuda:{dev}", generator=g)
+            x = torch.eye(n, dtype=torch.float16, device=f"cuda:{dev}")[:8]
+            y8 = ops.gemv(codes, lut, x, m, n, fmt)
+            y1 = ops.gemv(codes, lut, x[:1], m, n, fmt)
+            dense = ops.decompress(codes, lut, m, n, fmt)
+            yg = ops.gemm(codes[: 128 // 32], lut, torch.eye(n, dtype=torch.float16, device=f"cuda:{dev}")[:256], 128, n, fmt)
+            torch.cuda.synchronize()
+            ops.device_status()
+            assert torch.equal(y8, dense.t()[:8]) and torch.equal(y1, dense.t()[:1]) and torch.equal(yg, dense[:128].t()[:256])
+            results.append(dense.cpu())
+    assert torch.equal(results[0], results[1])

@@ -96,3 +96,38 @@ def test_hf_llama_swap_and_packed_checkpoint(tmp_path):
         assert torch.equal(fresh.state_dict()[k], v), k
     # same codes and tables; the matvec's partial sums meet in a different order on every launch
     assert (again - got).abs().max().item() <= 2e-3 * want.abs().max().item()
+
+
+def test_packed_layer_geometry_for_llama2_7b_gate_proj_needs_no_gpu():
+    """11008 rows in 32 banks is 344 rows per bank: not a multiple of 32.  The reference accepts it
+    (quantize_hf.py:120-126 needs m % (num_banks * batch_size) == 0 only); the packed layer stores 11 blocks per bank."""
+    import quantize_hf as q
+    layer = q.FactorizedRPTCLinear(11008, 4096, 16, 32, device="cpu")
+    assert layer.bank_rows == 344 and layer.bank_blocks == 11
+    assert tuple(layer.codes.shape) == (32 * 11, 64, 32, 4)
+    codes, lut, stored, sl = layer._bank(31)
+    assert stored == 352 and codes.shape[0] == 11 and (sl.start, sl.stop) == (31 * 344, 11008)
+    with pytest.raises(ValueError):
+        q.FactorizedRPTCLinear(11008, 4096, 16, 33, device="cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens", [1, 12])
+def test_packed_layer_with_banks_that_are_not_whole_row_blocks(tokens):
+    """Llama-2-7B's gate projection height with the reference's default 32 banks, built from random symbols: the decode
+    equals the oracle's row by row, and the forward pass the dense product."""
+    import quantize_hf as q
+    g = torch.Generator().manual_seed(9)
+    m, n, L, banks = 11008, 256, 8, 32
+    symbols = torch.randint(0, 4, (m, n), generator=g, dtype=torch.int32)
+    alphabets = torch.randn((banks, 1 << L), generator=g)
+    ones, zeros = torch.ones(m), torch.zeros(m)
+    layer = q.FactorizedRPTCLinear.from_parts(symbols, alphabets, zeros, torch.zeros(n), ones, torch.ones(n))
+    dec = layer.decoded().cpu().numpy()
+    for r in (0, 343, 344, 5000, 11007):
+        want = o.dequantize_symbols(alphabets[r // 344].numpy().astype(np.float16), symbols[r].numpy())
+        assert np.array_equal(dec[r].view(np.uint16), want.view(np.uint16)), r
+    x = torch.randn(tokens, n, generator=g).cuda().half()
+    want = x.double() @ layer.decoded().double().t()
+    got = layer(x).double()
+    assert (got - want).abs().max().item() <= 2e-3 * want.abs().max().item()
