@@ -80,3 +80,71 @@ def assert_same_bits(a, b, what=""):
     if not torch.equal(a, b):
         bad = (a != b).nonzero()
         raise AssertionError(f"{what}: {len(bad)} of {a.numel()} elements differ, first at {bad[0].tolist()}")
+
+
+def hash_entry(t, S):
+    """Table entry the fused reference kernel looks up for window t (inference.cu:250-257)."""
+    t = t.astype(np.uint64)
+    return (((t * (t + 1)) >> np.uint64(8)) & np.uint64((1 << S) - 1)).astype(np.int64)
+
+
+def words_avoiding_low_entries(rng, m, n, S, lowest=8):
+    """Row-major stream words [m, n/16] in which NO step of the fused reference kernel looks up a table entry below
+    `lowest`, under that kernel's own history rule (every 32nd unit takes its own last word as carry, inference.cu:232;
+    this includes the first unit of a row, so even a row's first windows are not the near-zero ones).
+
+    Any bitstream is a valid trellis path, so the row is walked greedily: each 4-bit symbol is drawn (random order of
+    the 16 candidates) among those whose 16-bit window is `alive`: its entry is >= lowest and it has an alive successor
+    (the greatest such set, by pruning).  In a unit with the carry deviation the first three windows hold the unit's
+    LAST 16 bits; such a unit is redrawn until they comply."""
+    states = np.arange(1 << 16, dtype=np.uint32)
+    alive = hash_entry(states, S) >= lowest
+    succ = ((states[:, None] << 4) | np.arange(16, dtype=np.uint32)[None, :]) & 0xFFFF
+    while True:
+        pruned = alive & alive[succ].any(axis=1)
+        if (pruned == alive).all():
+            break
+        alive = pruned
+    assert alive.mean() > 0.5
+    nu = n // 64
+    nib = np.zeros((m, nu, 32), dtype=np.uint32)
+    hist = np.zeros(m, dtype=np.uint32)
+    for u in range(nu):
+        lane0 = u % 32 == 0
+        todo = np.ones(m, dtype=bool)
+        new_hist = hist.copy()
+        for _ in range(500):
+            idx = np.nonzero(todo)[0]
+            if len(idx) == 0:
+                break
+            k = len(idx)
+            h = hist[idx].copy()
+            nb = np.zeros((k, 32), dtype=np.uint32)
+            good = np.ones(k, dtype=bool)
+            start = 0
+            if lane0:                                  # checked at the end, against the unit's own last 16 bits
+                for s in range(3):
+                    nb[:, s] = rng.integers(0, 16, k)
+                    h = ((h << 4) | nb[:, s]) & 0xFFFF
+                start = 3
+            for s in range(start, 32):
+                cand = (rng.integers(0, 16, k)[:, None] + np.arange(16)[None, :]).astype(np.uint32) % 16
+                t = ((h[:, None] << 4) | cand) & 0xFFFF
+                ok = alive[t]
+                good &= ok.any(axis=1)                 # a dead end can only follow the three free symbols of a lane-0 unit
+                pick = ok.argmax(axis=1)
+                nb[:, s] = cand[np.arange(k), pick]
+                h = t[np.arange(k), pick]
+            if lane0:
+                hq = h.copy()
+                for s in range(3):
+                    hq = ((hq << 4) | nb[:, s]) & 0xFFFF
+                    good &= hash_entry(hq, S) >= lowest
+            nib[idx[good], u] = nb[good]
+            new_hist[idx[good]] = h[good]
+            todo[idx[good]] = False
+        assert not todo.any()
+        hist = new_hist
+    shifts = np.arange(28, -4, -4, dtype=np.uint32)
+    words = (nib.reshape(m, nu, 4, 8) << shifts[None, None, None, :]).sum(axis=3, dtype=np.uint64).astype(np.uint32)
+    return words.reshape(m, nu * 4)

@@ -4,7 +4,10 @@ oracle/build_ref.sh) on seeded inputs and saves inputs + output to an .npz.
 It runs as a child process of the GPU tests because the reference calls exit() on any CUDA error
 (inference.cu:32-39), which must not take the test session down with it.
 
-    python tests/ref_runner.py <decompress|matvec_16_8_1|matvec_16_6_1|matvec_t_16> <out.npz> <m> <n> <seed>
+    python tests/ref_runner.py <decompress|matvec_16_8_1|matvec_16_6_1|matvec_t_16> <out.npz> <m> <n> <seed> [words.npy]
+
+With a sixth argument the stream words ([m, n/16] uint32, row-major) are read from that file instead of being drawn.
+Exit codes: 0 done, 3 the reference extension is not built, 4 unknown entry point.
 """
 import glob
 import importlib.util
@@ -34,6 +37,9 @@ def main():
         sys.exit(3)
     rng = np.random.default_rng(seed)
     words = rng.integers(0, 2**32, (m, n // 16), dtype=np.uint64).astype(np.uint32)      # row-major stream words
+    if len(sys.argv) > 6:
+        words = np.load(sys.argv[6]).astype(np.uint32)
+        assert words.shape == (m, n // 16)
     x = rng.standard_normal(n).astype(np.float16)
     res = {"words": words, "x": x}
     dev = "cuda"

@@ -1,0 +1,162 @@
+"""The benchmark configurations run as they are written, each checked against the CPU oracle or the fp32 reference
+forward (full sizes: these are the parity cases behind the numbers bench.py reports).
+
+  config 1  one 4096 x 4096 linear: N(0,1) weights, random sign + Hadamard on both sides, encoded with the RPTC trellis
+            (L = 16, 2 bits per weight; rptc.py:13-71), then decompress + matvec on one fp16 vector
+  config 2  decompression only: 4096x4096, 4096x11008, 11008x4096, 8192x28672 at K = 2, 3, 4, bit-exact
+  config 4  the whole Llama-2-7B shape (32 layers): decode after a 128-token prompt, and one 2048-token forward, logits
+            against the fp32 forward of the same network
+(config 3, the layer-shape sweep of the fused GEMV / GEMM, is test_gpu_probe.py, test_gpu_gemv.py and test_gpu_gemm.py;
+config 5, the tensor-parallel 70B shape, is test_gpu_tp.py.)
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import c_oracle
+import rptc_oracle as o
+from gpu_util import GEMV_HFMA2_TOL, assert_same_bits, rand_lut, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- config 2 ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n", [(4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672)])
+@pytest.mark.parametrize("code,K,S", [(o.CODE_A, 2, 0), (o.CODE_A, 3, 0), (o.CODE_A, 4, 0), (o.CODE_B, 2, 8), (o.CODE_C, 2, 9)])
+def test_config2_decompress_bit_exact_at_full_size(m, n, code, K, S):
+    """Every element of every case against the multi-threaded C oracle (seeded random codes: any bitstream is a valid
+    trellis path; Gaussian table).  The native TILED layout, reached through rptc_repack from the row-major stream."""
+    from rptc_b200 import Format, ops
+    rng = np.random.default_rng(m * 5 + n * 3 + K + code)
+    rm = rng.integers(0, 2**32, (m, n * K // 32), dtype=np.uint64).astype(np.uint32)
+    lut = rand_lut(rng, code, 16, S)
+    ref = c_oracle.decompress(rm, lut, m, n, code=code, K=K, L=16, S=S, layout=o.LAYOUT_ROWMAJOR)
+    tiled = ops.repack(to_dev(rm), o.LAYOUT_ROWMAJOR, o.LAYOUT_TILED, m, n * K // 128)
+    got = ops.decompress(tiled, to_dev(lut), m, n, Format(code, K, 16, S, o.LAYOUT_TILED))
+    torch.cuda.synchronize()
+    ops.device_status()
+    assert_same_bits(got, torch.from_numpy(ref).cuda(), f"{m}x{n} code {code} K={K}")
+
+
+# ---- config 1 ---------------------------------------------------------------------------------------------------------
+def _fwht_rows(a: torch.Tensor, block: int) -> torch.Tensor:
+    """Orthonormal block-diagonal Hadamard transform along the last axis, fp32/fp64 torch (natural order)."""
+    r, n = a.shape
+    a = a.reshape(r, n // block, block)
+    h = 1
+    while h < block:
+        a = a.reshape(r, n // block, block // (2 * h), 2, h)
+        a = torch.stack((a[..., 0, :] + a[..., 1, :], a[..., 0, :] - a[..., 1, :]), dim=-2).reshape(r, n // block, block)
+        h *= 2
+    return a.reshape(r, n) / math.sqrt(block)
+
+
+def test_config1_single_linear_with_viterbi_codes_and_incoherence():
+    import rptc
+    from rptc_b200 import CODE_LUT, LAYOUT_ROWMAJOR, LAYOUT_TILED, Format, ops
+    from rptc_b200.linear import RPTCLinear, random_signs
+    m = n = 4096
+    L = 16
+    g = torch.Generator(device="cuda").manual_seed(42)
+    W = torch.randn(m, n, generator=g, device="cuda")                                   # iid N(0,1), fp32
+    s_in, s_out = random_signs(n, g, "cuda"), random_signs(m, g, "cuda")
+    # the matrix the trellis sees: W' = H D_out W D_in H, so that D_out H W' H D_in = W
+    Wt = _fwht_rows(W * s_in.float()[None, :], n)
+    Wt = _fwht_rows((Wt * s_out.float()[:, None]).t().contiguous(), m).t().contiguous()
+    M = 1 << L
+    q = (2 * torch.arange(M, dtype=torch.float64, device="cuda") + 1) / (2 * M)
+    alphabet = (2.0 ** 0.5 * torch.erfinv(2 * q - 1)).float()[torch.randperm(M, generator=g, device="cuda")]      # rptc.py:143-146
+    sym, loss = rptc.quantize_rows(alphabet, torch.ones(n, device="cuda"), Wt)          # the CUDA Viterbi encoder
+    assert int(sym.min()) >= 0 and int(sym.max()) <= 3
+    words = rptc.pack_symbols(sym)
+    fmt = Format(CODE_LUT, 2, L, 0, LAYOUT_TILED)
+    codes = ops.repack(words.contiguous(), LAYOUT_ROWMAJOR, LAYOUT_TILED, m, n // 64)
+    lut16 = alphabet.half()
+    lin = RPTCLinear(n, m, fmt, codes, lut16, 1.0, s_in, s_out)
+    # (a) decompress: every element against the CPU decode of the same packed codes
+    dense = lin.decoded()
+    ref = c_oracle.decompress(words.cpu().numpy().view(np.uint32), lut16.cpu().numpy(), m, n, code=0, K=2, L=L, layout=o.LAYOUT_ROWMAJOR)
+    assert_same_bits(dense, torch.from_numpy(ref).cuda(), "config 1 decompress")
+    for r in (0, 2047, m - 1):                                                          # and against the literal scan of rptc.py:74-85
+        want = o.dequantize_symbols(lut16.cpu().numpy(), sym[r].cpu().numpy())
+        assert np.array_equal(dense[r].cpu().numpy().view(np.uint16), want.view(np.uint16))
+    # (b) the code does its job: distortion of a 2-bit trellis code on Gaussian data (rate-distortion bound 0.0625)
+    mse = float(((Wt - dense.float()) ** 2).mean())
+    assert 0.06 < mse < 0.09, mse
+    torch.testing.assert_close(loss.sum() / (m * n), ((Wt - alphabet[sym_states(sym, L)]) ** 2).mean(), rtol=1e-3, atol=1e-5)
+    # (c) matvec on one fp16 vector: the fused kernel against the CPU path (C oracle: decode + fp32 matvec) on the
+    # transformed activations, and the whole layer against the effective dense matrix
+    x = torch.randn(n, generator=g, device="cuda").half()
+    xt = lin.transform_in(x[None, :])
+    acc = torch.zeros((1, m), dtype=torch.float32, device="cuda")
+    lin.matvec_acc(xt, acc)
+    torch.cuda.synchronize()
+    cpu = c_oracle.gemv(words.cpu().numpy().view(np.uint32), lut16.cpu().numpy(), xt.cpu().numpy(), m, n, code=0, K=2, L=L, layout=0)
+    exact = xt.double() @ dense.double().t()
+    bound = GEMV_HFMA2_TOL * dense.double().norm(dim=1)[None, :] * xt.double().norm() + 1e-4
+    assert bool(((acc.double() - exact).abs() <= bound).all())
+    assert bool(((torch.from_numpy(cpu).cuda().double() - exact).abs() <= 1e-5 * dense.double().norm(dim=1)[None, :] * xt.double().norm() + 1e-4).all())
+    y = lin(x[None, :]).double()[0]
+    want = lin.effective_weight().double() @ x.double()
+    rel = float((y - want).abs().max() / want.abs().max())
+    assert rel <= 4e-3, rel                          # fp16 roundings of the two transforms on top of the matvec's own
+    # the quantised layer approximates the original one as a 2-bit code can: relative error ~ sqrt(mse)
+    true = W.double() @ x.double()
+    assert float((y - true).norm() / true.norm()) < 0.35
+    ops.device_status()
+
+
+def sym_states(sym: torch.Tensor, L: int) -> torch.Tensor:
+    state = torch.zeros(sym.shape[0], dtype=torch.int64, device=sym.device)
+    out = torch.empty(sym.shape, dtype=torch.int64, device=sym.device)
+    for i in range(sym.shape[1]):
+        state = ((state << 2) | sym[:, i].long()) & ((1 << L) - 1)
+        out[:, i] = state
+    return out
+
+
+# ---- config 4 ---------------------------------------------------------------------------------------------------------
+# Stated tolerance: max |logit - reference| <= LOGIT_TOL * max |reference| at every checked position.
+LOGIT_TOL = 1e-2
+
+
+def test_config4_llama2_7b_shape_decode_and_prefill_logits():
+    """All 32 layers of the Llama-2-7B shape, every block linear RPTC 2-bit (HASH S=8, RHT both sides), random-init,
+    uniform-random token ids.  (a) a 128-token prompt through the fused dequant-GEMM, then 8 decode steps through the
+    captured CUDA graph: logits of the last prompt position and of every decode step; (b) one 2048-token forward: logits
+    of its last position.  Reference: fp32 torch forward of the same network with the bit-exact decoded weights."""
+    from rptc_b200 import ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig.llama2_7b(max_pos=2048 + 16)
+    model = RPTCLlama(cfg, rows=1, seed=1)
+    g = torch.Generator(device="cuda").manual_seed(42)
+    P, D = 128, 8
+    tokens = torch.randint(0, cfg.vocab, (1, P + D), device="cuda", generator=g)
+    with torch.no_grad():
+        ref = model.reference_logits(tokens)                  # [1, P + D, vocab] fp32
+    worst = {}
+    model.reset()
+    got = model.prefill(tokens[:, :P]).float()
+    torch.cuda.synchronize()
+    worst["prefill 128"] = float((got - ref[:, P - 1]).abs().max() / ref[:, P - 1].abs().max())
+    model.capture(pdl=True)
+    for t in range(P, P + D):
+        model.ids.copy_(tokens[:, t].to(torch.int32))
+        model.step()
+        torch.cuda.synchronize()
+        worst[f"decode {t}"] = float((model.logits.float() - ref[:, t]).abs().max() / ref[:, t].abs().max())
+    ops.device_status()
+    del ref
+    long_tokens = torch.randint(0, cfg.vocab, (1, 2048), device="cuda", generator=g)
+    with torch.no_grad():
+        ref_last = model.reference_logits(long_tokens)[:, -1].clone()
+    model.graph = None
+    model.reset()
+    got = model.prefill(long_tokens).float()
+    torch.cuda.synchronize()
+    ops.device_status()
+    worst["prefill 2048"] = float((got - ref_last).abs().max() / ref_last.abs().max())
+    print("config 4 max-rel logit error: " + ", ".join(f"{k}: {v:.2e}" for k, v in worst.items()))
+    assert max(worst.values()) <= LOGIT_TOL, worst

@@ -153,3 +153,16 @@ def test_rht_matches_scipy_hadamard():
     assert np.allclose(o.rht(x, s, 256), (x * s) @ H.T)
     assert np.allclose(o.rht(o.rht(x, s, 256), s, 256, transpose=True), x)
     assert o.hadamard_block(11008) == 256 and o.hadamard_block(4096) == 4096 and o.hadamard_block(28672) == 4096
+
+
+@pytest.mark.parametrize("S", [8, 6])
+def test_streams_built_for_the_reference_binary_pin_avoid_entries_below_eight(S):
+    """The generator behind the exact pin of the HASH code against the compiled reference kernel (tests/test_gpu_legacy.py):
+    under that kernel's own history rule no step may look up a table entry below 8."""
+    from gpu_util import hash_entry, words_avoiding_low_entries
+    n = 4096
+    w = words_avoiding_low_entries(np.random.default_rng(S), 64, n, S)
+    assert w.shape == (64, n // 16) and w.dtype == np.uint32
+    win = o.windows(w, 4, n // 2, o.QUIRK_K2_LANE0_CARRY)
+    assert (hash_entry(win, S) >= 8).all()
+    assert abs(np.unpackbits(w.view(np.uint8)).mean() - 0.5) < 0.01          # still looks like a random stream
