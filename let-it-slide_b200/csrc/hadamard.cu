@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p
             const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
             const int j = (idx & 63) + i;                       // frequency index
             float sn, cs;
-            sincosf(ps * __powf(p.theta, -2.f * j / 128.f), &sn, &cs);
+            sincosf(ps * powf(p.theta, -2.f * j / 128.f), &sn, &cs);
             o[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
         }
         if (head < p.hq) store8_f16(p.q_out + row * p.ld_q + col, o);

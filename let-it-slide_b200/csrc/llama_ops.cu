@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     if (head < hq + hkv) {
         float lo = 0.f, hi = 0.f;
         if (t < d / 2) {
-            const float inv_freq = __powf(theta, -2.f * t / d);
+            const float inv_freq = powf(theta, -2.f * t / d);
             float sn, cs;
             sincosf(p * inv_freq, &sn, &cs);
             const float a = __half2float(src[t]), b = __half2float(src[t + d / 2]);
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(256) rope_cache_prompt_kernel(__half *__restri
     const int half_d = d / 2, i = threadIdx.x % 64, grp = threadIdx.x / 64;      // pair index, head group (4 groups)
     if (i >= half_d) return;
     float sn, cs;
-    sincosf(p * __powf(theta, -2.f * i / d), &sn, &cs);
+    sincosf(p * powf(theta, -2.f * i / d), &sn, &cs);
     __half *tok = qkv + ((int64_t)row * T + p) * ld_qkv;
     for (int head = grp; head < hq + 2 * hkv; head += 4) {
         __half *src = tok + (int64_t)head * d;
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         const int grp0 = t >> 4;
         if (signs_out && grp0 < 3) so_raw = *reinterpret_cast<const uint4 *>(signs_out + (grp0 == 0 ? head : grp0 == 1 ? hq + kvh : hq + hkv + kvh) * D + i8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * __powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &rot_sn[i], &rot_cs[i]);
+        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &rot_sn[i], &rot_cs[i]);
     }
     if (fused) {
         // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv

@@ -550,10 +550,15 @@ class RPTCLlama:
         ops.next_token(self.logits, self.next_ids, self.ids, self.pos, None)        # pos -> T, ids -> greedy choice
         return self.logits
 
-    def reference_logits(self, tokens: torch.Tensor) -> torch.Tensor:
-        """fp32 torch forward of the same network on `tokens` [rows, T] -> logits [rows, T, vocab]."""
+    def reference_logits(self, tokens: torch.Tensor, act_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """fp32 torch forward of the same network on `tokens` [rows, T] -> logits [rows, T, vocab].
+
+        act_dtype = torch.float16 gives the yardstick of a stock half-precision evaluation instead: the same fp32 arithmetic,
+        but every activation that a half-precision model stores (the normalised layer inputs, q/k/v, the attention output,
+        the gated-MLP middle, the residual stream) is rounded to fp16 where it is stored."""
         cfg = self.cfg
         T = tokens.shape[1]
+        rnd = (lambda t: t) if act_dtype is None else (lambda t: t.to(act_dtype).float())
         h = self.embed[tokens.long()].float()
         half = cfg.head_dim // 2
         inv = cfg.rope_theta ** (-torch.arange(half, device=self.device, dtype=torch.float32) * 2 / cfg.head_dim)
@@ -561,11 +566,11 @@ class RPTCLlama:
         cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
 
         def rms(x, w):
-            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.rms_eps) * w.float()
+            return rnd(x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.rms_eps) * w.float())
 
         def rope(x):
             a, b = x[..., :half], x[..., half:]
-            return torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1)
+            return rnd(torch.cat((a * cs - b * sn, b * cs + a * sn), dim=-1))
 
         q_dim, kv_dim = self.heads_l * cfg.head_dim, self.kv_heads_l * cfg.head_dim
         mask = torch.full((T, T), float("-inf"), device=self.device).triu(1)
@@ -578,18 +583,18 @@ class RPTCLlama:
 
         for b in self.blocks:
             x = rms(h, b.norm1)
-            qkv = x @ b.qkv.effective_weight().t()
+            qkv = rnd(x @ b.qkv.effective_weight().t())
             q = rope(qkv[..., :q_dim].reshape(-1, T, self.heads_l, cfg.head_dim))
             k = rope(qkv[..., q_dim:q_dim + kv_dim].reshape(-1, T, self.kv_heads_l, cfg.head_dim))
             v = qkv[..., q_dim + kv_dim:].reshape(-1, T, self.kv_heads_l, cfg.head_dim)
             rep = self.heads_l // self.kv_heads_l
             k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
             att = torch.einsum("bthd,bshd->bhts", q, k) * cfg.head_dim ** -0.5 + mask
-            o = torch.einsum("bhts,bshd->bthd", att.softmax(-1), v).reshape(-1, T, q_dim)
-            h = h + reduce(o @ b.o.effective_weight().t())
+            o = rnd(torch.einsum("bhts,bshd->bthd", att.softmax(-1), v).reshape(-1, T, q_dim))
+            h = rnd(h + reduce(o @ b.o.effective_weight().t()))
             x = rms(h, b.norm2)
-            gu = x @ b.gate_up.effective_weight().t()
-            h = h + reduce((torch.nn.functional.silu(gu[..., : self.ffn_l]) * gu[..., self.ffn_l:]) @ b.down.effective_weight().t())
+            gu = rnd(x @ b.gate_up.effective_weight().t())
+            h = rnd(h + reduce(rnd(torch.nn.functional.silu(gu[..., : self.ffn_l]) * gu[..., self.ffn_l:]) @ b.down.effective_weight().t()))
         return rms(h, self.norm_f) @ self.head.float().t()
 
 

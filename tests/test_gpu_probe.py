@@ -239,11 +239,11 @@ def test_probe_matvec_that_computes_its_rmsnorm_input(m, n, rows, with_acc):
 
 
 @pytest.mark.parametrize("rows", [1, 2])
-@pytest.mark.parametrize("m,n,block", [(4096, 11008, 256), (8192, 3584, 256), (4096, 1792, 128)])
+@pytest.mark.parametrize("m,n,block", [(4096, 11008, 256), (8192, 3584, 256), (4096, 1792, 64)])
 def test_probe_down_projection_that_computes_its_swiglu_input(m, n, rows, block):
     """rptc_gemv_swiglu: x = H(s_in * fp16(silu(g) * u)) in blocks of `block` columns, (g | u) the output transform of
     the gate-up accumulator.  With g = 1 and u = +-u0 (u0 the fp16 number for which fp16(silu(1) * u0) is exactly 1) in
-    one block and u = 0 elsewhere, x is exactly sqrt(block) * e_c."""
+    one block and u = 0 elsewhere, x is exactly sqrt(block) * e_c (blocks of 4^k columns, so that the factor is a power of two)."""
     from rptc_b200 import Format, ops
     fmt = Format()
     codes, lut = _random_layer(m, n, fmt, m + n + rows + block)
