@@ -125,6 +125,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// Ampere-style asynchronous copy of 16 bytes global -> shared, bypassing L1; completion is tracked per thread in groups.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {      // until at most N of this thread's groups are still in flight
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -169,6 +178,12 @@ __device__ __forceinline__ uint32_t ld_ordered_u32(const void *p) {
     uint32_t v;
     asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+// (a & mask) | c as ONE three-input logic instruction (the compiler does not always fuse the pair).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
+    return d;
 }
 __device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 __device__ __forceinline__ uint32_t half2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
@@ -360,7 +375,7 @@ __device__ __forceinline__ void make_windows(const uint32_t (&w)[GroupShape<K>::
 // Weight pair p (columns 2p, 2p+1) of a group from its window registers.  `p` must be a constant after unrolling.
 // The registers may cover any whole number of words (a group, or a single word with the word before it).
 template <int CODE, int K, int N>
-__device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[N], const Lut<CODE> &lut, int p) {
+__device__ __forceinline__ uint32_t decode_pair_bits(const uint32_t (&R)[N], const Lut<CODE> &lut, int p) {
     if (CODE == RPTC_CODE_LUT) {
         uint32_t h[2];
 #pragma unroll
@@ -371,7 +386,7 @@ __device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[N], const Lut
             const uint32_t state = (R[o] >> sh) & lut.mask;
             h[q] = lds16(lut.base + 2u * state);
         }
-        return u32_as_half2(h[0] | (h[1] << 16));
+        return h[0] | (h[1] << 16);
     } else {
         constexpr int BPS = 2 * K;   // bits per step
         const int e = BPS * (p + 1);
@@ -380,15 +395,44 @@ __device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[N], const Lut
         const uint32_t t = R[o] >> sh;
         if (CODE == RPTC_CODE_HASH) {
             const uint32_t h = t * t + t;
-            return u32_as_half2(lds32_hash((h & 0xFF00u) | lut.base));
+            return lds32_hash(and_or(h, 0xFF00u, lut.base));
         } else {
             // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
             // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.
             uint32_t h = t * (2u * t + 1u);
             h ^= h >> lut.shift;
-            return u32_as_half2(lds32(lut.base + ((h & lut.mask) << 7)));
+            return lds32(lut.base + ((h & lut.mask) << 7));
         }
     }
+}
+// Four consecutive pairs p0 .. p0+3 at once, written stage by stage (all windows, then all hashes, then all addresses, then all
+// loads) so that four independent dependency chains are in flight instead of one.
+template <int CODE, int K, int N>
+__device__ __forceinline__ void decode_quad_bits(const uint32_t (&R)[N], const Lut<CODE> &lut, int p0, uint32_t (&out)[4]) {
+    if (CODE == RPTC_CODE_HASH) {
+        uint32_t t[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = 2 * K * (p0 + i + 1);
+            const int o = (e - 1) >> 4;
+            const int sh = 16 * (o + 1) - e;
+            t[i] = R[o] >> sh;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) t[i] = t[i] * t[i] + t[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) t[i] = and_or(t[i], 0xFF00u, lut.base);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = lds32_hash(t[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = decode_pair_bits<CODE, K>(R, lut, p0 + i);
+    }
+}
+// The same as an fp16 pair (low half = column 2p).
+template <int CODE, int K, int N>
+__device__ __forceinline__ __half2 decode_pair(const uint32_t (&R)[N], const Lut<CODE> &lut, int p) {
+    return u32_as_half2(decode_pair_bits<CODE, K>(R, lut, p));
 }
 
 template <int CODE, int K, typename Emit>

@@ -69,6 +69,13 @@ __device__ __forceinline__ int64_t k2_legacy_pair(int64_t s, int64_t n) {
     return 4 * (p % q8) + p / q8;
 }
 
+// D += A B on one 16 x 8 x 16 tile: fp16 operands, fp32 accumulation.
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // The general kernel: any layout (strided 128-bit loads straight from memory, one unit of one row block per
 // step), the reference kernels' lane-0 deviations, batch 1.  The native TILED layout takes the two kernels below.
 template <int CODE, int K>
@@ -191,24 +198,39 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     if (!waited_prior) pdl_wait_prior_grids();
 }
 
-// ---- the batch 1-2 fast path: two row blocks per warp ----------------------------------------------------
-// Same decomposition as gemv_kernel, but a granule is one unit of TWO adjacent row blocks (lane l owns rows
-// 64*p + l and 64*p + 32 + l).  The two 512-byte pieces arrive in one ring stage on one mbarrier, and the
-// activation quads read from shared memory serve both rows: the broadcast x loads, which cost more
-// shared-memory wavefronts than their count suggests, are halved per weight.  TILED layout only.
+// ---- batch 1-2: lane = row, products on the tensor cores -----------------------------------------------------------
+// The decomposition of the pair kernel (a granule = one 128-bit unit of two adjacent 32-row blocks, lane l owns rows
+// 64*p + l and 64*p + 32 + l, a warp walks along its rows), with two changes.
 //
-// INPUT != 0: instead of copying x from memory each CTA computes it from the previous layer's accumulator and
-// the residual stream: the single-CTA glue kernel between two matvecs, its launch and its round trip through
-// memory disappear, at the price of every CTA repeating the arithmetic of one 4096-element row.
-template <int CODE, int K, int BATCH, int INPUT>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvParams p) {
+// Products.  One mma.sync m16n8k16 (fp16 in, fp32 accumulate) takes FOUR decoded pairs of a lane at once: pairs 2i and
+// 2i+1 of the lane's row in block a (a0, a2) and of its row in block b (a1, a3).  Rows g and g+8 of the A tile are then
+// a mix of the four lanes (g, 0..3), i.e. of four different rows of W -- which is harmless, because B separates them
+// again: lane t's k slots meet the activations only in output column n = t (first activation row) and n = 4 + t
+// (second), every other entry of B is zero.  D[g][4b + t] is the partial dot product of row 4g + t of block a with
+// activation row b, D[g+8][4b + t] the same for block b.  B costs less than before: the lane that supplies column
+// n = g of B reads the activations when g % 4 == t (and g / 4 < BATCH) and holds zeros otherwise, so only four (eight)
+// lanes of a warp take part in the shared-memory loads of x.  Against the HFMA2 form this removes 24
+// of 32 multiply instructions per unit and row block and all fp16 partial sums: the accumulation is fp32 throughout.
+//
+// Codes.  Each lane copies its own 16 bytes of a unit from global memory into a per-warp shared-memory ring with
+// cp.async (the 32 rows of a unit are 512 contiguous bytes in the TILED layout: one fully coalesced request per warp),
+// three granules ahead, and reads back only its own bytes: the per-thread group wait is the whole synchronisation --
+// no barrier, no lane that issues copies on behalf of the others, no register or scoreboard held by a load in flight.
+//
+// MODE 0: activations copied from memory.  MODE 1: computed by every CTA from the previous layer's accumulator and the
+// residual stream (rptc_gemv_glued).  MODE 2: the down projection of a gated MLP -- granules ordered by 256-column
+// blocks first, each CTA makes the blocks of x it needs from the gate-up accumulator (rptc_gemv_swiglu).
+template <int CODE, int K, int BATCH, int MODE>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;
     constexpr int PAIRS = WPU / 2;
     constexpr int NW2 = 2 * GroupShape<K>::kWords;
+    constexpr uint32_t UPB = 256 / WPU;                       // units per 256-column block (MODE 2)
+    static_assert(BATCH == 1 || BATCH == 2, "eight output columns: four rows x two activation rows");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
     const uint32_t s0 = smem_addr(smem_raw);
-    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
     const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
     uint32_t lut_tab, xs;
     if (CODE == RPTC_CODE_HASH) {
@@ -224,93 +246,164 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
     }
     // ---- prologue: nothing here depends on the kernels before this one ----
     const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
-        mbar_fence_init();
-    }
-    __syncwarp();
     const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
     pdl_allow_next_grid();
 
     const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
-    const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
     const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;
     const int64_t rb_stride = (int64_t)p.n_units << 5;        // 128-bit units between row blocks of the TILED layout
-    uint32_t slot = 0, phase = 0;
-    bool ok = true, waited_prior = false;
-    bool table_pending = false;      // the table's values are in registers; they go to shared memory under the first loads
+    // this lane's column of B: activation row g / 4 for the lanes with g % 4 == t, zeros for the others
+    const bool feeds_x = (g & 3) == t4 && (g >> 2) < BATCH;
+    // where this lane's sums end up: D[g][2t], D[g][2t+1] are rows 4g + (2t & 3) + {0, 1}, activation row t / 2
+    const int out_row = 4 * g + ((2 * t4) & 3), out_batch = t4 >> 1;
+    bool waited_prior = false;
 
     for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
-        const int32_t nu = min(p.seg_units, p.n_units - useg0);
+        const int32_t nu = MODE == 2 ? p.n_units : min(p.seg_units, p.n_units - useg0);
+        // Two-level even split of the T granules: contiguous ranges per CTA (sizes differ by at most one), then per warp
+        // inside the CTA (again by at most one).  The warps that carry one granule more are thereby spread over all SMs
+        // -- and over the four schedulers of each -- instead of filling the first CTAs of the grid.
         const uint32_t T = n_rbp * (uint32_t)nu;
-        const uint32_t per = T / GW, extra = T - per * GW;
-        const uint32_t g0 = gw * per + min(gw, extra);
-        const uint32_t count = per + (gw < extra ? 1u : 0u);
-        const uint32_t rbp0 = count ? g0 / (uint32_t)nu : 0u;
-        const int32_t u0 = count ? (int32_t)(g0 - rbp0 * (uint32_t)nu) : 0;
+        const uint32_t cta_per = T / gridDim.x, cta_extra = T - cta_per * gridDim.x;
+        const uint32_t cta_g0 = blockIdx.x * cta_per + min((uint32_t)blockIdx.x, cta_extra);
+        const uint32_t cta_n = cta_per + (blockIdx.x < cta_extra ? 1u : 0u);
+        const uint32_t w_per = cta_n / kGemvWarps, w_extra = cta_n - w_per * kGemvWarps;
+        const uint32_t g0 = cta_g0 + (uint32_t)warp * w_per + min((uint32_t)warp, w_extra);
+        const uint32_t count = w_per + ((uint32_t)warp < w_extra ? 1u : 0u);
 
-        // fetch cursor (lane 0)
-        uint32_t frbp = rbp0;
-        int32_t fu = u0;
-        const uint4 *fptr = p.codes + (int64_t)(2 * rbp0) * rb_stride + ((int64_t)(useg0 + u0) << 5);
-        auto issue_stage = [&](uint32_t at_slot) {
-            const bool has_b = 2 * frbp + 1 < n_rb;
-            const uint32_t bar = bars + 8u * at_slot, dst = ring + at_slot * kStageBytes;
-            mbar_expect_tx(bar, has_b ? 2 * kUnitBytes : kUnitBytes);
-            bulk_g2s(dst, fptr, kUnitBytes, bar);
-            if (has_b) bulk_g2s(dst + kUnitBytes, fptr + rb_stride, kUnitBytes, bar);
-            fptr += 32;
-            if (++fu == nu) {
-                fu = 0;
-                ++frbp;
-                fptr = p.codes + (int64_t)(2 * frbp) * rb_stride + ((int64_t)useg0 << 5);
+        // ---- granule order.  MODE 0/1: pairs of row blocks outermost, units along the row.  MODE 2: 256-column
+        // blocks outermost, then pairs of row blocks, then the units of the block.
+        struct Cursor {
+            uint32_t rbp;       // pair of row blocks
+            int32_t u;          // unit within the row (MODE 2) or within the segment (MODE 0/1)
+            const uint4 *ptr;   // this lane's 16 bytes of block a
+        };
+        const uint32_t cell = n_rbp * UPB;
+        auto cursor_at = [&](uint32_t gi) {
+            Cursor c;
+            if (MODE == 2) {
+                const uint32_t cb = gi / cell, rem = gi - cb * cell;
+                c.rbp = rem / UPB;
+                c.u = (int32_t)(cb * UPB + (rem - c.rbp * UPB));
+            } else {
+                c.rbp = gi / (uint32_t)nu;
+                c.u = (int32_t)(gi - c.rbp * (uint32_t)nu);
+            }
+            c.ptr = p.codes + (int64_t)(2 * c.rbp) * rb_stride + ((int64_t)(useg0 + c.u) << 5) + lane;
+            return c;
+        };
+        auto advance = [&](Cursor &c) {      // to the next granule in this kernel's order
+            ++c.u;
+            c.ptr += 32;
+            if (MODE == 2) {
+                if (((uint32_t)c.u & (UPB - 1)) == 0) {      // end of the 256-column block: same block, next pair of row blocks
+                    c.u -= (int32_t)UPB;
+                    if (++c.rbp == n_rbp) {
+                        c.rbp = 0;
+                        c.u += (int32_t)UPB;
+                    }
+                    c.ptr = p.codes + (int64_t)(2 * c.rbp) * rb_stride + ((int64_t)c.u << 5) + lane;
+                }
+            } else if (c.u == nu) {
+                c.u = 0;
+                ++c.rbp;
+                c.ptr = p.codes + (int64_t)(2 * c.rbp) * rb_stride + ((int64_t)useg0 << 5) + lane;
             }
         };
-        uint32_t to_issue = count;
-        {
-            const uint32_t ahead = min(count, (uint32_t)kStages);
-            if (lane == 0) {
-                uint32_t sl = slot;
-                for (uint32_t k = 0; k < ahead; ++k) {
-                    issue_stage(sl);
-                    if (++sl == kStages) sl = 0;
-                }
+        Cursor fc = cursor_at(count ? g0 : 0u);      // fetch cursor
+        Cursor cc = fc;                              // decode cursor
+        // ---- the first PF granules and the 16 stream bits in front of the first one: all of it weights, so all of it
+        // can be under way before anything that depends on the grid in front
+        // Each lane copies its own 16 bytes of both row blocks into the warp's ring with asynchronous copies (tracked per
+        // thread in groups, one group per granule: no register, scoreboard or barrier is tied up while they travel) and
+        // reads back only what it copied itself, so the group wait is all the synchronisation there is.
+        uint32_t fetched = 0;
+        auto fetch = [&](uint32_t slot) {
+            if (fetched < count) {
+                const uint32_t dst = ring + slot * kStageBytes + 16u * lane;
+                cp_async16(dst, fc.ptr);
+                cp_async16(dst + kUnitBytes, 2 * fc.rbp + 1 < n_rb ? fc.ptr + rb_stride : fc.ptr);      // no second block: block a again, sums dropped
+                advance(fc);
+                ++fetched;
             }
-            to_issue -= ahead;
+            cp_async_commit();      // an empty group when nothing is left keeps the count of groups in flight constant
+        };
+        // Before the dependency wait only the first granule is requested: a lane's copies queue up in the load/store unit,
+        // and a full ring of them ahead of the activation loads would delay those -- the critical ones -- by a trip to DRAM.
+        // The rest of the ring follows as soon as the activation loads are on their way (`late_prologue`).
+        if (MODE == 0) fetch(0);
+        bool late_pending = true;
+        auto late_prologue = [&]() {
+            if (!late_pending) return;
+            late_pending = false;
+#pragma unroll
+            for (int i = MODE == 0 ? 1 : 0; i < kStages; ++i) fetch(i);
+            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);      // the codebook loads were issued long ago
+        };
+        // The 16 stream bits in front of a run's first unit (the last word of the unit before it in the same rows, or the
+        // shard's carry_in at a row start) are fetched one run ahead: those of the first two runs here, before the wait.
+        auto load_history = [&](const Cursor &c, uint32_t &pa, uint32_t &pb) {
+            const int64_t row_a = ((int64_t)c.rbp << 6) + lane;
+            const bool has_b = 2 * c.rbp + 1 < n_rb;
+            if (useg0 + c.u == 0) {
+                pa = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
+                pb = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
+            } else {
+                const uint32_t *last = reinterpret_cast<const uint32_t *>(c.ptr - 32) + 3;
+                pa = __ldg(last);
+                pb = has_b ? __ldg(last + 4 * rb_stride) : 0u;
+            }
+        };
+        auto run_length = [&](const Cursor &c) -> uint32_t {      // granules from c to the end of its run
+            return MODE == 2 ? UPB - ((uint32_t)c.u & (UPB - 1)) : (uint32_t)(nu - c.u);
+        };
+        auto run_after = [&](const Cursor &c) {                    // first granule of the run after the one c lies in
+            Cursor n = c;
+            if (MODE == 2) {
+                n.u = (int32_t)((uint32_t)c.u & ~(UPB - 1));
+                if (++n.rbp == n_rbp) {
+                    n.rbp = 0;
+                    n.u += (int32_t)UPB;
+                }
+            } else {
+                n.u = 0;
+                ++n.rbp;
+            }
+            n.ptr = p.codes + (int64_t)(2 * n.rbp) * rb_stride + ((int64_t)(useg0 + n.u) << 5) + lane;
+            return n;
+        };
+        uint32_t prev_a = 0u, prev_b = 0u, next_prev_a = 0u, next_prev_b = 0u;
+        uint32_t left_after_run = 0;          // granules of this warp behind the current run
+        if (count) {
+            load_history(cc, prev_a, prev_b);
+            const uint32_t len = min(run_length(cc), count);
+            left_after_run = count - len;
+            if (left_after_run) load_history(run_after(cc), next_prev_a, next_prev_b);
         }
 
-        // The 16 stream bits in front of this warp's first unit: part of the weights, so they can be fetched before
-        // anything that depends on the grid in front (later runs start at a row's first unit and need no fetch).
-        uint32_t first_prev_a = 0u, first_prev_b = 0u;
-        if (count) {
-            const int64_t row_a = ((int64_t)rbp0 << 6) + lane;
-            const bool has_b = 2 * rbp0 + 1 < n_rb;
-            const int32_t ug = useg0 + u0;
-            if (ug == 0) {
-                first_prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
-                first_prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
-            } else {
-                const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp0) * rb_stride +
-                                                                           ((int64_t)(ug - 1) << 5) + lane) + 3;
-                first_prev_a = __ldg(last);
-                first_prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
-            }
-        }
-        // ---- activations of this column segment -> shared memory ----
+        // ---- activations -> shared memory ----
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
-            // the codebook loads were issued before the wait; with computed activations the table is written while the
-            // glue's own loads are in flight (below)
-            table_pending = true;
-            if (INPUT != 0 && p.n != 4096) {
-                lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
-                table_pending = false;
-            }
         }
         if (useg0 > 0) __syncthreads();
-        if (INPUT != 0) {
+        if (MODE == 2) {
+            // column blocks of this CTA's warps together (its granules are consecutive)
+            const uint32_t cb_first = cta_g0 / cell, cb_last = cta_n ? (cta_g0 + cta_n - 1) / cell : cb_first;
+            if (p.clear) {
+                float4 *z = reinterpret_cast<float4 *>(p.clear);
+                for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.clear_count; i += (int64_t)gridDim.x * kGemvThreads)
+                    z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+            for (uint32_t b = cb_first + warp; b <= cb_last; b += kGemvWarps)
+#pragma unroll 1
+                for (int r = 0; r < BATCH; ++r)
+                    swiglu_chunk(p.sw, r, (int64_t)b * 256 + 8 * lane, nullptr, false,
+                                 x_sm + (size_t)r * (x_batch_stride >> 1) + (size_t)(b - cb_first) * 256 + 8 * lane, late_prologue);
+            // x of unit u sits at xs + (u - cb_first * UPB) * 2 WPU: fold the offset into the base
+            xs -= cb_first * UPB * (uint32_t)(WPU * 2);
+        } else if (MODE == 1) {
             // one segment by construction (the host refuses wider rows)
             if (p.in.clear) {
                 float4 *z = reinterpret_cast<float4 *>(p.in.clear);
@@ -318,34 +411,29 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                      i += (int64_t)gridDim.x * kGemvThreads)
                     z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
-            {
-                float *ex = reinterpret_cast<float *>(smem_raw + (xs - s0) + BATCH * x_batch_stride);
-                FinishNormParams q;
-                q.acc = const_cast<float *>(p.in.acc);
-                q.ld_acc = p.in.ld_acc;
-                q.signs_out = static_cast<const __half *>(p.in.signs_out);
-                q.scale_out = p.in.scale_out;
-                q.h = const_cast<__half *>(static_cast<const __half *>(p.in.h_in));
-                q.h_out = static_cast<__half *>(p.in.h_out);
-                q.ld_h = p.in.ld_h;
-                q.w_norm = static_cast<const __half *>(p.in.w_norm);
-                q.eps = p.in.eps;
-                q.signs_in = static_cast<const __half *>(p.in.signs_in);
-                q.transform_in = 1;
-                q.out = x_sm;
-                q.ld_out = x_batch_stride >> 1;
-                q.n = (int32_t)p.n;
-                q.block = 4096;
+            if (p.n != 4096) late_prologue();      // the wide form has no hook
+            float *ex = reinterpret_cast<float *>(smem_raw + (xs - s0) + BATCH * x_batch_stride);
+            FinishNormParams q;
+            q.acc = const_cast<float *>(p.in.acc);
+            q.ld_acc = p.in.ld_acc;
+            q.signs_out = static_cast<const __half *>(p.in.signs_out);
+            q.scale_out = p.in.scale_out;
+            q.h = const_cast<__half *>(static_cast<const __half *>(p.in.h_in));
+            q.h_out = static_cast<__half *>(p.in.h_out);
+            q.ld_h = p.in.ld_h;
+            q.w_norm = static_cast<const __half *>(p.in.w_norm);
+            q.eps = p.in.eps;
+            q.signs_in = static_cast<const __half *>(p.in.signs_in);
+            q.transform_in = 1;
+            q.out = reinterpret_cast<__half *>(smem_raw + (xs - s0));
+            q.ld_out = x_batch_stride >> 1;
+            q.n = (int32_t)p.n;
+            q.block = 4096;
 #pragma unroll 1
-                for (int b = 0; b < BATCH; ++b) {
-                    if (p.n == 4096)
-                        finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, [&]() {
-                            if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
-                            table_pending = false;
-                        });
-                    else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
-                }
+            for (int b = 0; b < BATCH; ++b) {
+                if (p.n == 4096)
+                    finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, late_prologue);
+                else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
             }
         } else {
             const int64_t col0 = (int64_t)useg0 * WPU;
@@ -361,8 +449,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
-                        if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);       // under the loads above
-                        table_pending = false;
+                        late_prologue();                                                       // under the loads above
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (i0 + k * kGemvThreads < vecs)
@@ -381,274 +468,33 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_pair_kernel(const GemvPa
                 }
             }
         }
-        if (table_pending) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);       // threads that loaded nothing, other paths
-        table_pending = false;
+        late_prologue();      // threads that loaded nothing, other paths
         __syncthreads();
 
-        // ---- main loop: runs of consecutive units inside one pair of row blocks ----
-        uint32_t rbp = rbp0;
-        int32_t u = u0;
-        uint32_t k = 0;
-        while (k < count && ok) {
-            const uint32_t run = min(count - k, (uint32_t)(nu - u));
-            const int64_t row_a = ((int64_t)rbp << 6) + lane;
-            const bool has_b = 2 * rbp + 1 < n_rb;
-            uint32_t prev_a, prev_b;
-            if (k == 0) {
-                prev_a = first_prev_a;
-                prev_b = first_prev_b;
-            } else {
-                const int32_t ug = useg0 + u;
-                if (ug == 0) {
-                    prev_a = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
-                    prev_b = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
-                } else {
-                    const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbp) * rb_stride +
-                                                                               ((int64_t)(ug - 1) << 5) + lane) + 3;
-                    prev_a = __ldg(last);
-                    prev_b = has_b ? __ldg(last + 4 * rb_stride) : 0u;
-                }
-            }
-            float facc_a[BATCH], facc_b[BATCH];
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
-            uint32_t xu = xs + (uint32_t)u * (WPU * 2u);
-#pragma unroll 1
-            for (uint32_t j = 0; j < run; ++j) {
-                ok = mbar_wait(bars + 8u * slot, phase, p.status);
-                if (!ok) break;
-                const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
-                const uint4 va = lds128(stage_base);
-                const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
-                uint32_t Ra[NW2], Rb[NW2];
-                {
-                    const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
-                    make_windows<K>(wa, prev_a, Ra);
-                    make_windows<K>(wb, prev_b, Rb);
-                }
-                prev_a = va.w;
-                prev_b = vb.w;
-                __half2 ha[BATCH][4], hb[BATCH][4];
-                uint4 xv[BATCH];
-#pragma unroll
-                for (int pi = 0; pi < PAIRS; ++pi) {
-                    if ((pi & 3) == 0) {
-#pragma unroll
-                        for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
-                    }
-                    const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
-                    const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) {
-                        const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                        const __half2 x2 = u32_as_half2(xq);
-                        ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
-                        hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
-                    }
-                }
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
-                    const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
-                    facc_a[b] += fa.x + fa.y;
-                    facc_b[b] += fb.x + fb.y;
-                }
-                xu += WPU * 2u;
-                __syncwarp();                     // every lane has taken its words: the slot can be refilled
-                if (to_issue) {
-                    if (lane == 0) issue_stage(slot);
-                    --to_issue;
-                }
-                if (++slot == kStages) {
-                    slot = 0;
-                    phase ^= 1u;
+        // ---- main loop: one granule per step ----
+        const uint32_t x_base = xs + (uint32_t)(g >> 2) * x_batch_stride;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator tiles: two shorter MMA chains
+        auto flush = [&](uint32_t rbp) {
+            if (out_batch < BATCH) {
+                const int64_t row_a = ((int64_t)rbp << 6) + out_row;
+                const bool has_b = 2 * rbp + 1 < n_rb;
+                float *dst = p.acc + (int64_t)out_batch * p.ld_acc + row_a;
+                atomicAdd(dst, c0[0] + c1[0]);
+                atomicAdd(dst + 1, c0[1] + c1[1]);
+                if (has_b) {
+                    atomicAdd(dst + 32, c0[2] + c1[2]);
+                    atomicAdd(dst + 33, c0[3] + c1[3]);
                 }
             }
 #pragma unroll
-            for (int b = 0; b < BATCH; ++b) {
-                atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
-                if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
-            }
-            k += run;
-            u += (int32_t)run;
-            if (u == nu) {
-                u = 0;
-                ++rbp;
-            }
-        }
-        if (!ok) {
-            // After a failed wait: give the copies still in flight a bounded chance to land before
-            // the shared memory they target is released, then stop.
-            for (int s = 0; s < kStages; ++s) {
-                mbar_wait(bars + 8u * slot, phase, p.status);
-                if (++slot == kStages) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-            }
-            break;
-        }
-    }
-    if (!waited_prior) pdl_wait_prior_grids();
-}
-
-// ---- the down projection of a gated MLP: activations made from the gate-up accumulator, block by block -----------
-// The pair kernel's granules in a different order: 256-column blocks outermost, then pairs of row blocks, then the
-// units of the block.  A CTA's granules then lie in one or two column blocks, so the CTA needs only those 256-column
-// pieces of x -- and makes them itself from the gate-up layer's fp32 accumulator (output transform of gate and up,
-// SiLU(gate) * up, this layer's input transform; one warp per block and row, no CTA barrier inside).  The separate
-// SwiGLU launch and the staging of the full activation row disappear.  Runs are as long as in the row-major order
-// (a warp holds ~4.6 granules of the 7B down projection either way).  The accumulator it reads is shared by several
-// CTAs and therefore zeroed by a later launch.
-template <int CODE, int K, int BATCH>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const GemvParams p) {
-    constexpr int WPU = 128 / K;
-    constexpr int PAIRS = WPU / 2;
-    constexpr int NW2 = 2 * GroupShape<K>::kWords;
-    constexpr uint32_t UPB = 256 / WPU;                       // units per 256-column block
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t s0 = smem_addr(smem_raw);
-    const uint32_t bars = s0 + (uint32_t)warp * kStages * 8u;
-    const uint32_t ring = s0 + kBarBytes + (uint32_t)warp * kStages * kStageBytes;
-    uint32_t lut_tab, xs;
-    if (CODE == RPTC_CODE_HASH) {
-        lut_tab = kHashLutWindow;
-        xs = kHashLutWindow + kHashLutBytes;
-    } else {
-        lut_tab = s0 + kBarBytes + kRingBytes;
-        xs = lut_tab + lut_bytes<CODE>(p.L, p.S);
-    }
-    if (CODE == RPTC_CODE_HASH && s0 + kBarBytes + kRingBytes > kHashLutWindow) {
-        if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemPlan);
-        return;
-    }
-    const LutPending lut_pending = lut_fill_begin<CODE>(lut_tab, p.lut, p.L, p.S);
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(bars + 8u * s, 1);
-        mbar_fence_init();
-    }
-    __syncwarp();
-    const Lut<CODE> lut = lut_view<CODE>(lut_tab, p.L, p.S);
-    pdl_allow_next_grid();
-
-    const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
-    const uint32_t GW = gridDim.x * kGemvWarps, gw = blockIdx.x * kGemvWarps + warp;
-    const uint32_t cell = n_rbp * UPB;                          // granules of one column block
-    const uint32_t T = n_rbp * (uint32_t)p.n_units;
-    const uint32_t per = T / GW, extra = T - per * GW;
-    auto first_of = [&](uint32_t w) { return w * per + min(w, extra); };
-    const uint32_t g0 = first_of(gw), count = per + (gw < extra ? 1u : 0u);
-    // column blocks of this CTA's warps together (its granules are consecutive)
-    const uint32_t cta_g0 = first_of(blockIdx.x * kGemvWarps), cta_g1 = first_of((blockIdx.x + 1) * kGemvWarps);
-    const uint32_t cb_first = cta_g0 / cell, cb_last = cta_g1 > cta_g0 ? (cta_g1 - 1) / cell : cb_first;
-    const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u;       // seg_units: the most units a CTA can need
-    const int64_t rb_stride = (int64_t)p.n_units << 5;
-    uint32_t slot = 0, phase = 0;
-    bool ok = true;
-
-    // this warp's first granule
-    const uint32_t cb0 = g0 / cell, rem0 = g0 - cb0 * cell, rbp0 = rem0 / UPB, u40 = rem0 - rbp0 * UPB;
-    uint32_t fcb = cb0, frbp = rbp0, fu4 = u40;                 // fetch cursor (lane 0)
-    const uint4 *fptr = p.codes + (int64_t)(2 * rbp0) * rb_stride + ((int64_t)(cb0 * UPB + u40) << 5);
-    auto issue_stage = [&](uint32_t at_slot) {
-        const bool has_b = 2 * frbp + 1 < n_rb;
-        const uint32_t bar = bars + 8u * at_slot, dst = ring + at_slot * kStageBytes;
-        mbar_expect_tx(bar, has_b ? 2 * kUnitBytes : kUnitBytes);
-        bulk_g2s(dst, fptr, kUnitBytes, bar);
-        if (has_b) bulk_g2s(dst + kUnitBytes, fptr + rb_stride, kUnitBytes, bar);
-        fptr += 32;
-        if (++fu4 == UPB) {
-            fu4 = 0;
-            if (++frbp == n_rbp) {
-                frbp = 0;
-                ++fcb;
-            }
-            fptr = p.codes + (int64_t)(2 * frbp) * rb_stride + ((int64_t)(fcb * UPB) << 5);
-        }
-    };
-    uint32_t to_issue = count;
-    {
-        const uint32_t ahead = min(count, (uint32_t)kStages);
-        if (lane == 0) {
-            uint32_t sl = slot;
-            for (uint32_t k = 0; k < ahead; ++k) {
-                issue_stage(sl);
-                if (++sl == kStages) sl = 0;
-            }
-        }
-        to_issue -= ahead;
-    }
-
-    // The 16 stream bits in front of a run's first unit are part of the weights: those of the first run are fetched here,
-    // before the wait, those of every later run while the run before it is being decoded.
-    auto load_history = [&](uint32_t cbx, uint32_t rbpx, uint32_t u4x, uint32_t &pa, uint32_t &pb) {
-        const int64_t row_a = ((int64_t)rbpx << 6) + lane;
-        const bool has_b = 2 * rbpx + 1 < n_rb;
-        const int32_t ug = (int32_t)(cbx * UPB + u4x);
-        if (ug == 0) {
-            pa = p.carry_in ? __ldg(p.carry_in + row_a) : 0u;
-            pb = (p.carry_in && has_b) ? __ldg(p.carry_in + row_a + 32) : 0u;
-        } else {
-            const uint32_t *last = reinterpret_cast<const uint32_t *>(p.codes + (int64_t)(2 * rbpx) * rb_stride + ((int64_t)(ug - 1) << 5) + lane) + 3;
-            pa = __ldg(last);
-            pb = has_b ? __ldg(last + 4 * rb_stride) : 0u;
-        }
-    };
-    uint32_t next_prev_a = 0u, next_prev_b = 0u;
-    if (count) load_history(cb0, rbp0, u40, next_prev_a, next_prev_b);
-
-    pdl_wait_prior_grids();
-    if (p.clear) {
-        float4 *z = reinterpret_cast<float4 *>(p.clear);
-        for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.clear_count; i += (int64_t)gridDim.x * kGemvThreads)
-            z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    // ---- activations of this CTA's column blocks: one warp per block and row ----
-    {
-        __half *x_sm = reinterpret_cast<__half *>(smem_raw + (xs - s0));
-        bool table_written = false;      // the table goes to shared memory while a warp's SwiGLU loads are in flight
-        for (uint32_t b = cb_first + warp; b <= cb_last; b += kGemvWarps)
-#pragma unroll 1
-            for (int r = 0; r < BATCH; ++r)
-                swiglu_chunk(p.sw, r, (int64_t)b * 256 + 8 * lane, nullptr, false,
-                             x_sm + (size_t)r * (x_batch_stride >> 1) + (size_t)(b - cb_first) * 256 + 8 * lane, [&]() {
-                                 if (!table_written) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
-                                 table_written = true;
-                             });
-        if (!table_written) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
-    }
-    __syncthreads();
-
-    // ---- main loop: runs of consecutive units inside one column block and pair of row blocks ----
-    uint32_t cb = cb0, rbp = rbp0, u4 = u40, k = 0;
-    while (k < count && ok) {
-        const uint32_t run = min(count - k, UPB - u4);
-        const int64_t row_a = ((int64_t)rbp << 6) + lane;
-        const bool has_b = 2 * rbp + 1 < n_rb;
-        uint32_t prev_a = next_prev_a, prev_b = next_prev_b;
-        // where the run after this one starts; its history words travel while this run is decoded
-        uint32_t cb_n = cb, rbp_n = rbp, u4_n = u4 + run;
-        if (u4_n == UPB) {
-            u4_n = 0;
-            if (++rbp_n == n_rbp) {
-                rbp_n = 0;
-                ++cb_n;
-            }
-        }
-        if (k + run < count) load_history(cb_n, rbp_n, u4_n, next_prev_a, next_prev_b);
-        float facc_a[BATCH], facc_b[BATCH];
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) facc_a[b] = facc_b[b] = 0.f;
-        uint32_t xu = xs + ((cb - cb_first) * UPB + u4) * (WPU * 2u);
-#pragma unroll 1
-        for (uint32_t j = 0; j < run; ++j) {
-            ok = mbar_wait(bars + 8u * slot, phase, p.status);
-            if (!ok) break;
-            const uint32_t stage_base = ring + slot * kStageBytes + 16u * lane;
-            const uint4 va = lds128(stage_base);
-            const uint4 vb = has_b ? lds128(stage_base + kUnitBytes) : make_uint4(0u, 0u, 0u, 0u);
+            for (int i = 0; i < 4; ++i) c0[i] = c1[i] = 0.f;
+        };
+        // One granule: windows, 16 (K = 2) lookups per row block, 8 MMAs; then the bookkeeping of run ends.
+        uint32_t slot = 0;
+        auto granule = [&](uint32_t k) {
+            cp_async_wait<kStages - 1>();      // all but the kStages - 1 youngest groups have landed: this granule is here
+            const uint32_t stage = ring + slot * kStageBytes + 16u * lane;
+            const uint4 va = lds128(stage), vb = lds128(stage + kUnitBytes);
             uint32_t Ra[NW2], Rb[NW2];
             {
                 const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
@@ -657,59 +503,43 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
             }
             prev_a = va.w;
             prev_b = vb.w;
-            __half2 ha[BATCH][4], hb[BATCH][4];
-            uint4 xv[BATCH];
+            fetch(slot);                       // the words are in registers: the slot takes the granule kStages ahead
+            if (++slot == kStages) slot = 0;
+            const uint32_t xu = x_base + (uint32_t)cc.u * (uint32_t)(WPU * 2);
+            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-            for (int pi = 0; pi < PAIRS; ++pi) {
-                if ((pi & 3) == 0) {
-#pragma unroll
-                    for (int b = 0; b < BATCH; ++b) xv[b] = lds128(xu + (uint32_t)b * x_batch_stride + 4u * pi);
+            for (int pi = 0; pi < PAIRS; pi += 4) {
+                // only the four (eight) lanes whose column of B is in use read activations; the others hold zeros
+                if (feeds_x) xv = lds128(xu + 4u * pi);
+                uint32_t wa[4], wb[4];
+                decode_quad_bits<CODE, K>(Ra, lut, pi, wa);
+                decode_quad_bits<CODE, K>(Rb, lut, pi, wb);
+                mma_16816(c0, wa[0], wb[0], wa[1], wb[1], xv.x, xv.y);
+                mma_16816(c1, wa[2], wb[2], wa[3], wb[3], xv.z, xv.w);
+            }
+            // the next granule: same rows one unit on, or (end of the row / of the column block) other rows
+            const uint32_t rbp_done = cc.rbp;
+            const int32_t u_done = cc.u;
+            advance(cc);
+            if (cc.rbp != rbp_done || cc.u != u_done + 1) {
+                flush(rbp_done);
+                prev_a = next_prev_a;
+                prev_b = next_prev_b;
+                if (k + 1 < count) {
+                    const uint32_t len = min(run_length(cc), left_after_run);
+                    left_after_run -= len;
+                    if (left_after_run) load_history(run_after(cc), next_prev_a, next_prev_b);
                 }
-                const __half2 wa2 = decode_pair<CODE, K>(Ra, lut, pi);
-                const __half2 wb2 = decode_pair<CODE, K>(Rb, lut, pi);
-#pragma unroll
-                for (int b = 0; b < BATCH; ++b) {
-                    const uint32_t xq = (pi & 3) == 0 ? xv[b].x : (pi & 3) == 1 ? xv[b].y : (pi & 3) == 2 ? xv[b].z : xv[b].w;
-                    const __half2 x2 = u32_as_half2(xq);
-                    ha[b][pi & 3] = pi < 4 ? __hmul2(wa2, x2) : __hfma2(wa2, x2, ha[b][pi & 3]);
-                    hb[b][pi & 3] = pi < 4 ? __hmul2(wb2, x2) : __hfma2(wb2, x2, hb[b][pi & 3]);
-                }
+            } else if (k + 1 == count) {
+                flush(rbp_done);
             }
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) {
-                const float2 fa = __half22float2(__hadd2(__hadd2(ha[b][0], ha[b][1]), __hadd2(ha[b][2], ha[b][3])));
-                const float2 fb = __half22float2(__hadd2(__hadd2(hb[b][0], hb[b][1]), __hadd2(hb[b][2], hb[b][3])));
-                facc_a[b] += fa.x + fa.y;
-                facc_b[b] += fb.x + fb.y;
-            }
-            xu += WPU * 2u;
-            __syncwarp();
-            if (to_issue) {
-                if (lane == 0) issue_stage(slot);
-                --to_issue;
-            }
-            if (++slot == kStages) {
-                slot = 0;
-                phase ^= 1u;
-            }
-        }
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-            atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a, facc_a[b]);
-            if (has_b) atomicAdd(p.acc + (int64_t)b * p.ld_acc + row_a + 32, facc_b[b]);
-        }
-        k += run;
-        cb = cb_n, rbp = rbp_n, u4 = u4_n;
+        };
+#pragma unroll 1
+        for (uint32_t k = 0; k < count; ++k) granule(k);
+        cp_async_wait<0>();                    // nothing of this segment's ring is in flight any more
+        if (MODE != 0) break;      // computed activations live in one segment
     }
-    if (!ok) {
-        for (int s = 0; s < kStages; ++s) {      // bounded chance for the copies in flight to land
-            mbar_wait(bars + 8u * slot, phase, p.status);
-            if (++slot == kStages) {
-                slot = 0;
-                phase ^= 1u;
-            }
-        }
-    }
+    if (!waited_prior) pdl_wait_prior_grids();
 }
 
 // ---- tensor-core form of the pair kernel ---------------------------------------------------------------
@@ -726,12 +556,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_colblock_kernel(const Ge
 // Per 64 weights a lane issues 4 word loads, 12 window instructions, 4 per pair for the lookup, 8 MMAs and 2
 // activation loads, a third less than the HFMA2 form, there is no fp16 partial sum, and BATCH up to 8 costs
 // only the shared memory for x.
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 template <int CODE, int K, int BATCH, int INPUT>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;
@@ -768,7 +592,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
     pdl_allow_next_grid();
 
     const uint32_t n_rb = (uint32_t)(p.m >> 5), n_rbp = (n_rb + 1) >> 1;
-    const uint32_t gw = blockIdx.x * kGemvWarps + warp, GW = gridDim.x * kGemvWarps;
     const uint32_t x_batch_stride = (uint32_t)p.seg_units * WPU * 2u + kXPad;
     const int64_t rb_stride = (int64_t)p.n_units << 5;        // 128-bit units between row blocks of the TILED layout
     const int halo_src = (lane & ~3) | ((t4 + 3) & 3);
@@ -777,10 +600,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
 
     for (int32_t useg0 = 0; useg0 < p.n_units; useg0 += p.seg_units) {
         const int32_t nu = min(p.seg_units, p.n_units - useg0);
+        // two-level even split: contiguous ranges per CTA, then per warp (see gemv_rows_kernel)
         const uint32_t T = n_rbp * (uint32_t)nu;
-        const uint32_t per = T / GW, extra = T - per * GW;
-        const uint32_t g0 = gw * per + min(gw, extra);
-        const uint32_t count = per + (gw < extra ? 1u : 0u);
+        const uint32_t cta_per = T / gridDim.x, cta_extra = T - cta_per * gridDim.x;
+        const uint32_t cta_g0 = blockIdx.x * cta_per + min((uint32_t)blockIdx.x, cta_extra);
+        const uint32_t cta_n = cta_per + (blockIdx.x < cta_extra ? 1u : 0u);
+        const uint32_t w_per = cta_n / kGemvWarps, w_extra = cta_n - w_per * kGemvWarps;
+        const uint32_t g0 = cta_g0 + (uint32_t)warp * w_per + min((uint32_t)warp, w_extra);
+        const uint32_t count = w_per + ((uint32_t)warp < w_extra ? 1u : 0u);
         const uint32_t rbp0 = count ? g0 / (uint32_t)nu : 0u;
         const int32_t u0 = count ? (int32_t)(g0 - rbp0 * (uint32_t)nu) : 0;
 
@@ -970,10 +797,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
                     for (int h = 0; h < 2; ++h) {
 #pragma unroll
                         for (int i = 0; i < PW / 2; ++i) {
-                            const uint32_t a0 = half2_as_u32(decode_pair<CODE, K>(R[2 * h], lut, 2 * i));
-                            const uint32_t a1 = half2_as_u32(decode_pair<CODE, K>(R[2 * h + 1], lut, 2 * i));
-                            const uint32_t a2 = half2_as_u32(decode_pair<CODE, K>(R[2 * h], lut, 2 * i + 1));
-                            const uint32_t a3 = half2_as_u32(decode_pair<CODE, K>(R[2 * h + 1], lut, 2 * i + 1));
+                            const uint32_t a0 = (decode_pair_bits<CODE, K>(R[2 * h], lut, 2 * i));
+                            const uint32_t a1 = (decode_pair_bits<CODE, K>(R[2 * h + 1], lut, 2 * i));
+                            const uint32_t a2 = (decode_pair_bits<CODE, K>(R[2 * h], lut, 2 * i + 1));
+                            const uint32_t a3 = (decode_pair_bits<CODE, K>(R[2 * h + 1], lut, 2 * i + 1));
                             mma_16816(blk == 0 ? ca[h] : cb[h], a0, a1, a2, a3, xr[2 * i], xr[2 * i + 1]);
                         }
                     }
@@ -1066,11 +893,10 @@ static int launch_gemv_mma(const GemvParams &p, size_t smem, cudaStream_t stream
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
-template <int CODE, int K, int BATCH, int INPUT = 0>
-static int launch_gemv_pair(const GemvParams &p, size_t smem, cudaStream_t stream) {
-    if (BATCH >= RPTC_GEMV_MMA_MIN_BATCH) return launch_gemv_mma<CODE, K, BATCH, INPUT>(p, smem, stream);
+template <int CODE, int K, int BATCH, int MODE>
+static int launch_gemv_rows(const GemvParams &p, size_t smem, cudaStream_t stream) {
     static SmemOptIn opted;
-    auto kern = gemv_pair_kernel<CODE, K, BATCH, INPUT>;
+    auto kern = gemv_rows_kernel<CODE, K, BATCH, MODE>;
     if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
@@ -1080,11 +906,11 @@ static int dispatch(const GemvParams &p, int batch, bool tiled, size_t smem, cud
     if (!tiled) return batch == 1 && !p.in.h_in ? launch_gemv<CODE, K>(p, smem, stream) : RPTC_ERR_UNSUPPORTED;
     if (p.in.h_in) {
         if (batch > 2) return RPTC_ERR_UNSUPPORTED;
-        return batch == 1 ? launch_gemv_pair<CODE, K, 1, 1>(p, smem, stream) : launch_gemv_pair<CODE, K, 2, 1>(p, smem, stream);
+        return batch == 1 ? launch_gemv_rows<CODE, K, 1, 1>(p, smem, stream) : launch_gemv_rows<CODE, K, 2, 1>(p, smem, stream);
     }
     switch (batch) {
-        case 1: return launch_gemv_pair<CODE, K, 1>(p, smem, stream);
-        case 2: return launch_gemv_pair<CODE, K, 2>(p, smem, stream);
+        case 1: return launch_gemv_rows<CODE, K, 1, 0>(p, smem, stream);
+        case 2: return launch_gemv_rows<CODE, K, 2, 0>(p, smem, stream);
         case 4: return launch_gemv_mma<CODE, K, 4>(p, smem, stream);
         case 8: return launch_gemv_mma<CODE, K, 8>(p, smem, stream);
     }
@@ -1271,14 +1097,6 @@ extern "C" int rptc_gemv_glued(const void *codes, const void *lut, const uint32_
                     static_cast<cudaStream_t>(stream), in);
 }
 
-template <int CODE, int K, int BATCH>
-static int launch_gemv_colblock(const GemvParams &p, size_t smem, cudaStream_t stream) {
-    static SmemOptIn opted;
-    auto kern = gemv_colblock_kernel<CODE, K, BATCH>;
-    if (int e = allow_max_smem(kern, opted)) return e;
-    return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
-}
-
 extern "C" int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32_t *carry_in, const float *prev_acc, int64_t ld_prev,
                                 const void *signs_out, float scale_out, const void *signs_in, int block, float *acc, int64_t ld_acc,
                                 int64_t m, int64_t n, int batch, const rptc_format *fmt, float *clear, int64_t clear_count,
@@ -1332,8 +1150,8 @@ extern "C" int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32
     p.clear_count = clear_count;
     // the most 256-column blocks one CTA's granules can touch
     const int64_t upb = 256 / wpu, n_rbp = (m / 32 + 1) / 2, cell = n_rbp * upb;
-    const int64_t T = n_rbp * p.n_units, GW = (int64_t)num_sms() * kGemvWarps;
-    const int64_t cta_granules = (T / GW + 1) * kGemvWarps;
+    const int64_t T = n_rbp * p.n_units;
+    const int64_t cta_granules = T / num_sms() + 1;
     int64_t max_blocks = (cta_granules + cell - 2) / cell + 1;
     if (max_blocks > n / 256) max_blocks = n / 256;
     p.seg_units = (int32_t)(max_blocks * upb);
@@ -1346,14 +1164,14 @@ extern "C" int rptc_gemv_swiglu(const void *codes, const void *lut, const uint32
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (fmt->code) {
         case RPTC_CODE_LUT:
-            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LUT, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LUT, 2, 2>(p, smem, s);
-            return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LUT, 4, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LUT, 4, 2>(p, smem, s);
+            if (K == 2) return batch == 1 ? launch_gemv_rows<RPTC_CODE_LUT, 2, 1, 2>(p, smem, s) : launch_gemv_rows<RPTC_CODE_LUT, 2, 2, 2>(p, smem, s);
+            return batch == 1 ? launch_gemv_rows<RPTC_CODE_LUT, 4, 1, 2>(p, smem, s) : launch_gemv_rows<RPTC_CODE_LUT, 4, 2, 2>(p, smem, s);
         case RPTC_CODE_HASH:
-            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_HASH, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_HASH, 2, 2>(p, smem, s);
+            if (K == 2) return batch == 1 ? launch_gemv_rows<RPTC_CODE_HASH, 2, 1, 2>(p, smem, s) : launch_gemv_rows<RPTC_CODE_HASH, 2, 2, 2>(p, smem, s);
             break;
         case RPTC_CODE_LITE:
-            if (K == 2) return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LITE, 2, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LITE, 2, 2>(p, smem, s);
-            return batch == 1 ? launch_gemv_colblock<RPTC_CODE_LITE, 4, 1>(p, smem, s) : launch_gemv_colblock<RPTC_CODE_LITE, 4, 2>(p, smem, s);
+            if (K == 2) return batch == 1 ? launch_gemv_rows<RPTC_CODE_LITE, 2, 1, 2>(p, smem, s) : launch_gemv_rows<RPTC_CODE_LITE, 2, 2, 2>(p, smem, s);
+            return batch == 1 ? launch_gemv_rows<RPTC_CODE_LITE, 4, 1, 2>(p, smem, s) : launch_gemv_rows<RPTC_CODE_LITE, 4, 2, 2>(p, smem, s);
     }
     return RPTC_ERR_UNSUPPORTED;
 }

@@ -92,7 +92,7 @@ struct QkvFinishParams {
     __half *kcache, *vcache;     // [rows][max_pos][hkv][128]
     const int32_t *pos;
     int32_t hq, hkv, max_pos, block, chunk;
-    float theta;
+    RopeFreq freq;
     unsigned int *status;
 };
 
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p
             const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
             const int j = (idx & 63) + i;                       // frequency index
             float sn, cs;
-            sincosf(ps * powf(p.theta, -2.f * j / 128.f), &sn, &cs);
+            sincosf(ps * rope_inv_freq(p.freq, j), &sn, &cs);
             o[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
         }
         if (head < p.hq) store8_f16(p.q_out + row * p.ld_q + col, o);
@@ -296,7 +296,7 @@ extern "C" int rptc_qkv_finish(float *acc, int64_t ld_acc, const void *signs_out
     p.max_pos = max_pos;
     p.block = block;
     p.chunk = chunk;
-    p.theta = theta;
+    p.freq = rope_freq(theta, 128);
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
     return launch(qkv_finish_kernel, dim3((unsigned)(n / chunk), (unsigned)rows), dim3(chunk / 8), 0, static_cast<cudaStream_t>(stream), p);

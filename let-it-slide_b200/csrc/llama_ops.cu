@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__
 // at positions pos[row].  Caches: [rows][max_pos][hkv][d].  One CTA per (row, head of q|k|v).
 __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv, int64_t ld_qkv, const int32_t *__restrict__ pos,
                                                         __half *__restrict__ kcache, __half *__restrict__ vcache, int hq, int hkv,
-                                                        int d, int max_pos, float theta, unsigned int *__restrict__ status) {
+                                                        int d, int max_pos, RopeFreq freq, unsigned int *__restrict__ status) {
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     const int row = blockIdx.y, head = blockIdx.x, t = threadIdx.x;      // t < d/2
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
     if (head < hq + hkv) {
         float lo = 0.f, hi = 0.f;
         if (t < d / 2) {
-            const float inv_freq = powf(theta, -2.f * t / d);
+            const float inv_freq = rope_inv_freq(freq, t);
             float sn, cs;
             sincosf(p * inv_freq, &sn, &cs);
             const float a = __half2float(src[t]), b = __half2float(src[t + d / 2]);
@@ -95,12 +95,12 @@ __global__ void __launch_bounds__(64) rope_cache_kernel(__half *__restrict__ qkv
 // position are computed once per pair index instead of once per head.  Token t of row r sits in row r * T + t of qkv.
 __global__ void __launch_bounds__(256) rope_cache_prompt_kernel(__half *__restrict__ qkv, int64_t ld_qkv, __half *__restrict__ kcache,
                                                                __half *__restrict__ vcache, int hq, int hkv, int d, int max_pos,
-                                                               float theta) {
+                                                               RopeFreq freq) {
     const int p = blockIdx.x, row = blockIdx.y, T = gridDim.x;
     const int half_d = d / 2, i = threadIdx.x % 64, grp = threadIdx.x / 64;      // pair index, head group (4 groups)
     if (i >= half_d) return;
     float sn, cs;
-    sincosf(p * powf(theta, -2.f * i / d), &sn, &cs);
+    sincosf(p * rope_inv_freq(freq, i), &sn, &cs);
     __half *tok = qkv + ((int64_t)row * T + p) * ld_qkv;
     for (int head = grp; head < hq + 2 * hkv; head += 4) {
         __half *src = tok + (int64_t)head * d;
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                                                                   int64_t ld_out, int hq, int hkv, int max_pos, float scale,
                                                                   const __half *__restrict__ signs_in, float *__restrict__ acc,
                                                                   int64_t ld_acc, const __half *__restrict__ signs_out,
-                                                                  float scale_out, float theta, __half *__restrict__ kcache_w,
+                                                                  float scale_out, RopeFreq freq, __half *__restrict__ kcache_w,
                                                                   __half *__restrict__ vcache_w, unsigned int *__restrict__ status) {
     __shared__ float part[kAttnWarps][128];
     __shared__ float pm[kAttnWarps], pl[kAttnWarps];
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         const int grp0 = t >> 4;
         if (signs_out && grp0 < 3) so_raw = *reinterpret_cast<const uint4 *>(signs_out + (grp0 == 0 ? head : grp0 == 1 ? hq + kvh : hq + hkv + kvh) * D + i8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * powf(theta, -2.f * ((i8 & 63) + i) / 128.f), &rot_sn[i], &rot_cs[i]);
+        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * rope_inv_freq(freq, (i8 & 63) + i), &rot_sn[i], &rot_cs[i]);
     }
     if (fused) {
         // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv
@@ -472,7 +472,7 @@ extern "C" int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, vo
     if (!status) return RPTC_ERR_CUDA;
     return launch(rope_cache_kernel, dim3((unsigned)(hq + 2 * hkv), (unsigned)rows), dim3(64), 0, static_cast<cudaStream_t>(stream),
                   static_cast<__half *>(qkv), ld_qkv, pos, static_cast<__half *>(kcache), static_cast<__half *>(vcache), hq, hkv, d,
-                  max_pos, theta, status);
+                  max_pos, rope_freq(theta, d), status);
 }
 
 extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
@@ -488,7 +488,7 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
     return launch(attn_decode_kernel, dim3((unsigned)hq, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(qkv), ld_qkv, pos, static_cast<const __half *>(kcache), static_cast<const __half *>(vcache),
                   static_cast<__half *>(out), ld_out, hq, hkv, max_pos, scale, static_cast<const __half *>(signs_in),
-                  static_cast<float *>(nullptr), (int64_t)0, static_cast<const __half *>(nullptr), 0.f, 0.f,
+                  static_cast<float *>(nullptr), (int64_t)0, static_cast<const __half *>(nullptr), 0.f, RopeFreq{0.f, 0.f},
                   static_cast<__half *>(nullptr), static_cast<__half *>(nullptr), status);
 }
 
@@ -508,7 +508,7 @@ extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *sign
     return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(nullptr), (int64_t)0, pos, static_cast<const __half *>(kcache),
                   static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, heads, max_pos, 0.08838834764831845f,
-                  static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, theta,
+                  static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, rope_freq(theta, 128),
                   static_cast<__half *>(kcache), static_cast<__half *>(vcache), status);
 }
 
@@ -587,5 +587,5 @@ extern "C" int rptc_rope_cache_prompt(void *qkv, int64_t ld_qkv, int64_t rows, i
     if (int e = rptc_check_device()) return e;
     return launch(rope_cache_prompt_kernel, dim3((unsigned)tokens, (unsigned)rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
                   static_cast<__half *>(qkv), ld_qkv, static_cast<__half *>(kcache), static_cast<__half *>(vcache), hq, hkv, d, max_pos,
-                  theta);
+                  rope_freq(theta, d));
 }
