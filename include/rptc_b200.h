@@ -285,11 +285,13 @@ int rptc_peer_export(void *ptr, unsigned char *handle64);
 int rptc_peer_import(const unsigned char *handle64, void **ptr);
 int rptc_peer_close(void *ptr);
 /* h[rows][n] += sum over ranks of fp16( s_out * H(acc_rank) * scale );  acc is cleared.
- * data_ptrs[r]: rank r's exchange buffer, fp16 [2][world][rows*n];  flag_ptrs[r]: rank r's flags, uint32
- * [world][ctas] with ctas = rows * n / max(block,256);  epochs: local uint32 [ctas]; all zero-initialised.
+ * data_ptrs[r]: rank r's exchange buffer, 2 * world * rows * n * 4 bytes, zero-initialised: [2][world][rows*n/2] 64-bit
+ * words, each a 32-bit piece of payload with the exchange's epoch above it (the flag travels with the data; a 64-bit
+ * store arrives whole, so the receiver only polls its own buffer).  flag_ptrs: unused, may be NULL.  epochs: local
+ * uint32 [ctas], ctas = rows * n / max(block,256), zero-initialised.
  * Every rank must call it the same number of times with the same shapes.  A rank that waits longer than
  * timeout_ms (0 = 2000) for a peer gives up: the device status word is raised (rptc_device_status) and h is
- * left untouched for the rows it could not finish. */
+ * left untouched for the pieces it could not finish. */
 int rptc_peer_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *h, int64_t ld_h,
                      void *const *data_ptrs, void *const *flag_ptrs, void *epochs, int rank, int world, int64_t rows,
                      int64_t n, int block, int64_t timeout_ms, rptc_stream_t stream);

@@ -1,13 +1,14 @@
 // Output side of a row-parallel (tensor-parallel) quantised layer fused with its all-reduce and the
 // residual add, as ONE kernel over NVLink peer memory:
 //     h += sum over ranks r of ( s_out * H(acc_r) * scale )
-// Every rank transforms its fp32 partial accumulator, stores the fp16 result straight into a slot of
-// EVERY rank's exchange buffer with plain peer stores (no multimem, no NCCL), raises a per-CTA epoch
-// flag on each peer, waits -- with a time limit -- until all ranks' flags show the same epoch, and adds
-// the partials from its own buffer in rank order (so all ranks compute bit-identical sums) onto the
-// residual stream.  Decode messages are tiny (16 KiB at hidden 8192), so the cost is one NVLink round
-// trip instead of a collective launch.  Buffers are double-buffered by epoch parity; epochs are kept in
-// device memory per CTA, which makes the kernel replayable from a CUDA graph.
+// Every rank transforms its fp32 partial accumulator and stores the fp16 result straight into a slot of EVERY rank's
+// exchange buffer with plain peer stores (no multimem, no NCCL).  The flag travels WITH the data: each 32-bit word of
+// payload is stored together with the 32-bit epoch as one 64-bit store, which arrives whole or not at all, so the
+// receiver simply polls its own buffer until every word it needs carries the current epoch -- no fence, no second
+// round trip for a separate flag.  Decode messages are tiny (16 KiB at hidden 8192, 32 KiB in this form), so the cost
+// is one NVLink one-way trip instead of a collective launch.  The partials are added in rank order (all ranks compute
+// bit-identical sums) onto the residual stream.  Buffers alternate by epoch parity (a rank can be at most one exchange
+// ahead of its peers); epochs are kept in device memory per CTA, which makes the kernel replayable from a CUDA graph.
 // A wait that runs out raises the device status word and the kernel returns; nothing hangs.
 #include "common.cuh"
 #include "fwht.cuh"
@@ -23,8 +24,7 @@ struct PeerFinishParams {
     float scale;
     __half *h;                    // fp16 [rows][ld_h] residual stream, updated in place
     int64_t ld_h;
-    __half *data[kMaxPeers];      // every rank's exchange buffer: [2 parities][world][rows * n] fp16
-    uint32_t *flags[kMaxPeers];   // every rank's flag array: [world][n_ctas]
+    uint64_t *data[kMaxPeers];    // every rank's exchange buffer: [2 parities][world][rows * n / 2] x (payload word, epoch)
     uint32_t *epochs;             // local: [n_ctas]
     int32_t rank, world, n, block, chunk, rows;
     unsigned long long timeout_ns;
@@ -36,18 +36,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// Two (payload, epoch) words to a peer; each 64-bit half is single-copy atomic.
+__device__ __forceinline__ void st_pair_sys(uint64_t *p, uint64_t a, uint64_t b) {
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint4 ld_volatile_128(const void *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ void ld_pair_sys(const uint64_t *p, uint64_t &a, uint64_t &b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 
 __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams p) {
@@ -55,10 +49,10 @@ __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams
     __shared__ int timed_out;
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
-    const int t = threadIdx.x;
+    const int t = threadIdx.x, T = blockDim.x;
     const int64_t row = blockIdx.y;
     const int col = blockIdx.x * p.chunk + 8 * t;
-    const int cta = blockIdx.y * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
     if (t == 0) timed_out = 0;
     // ---- this rank's partial: s_out * H(acc) * scale, rounded to fp16 ----
     float v[8];
@@ -72,69 +66,81 @@ __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams
     uint4 sraw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
     if (p.signs_out) sraw = *reinterpret_cast<const uint4 *>(p.signs_out + col);
     const uint4 hraw = *reinterpret_cast<const uint4 *>(p.h + row * p.ld_h + col);
+    const uint32_t epoch = p.epochs[cta] + 1u;
     fwht8(v, p.block, ex);
     const float sc = p.scale * rsqrtf((float)p.block);
-    uint4 mine;
+    uint32_t mine[4];
     {
         const uint32_t sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
-        uint32_t o[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 s2 = __half22float2(u32_as_half2(sw[i]));
-            o[i] = half2_as_u32(__floats2half2_rn(v[2 * i] * sc * s2.x, v[2 * i + 1] * sc * s2.y));
+            mine[i] = half2_as_u32(__floats2half2_rn(v[2 * i] * sc * s2.x, v[2 * i + 1] * sc * s2.y));
         }
-        mine = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    // ---- publish to every rank (peer stores), then raise this CTA's flag on every rank ----
-    const uint32_t epoch = p.epochs[cta] + 1u;
-    const int64_t slot_elems = (int64_t)p.rows * p.n;
-    const int64_t off = ((int64_t)(epoch & 1u) * p.world + p.rank) * slot_elems + row * p.n + col;
-    for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4 *>(p.data[r] + off) = mine;
-    __threadfence_system();
-    __syncthreads();
-    if (t < p.world) {
-        st_release_sys(p.flags[t] + (int64_t)p.rank * n_ctas + cta, epoch);
-        // ---- wait (bounded) for rank t's flag in this rank's own array ----
-        const uint32_t *f = p.flags[p.rank] + (int64_t)t * n_ctas + cta;
-        const unsigned long long t0 = global_ns();
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-            if (global_ns() - t0 > p.timeout_ns) {
-                timed_out = 1;
-                atomicExch(p.status, kStatusWaitExpired);
-                break;
+    // ---- publish to every other rank: thread t's four words as two 16-byte stores, [j][t] inside the CTA's piece so
+    // that a warp's stores are contiguous ----
+    const int64_t slot = (int64_t)p.rows * p.n / 2;                                   // 64-bit words per (parity, source rank)
+    const int64_t piece = (row * p.n + (int64_t)blockIdx.x * p.chunk) / 2;            // this CTA's first word inside a slot
+    const int64_t mine_at = ((int64_t)(epoch & 1u) * p.world + p.rank) * slot + piece;
+    const uint64_t tag = (uint64_t)epoch << 32;
+    for (int r = 0; r < p.world; ++r) {
+        if (r == p.rank) continue;
+        uint64_t *dst = p.data[r] + mine_at;
+        st_pair_sys(dst + 2 * t, tag | mine[0], tag | mine[1]);
+        st_pair_sys(dst + 2 * (T + t), tag | mine[2], tag | mine[3]);
+    }
+    // ---- collect: poll this rank's own buffer until every word carries this epoch (bounded), summing in rank order ----
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bool ok = true;
+    const unsigned long long t0 = global_ns();
+    for (int r = 0; r < p.world; ++r) {
+        uint32_t q[4];
+        if (r == p.rank) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[i] = mine[i];
+        } else if (ok) {
+            const uint64_t *src = p.data[p.rank] + ((int64_t)(epoch & 1u) * p.world + r) * slot + piece;
+            uint64_t w0, w1, w2, w3;
+            uint32_t spins = 0;
+            for (;;) {
+                ld_pair_sys(src + 2 * t, w0, w1);
+                ld_pair_sys(src + 2 * (T + t), w2, w3);
+                if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch &&
+                    (uint32_t)(w3 >> 32) == epoch)
+                    break;
+                if ((++spins & 63u) == 0 && global_ns() - t0 > p.timeout_ns) {
+                    ok = false;
+                    break;
+                }
             }
+            q[0] = (uint32_t)w0, q[1] = (uint32_t)w1, q[2] = (uint32_t)w2, q[3] = (uint32_t)w3;
         }
+        if (!ok) break;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f2 = __half22float2(u32_as_half2(q[i]));
+            sum[2 * i] += f2.x, sum[2 * i + 1] += f2.y;
+        }
+    }
+    if (!ok) {
+        timed_out = 1;
+        atomicExch(p.status, kStatusWaitExpired);
     }
     __syncthreads();
     if (t == 0) p.epochs[cta] = epoch;
-    if (timed_out) return;
-    // ---- sum the partials in rank order, add the residual ----
-    float acc[8];
+    if (timed_out) return;      // the whole CTA leaves h untouched for the piece it could not finish
+    // ---- add the residual ----
+    uint32_t o[4];
     {
         const uint32_t hw[4] = {hraw.x, hraw.y, hraw.z, hraw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float2 f2 = __half22float2(u32_as_half2(hw[i]));
-            acc[2 * i] = f2.x, acc[2 * i + 1] = f2.y;
+            // the reduced layer output is an fp16 tensor; add it to the residual as the unfused path does
+            const float2 res = __half22float2(u32_as_half2(hw[i]));
+            const float2 red = __half22float2(__floats2half2_rn(sum[2 * i], sum[2 * i + 1]));
+            o[i] = half2_as_u32(__floats2half2_rn(res.x + red.x, res.y + red.y));
         }
-    }
-    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const __half *mybuf = p.data[p.rank] + ((int64_t)(epoch & 1u) * p.world) * slot_elems + row * p.n + col;
-    for (int r = 0; r < p.world; ++r) {
-        const uint4 q = ld_volatile_128(mybuf + (int64_t)r * slot_elems);
-        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f2 = __half22float2(u32_as_half2(qw[i]));
-            sum[2 * i] += f2.x, sum[2 * i + 1] += f2.y;
-        }
-    }
-    uint32_t o[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        // the reduced layer output is an fp16 tensor; add it to the residual as the unfused path does
-        const float2 red = __half22float2(__floats2half2_rn(sum[2 * i], sum[2 * i + 1]));
-        o[i] = half2_as_u32(__floats2half2_rn(acc[2 * i] + red.x, acc[2 * i + 1] + red.y));
     }
     *reinterpret_cast<uint4 *>(p.h + row * p.ld_h + col) = make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -177,7 +183,7 @@ extern "C" int rptc_peer_close(void *ptr) {
 extern "C" int rptc_peer_finish(float *acc, int64_t ld_acc, const void *signs_out, float scale, void *h, int64_t ld_h,
                                 void *const *data_ptrs, void *const *flag_ptrs, void *epochs, int rank, int world, int64_t rows,
                                 int64_t n, int block, int64_t timeout_ms, rptc_stream_t stream) {
-    if (!acc || !h || !data_ptrs || !flag_ptrs || !epochs) return RPTC_ERR_ARG;
+    if (!acc || !h || !data_ptrs || !epochs) return RPTC_ERR_ARG;
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return RPTC_ERR_ARG;
     if (block < 8 || block > 4096 || (block & (block - 1))) return RPTC_ERR_ARG;
     const int chunk = block < 256 ? 256 : block;
@@ -194,10 +200,10 @@ extern "C" int rptc_peer_finish(float *acc, int64_t ld_acc, const void *signs_ou
     p.h = static_cast<__half *>(h);
     p.ld_h = ld_h;
     for (int r = 0; r < kMaxPeers; ++r) {
-        p.data[r] = r < world ? static_cast<__half *>(data_ptrs[r]) : nullptr;
-        p.flags[r] = r < world ? static_cast<uint32_t *>(flag_ptrs[r]) : nullptr;
-        if (r < world && (!p.data[r] || !p.flags[r])) return RPTC_ERR_ARG;
+        p.data[r] = r < world ? static_cast<uint64_t *>(data_ptrs[r]) : nullptr;
+        if (r < world && !p.data[r]) return RPTC_ERR_ARG;
     }
+    (void)flag_ptrs;      // the flags travel inside the data words
     p.epochs = static_cast<uint32_t *>(epochs);
     p.rank = rank;
     p.world = world;

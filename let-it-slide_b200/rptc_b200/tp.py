@@ -65,7 +65,7 @@ class PeerAllReduce:
     """Exchange buffers for `rptc_peer_finish`: the output transform of a row-parallel layer, the all-reduce
     over the tensor-parallel ranks and the residual add as one kernel over NVLink peer memory.
 
-    Each rank allocates a data buffer [2][world][rows*n] fp16 and a flag array, exports their CUDA IPC handles
+    Each rank allocates a data buffer of [2][world][rows*n/2] 64-bit (payload, epoch) words, exports its CUDA IPC handle
     through `group` (any torch.distributed backend) and maps its peers' buffers.  One object serves every
     row-parallel layer of a model whose output width is `n` (they run one after another on one stream)."""
 
@@ -84,7 +84,7 @@ class PeerAllReduce:
             self._own.append(p.value)
             return p.value
 
-        data = alloc(2 * world * rows * n * 2)
+        data = alloc(2 * world * rows * n * 4)      # (payload word, epoch) pairs: twice the fp16 payload
         flags = alloc(world * self.n_ctas * 4)
         self.epochs = torch.zeros(self.n_ctas, dtype=torch.int32, device="cuda")
         handles = []

@@ -36,12 +36,11 @@ def test_wait_for_an_absent_peer_runs_out():
     lin = RPTCLinear.random(2048, 1024, seed=3)
     # "world" of two whose second rank is a pair of buffers nobody ever writes
     peer = PeerAllReduce(1, 1024, lin.block_out, 0, 1, timeout_ms=50)
-    ghost_data = torch.zeros(2 * 2 * 1024, dtype=torch.float16, device="cuda")
-    ghost_flags = torch.zeros(2 * peer.n_ctas, dtype=torch.int32, device="cuda")
-    own_data = torch.zeros(2 * 2 * 1024, dtype=torch.float16, device="cuda")
-    own_flags = torch.zeros(2 * peer.n_ctas, dtype=torch.int32, device="cuda")
+    # exchange buffers of [2 parities][2 ranks][1024 / 2] 64-bit (payload, epoch) words
+    ghost_data = torch.zeros(2 * 2 * 512, dtype=torch.int64, device="cuda")
+    own_data = torch.zeros(2 * 2 * 512, dtype=torch.int64, device="cuda")
     data = (ctypes.c_void_p * 2)(own_data.data_ptr(), ghost_data.data_ptr())
-    flags = (ctypes.c_void_p * 2)(own_flags.data_ptr(), ghost_flags.data_ptr())
+    flags = None                                         # the flags travel inside the data words
     acc = torch.ones((1, 1024), device="cuda")
     h = torch.zeros((1, 1024), dtype=torch.float16, device="cuda")
     st = lib().rptc_peer_finish(acc.data_ptr(), 1024, lin.signs_out.data_ptr(), 1.0, h.data_ptr(), 1024, data, flags,
