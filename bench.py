@@ -416,22 +416,22 @@ def run_kernels(args) -> None:
 # ------------------------------------------------------------------------------------------------
 # GPU arm: the decode workloads
 # ------------------------------------------------------------------------------------------------
-def decode_leg(args, torch, dist, cfg_kw, tp: bool, allreduce: str, world: int, rank: int, sampler, prompt_len: int):
+def decode_leg(args, torch, dist, cfg_kw, tp: bool, allreduce: str, world: int, rank: int, sampler, prompt_len: int, rows: int = 1):
     """Builds the model, pushes the prompt through the decode step, then times `steps` tokens twice: token feedback on the
     device (CUDA events) and host in the loop every step (wall clock).  Returns (model, device ms, e2e ms, h2d, d2h)."""
     from rptc_b200 import ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
     cfg = LlamaConfig(max_pos=prompt_len + max(3, args.warmup) + 2 * args.steps + 8, **cfg_kw)
     if tp:
-        model = RPTCLlama(cfg, rows=1, seed=0, tp_world=world, tp_rank=rank, peer_allreduce=allreduce == "peer")
+        model = RPTCLlama(cfg, rows=rows, seed=0, tp_world=world, tp_rank=rank, peer_allreduce=allreduce == "peer")
     else:
-        model = RPTCLlama(cfg, rows=1, seed=rank)
+        model = RPTCLlama(cfg, rows=rows, seed=rank)
     g = torch.Generator(device="cuda").manual_seed(42 + (0 if tp else rank))
-    prompt = torch.randint(0, cfg.vocab, (prompt_len,), device="cuda", generator=g, dtype=torch.int32)
+    prompt = torch.randint(0, cfg.vocab, (prompt_len, rows), device="cuda", generator=g, dtype=torch.int32)
     model.reset()
     model.capture(pdl=True)
     for t in range(prompt_len):                            # the prompt goes through the decode step, token by token
-        model.ids.copy_(prompt[t:t + 1])
+        model.ids.copy_(prompt[t])
         model.step()
     for _ in range(max(3, args.warmup)):
         model.step()
@@ -461,35 +461,35 @@ def decode_leg(args, torch, dist, cfg_kw, tp: bool, allreduce: str, world: int, 
     # in pinned memory (8 bytes, read over PCIe by the step's first kernel) and polls the id the step's last kernel
     # writes back (8 bytes), keeping one graph launch queued ahead.  Tensor parallel: the step's first kernel reads a
     # pinned int32, the last writes a pinned int64, and the host synchronises the stream every step.
-    first = int(model.ids.item())
+    first = model.ids.tolist()
     torch.cuda.synchronize()
     model.pos.copy_(pos_timed - 3)         # three untimed steps, then the positions of the device-resident leg
     model.sync_positions()
     if not tp:
         loop = model.host_loop()
-        first = loop.run([first], 3)[-1][0]
-        h2d, d2h = 8, 8
+        first = loop.run(first, 3)[-1]
+        h2d, d2h = 8 * rows, 8 * rows
         barrier()
         t0 = time.perf_counter()
-        loop.run([first], args.steps)
+        loop.run(first, args.steps)
         torch.cuda.synchronize()
     else:
-        host_in = torch.zeros(1, dtype=torch.int32).pin_memory()
-        host_out = torch.zeros(1, dtype=torch.int64).pin_memory()
-        host_in[0] = first
+        host_in = torch.zeros(rows, dtype=torch.int32).pin_memory()
+        host_out = torch.zeros(rows, dtype=torch.int64).pin_memory()
+        host_in.copy_(torch.tensor(first, dtype=torch.int32))
         model.bind_host_io(host_in, host_out)
         model.capture(pdl=True)
-        h2d, d2h = 4, 8
+        h2d, d2h = 4 * rows, 8 * rows
         for _ in range(3):
             model.step()
             torch.cuda.current_stream().synchronize()
-            host_in[0] = int(host_out[0])
+            host_in.copy_(host_out.to(torch.int32))
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             model.step()
             torch.cuda.current_stream().synchronize()
-            host_in[0] = int(host_out[0])
+            host_in.copy_(host_out.to(torch.int32))
     t1 = time.perf_counter()
     sampler.window(t0, t1)
     barrier()
@@ -536,18 +536,19 @@ def close_model(torch, dist, model, world: int) -> None:
         dist.barrier()
 
 
-def tp_record(args, torch, dist, world, rank, sampler, allreduce: str) -> dict | None:
-    """The partitioned shape on all ranks: Llama-2-70B, column/row splits, one all-reduce after o and down."""
+def tp_record(args, torch, dist, world, rank, sampler, allreduce: str, rows: int = 1) -> dict | None:
+    """The partitioned shape on all ranks: Llama-2-70B, column/row splits, one all-reduce after o and down; `rows`
+    sequences decode together (batch 1 and 16)."""
     cfg_kw, _ = WORKLOADS["llama2-70b-tp"]
-    model, ms, e2e_ms, h2d, d2h = decode_leg(args, torch, dist, cfg_kw, True, allreduce, world, rank, sampler, min(args.prompt, 32))
+    model, ms, e2e_ms, h2d, d2h = decode_leg(args, torch, dist, cfg_kw, True, allreduce, world, rank, sampler, min(args.prompt, 32), rows)
     ar_us = allreduce_us(torch, dist, model, world) if world > 1 else None
     bt = model.bytes_per_token(min(args.prompt, 32) + args.warmup + args.steps // 2)
     step_s = ms / args.steps * 1e-3
     peaks = measured_peaks()
-    rec = {"workload": "llama2-70b-tp", "tok_s": args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps, "allreduce": allreduce,
-           "parallelism": f"tp{world}", "launches_per_step": model.launches_per_step, "us_per_allreduce": ar_us,
+    rec = {"workload": "llama2-70b-tp", "batch": rows, "tok_s": rows * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+           "allreduce": allreduce, "parallelism": f"tp{world}", "launches_per_step": model.launches_per_step, "us_per_allreduce": ar_us,
            "allreduces_per_step": 2 * len(model.blocks), "packed_gb_per_gpu": bt["packed"] / 1e9,
-           "e2e_tok_s": args.steps / (e2e_ms * 1e-3), "scaling": "strong",
+           "e2e_tok_s": rows * args.steps / (e2e_ms * 1e-3), "scaling": "strong",
            "roofline": {"bound": "hbm", "achieved": bt["packed"] / step_s / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": bt["packed"] / step_s / 1e9 / peaks["hbm_gbs"], "what": "packed codes per GPU per token / step time"}}
     close_model(torch, dist, model, world)
@@ -614,12 +615,22 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
                                       "frac_min": worst["frac"], "frac_max": best["frac"], "bytes": "m*n*K/8 + 2^L*2 + 2*m*n",
                                       "peak_source": f"{peaks['source']} copy bandwidth", "cases": dec}
         ops.device_status()
+        # decode batch 16 of the same 7B shape (sixteen sequences step together)
+        m16, ms16, e2e16, _, _ = decode_leg(args, torch, dist, cfg_kw, False, args.allreduce, 1, 0, sampler, min(args.prompt, 32), rows=16)
+        out["decode_bs16"] = {"tok_s": 16 * args.steps / (ms16 * 1e-3), "ms_per_step": ms16 / args.steps,
+                              "e2e_tok_s": 16 * args.steps / (e2e16 * 1e-3), "launches_per_step": m16.launches_per_step}
+        close_model(torch, dist, m16, 1)
+        del m16
+        torch.cuda.empty_cache()
 
     if world > 1 and not tp and args.extras:
         # ---- the partitioned shape on the same ranks ----
         rec = tp_record(args, torch, dist, world, rank, sampler, "peer")
         if rank == 0:
             out["tp"] = rec
+        rec = tp_record(args, torch, dist, world, rank, sampler, "peer", rows=16)
+        if rank == 0:
+            out["tp_bs16"] = rec
         if args.tp_nccl:
             rec = tp_record(args, torch, dist, world, rank, sampler, "nccl")
             if rank == 0:

@@ -109,7 +109,8 @@ int rptc_repack(const void *src, int src_layout, void *dst, int dst_layout, int6
 int rptc_decompress(const void *codes, const void *lut, const uint32_t *carry_in, void *out, int64_t ld_out,
                     int64_t m, int64_t n, const rptc_format *fmt, rptc_stream_t stream);
 
-/* Fused decode + matvec, batch 1..8:  acc[b][row] += sum_c W[row][c] * x[b][c]   (fp32 acc).
+/* Fused decode + matvec, batch 1..64:  acc[b][row] += sum_c W[row][c] * x[b][c]   (fp32 acc).  One launch serves up to
+ * eight activation rows; larger batches (decode batch 16) run as consecutive launches of eight.
  * Replaces the kernels behind decompress_matvec_{16,20}_{6,8}_1 (inference.cu:189-277) and
  * decompress_matvec_t_{16,14} (inference_t.cu:68-175).  `acc` is fp32 SCRATCH of [batch][ld_acc]
  * that the caller zeroes (or pre-loads) and later converts with rptc_gemv_finish; partial sums

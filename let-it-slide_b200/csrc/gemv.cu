@@ -987,13 +987,15 @@ int check_format(const rptc_format *f);   // api.cu
 
 using namespace rptc;
 
+constexpr int kMaxGemvBatch = 64;      // rows of activations per call; more than eight run as a sequence of launches
+
 // Every check of rptc_gemv's arguments that needs no device work, in the order the entry point reports them.
 static int validate_gemv_args(const void *codes, const void *lut, const void *x, int64_t ld_x, const float *acc, int64_t ld_acc,
                               int64_t m, int64_t n, int batch, int x_order, const rptc_format *fmt) {
     if (!codes || !lut || !x || !acc || !fmt) return RPTC_ERR_ARG;
     if (int e = rptc::check_format(fmt)) return e;
     if (fmt->K != 2 && fmt->K != 4) return RPTC_ERR_UNSUPPORTED;
-    if (batch < 1 || batch > 8) return RPTC_ERR_ARG;
+    if (batch < 1 || batch > kMaxGemvBatch) return RPTC_ERR_ARG;
     if (x_order != RPTC_XORDER_NATURAL && x_order != RPTC_XORDER_K2_LEGACY) return RPTC_ERR_ARG;
     if (m <= 0 || n <= 0 || (m % 32) || (n % (128 / fmt->K))) return RPTC_ERR_SHAPE;
     if (x_order == RPTC_XORDER_K2_LEGACY && (n % 2048 || fmt->K != 2)) return RPTC_ERR_SHAPE;
@@ -1012,7 +1014,7 @@ extern "C" int rptc_gemv(const void *codes, const void *lut, const uint32_t *car
                          rptc_stream_t stream) {
     if (int e = validate_gemv_args(codes, lut, x, ld_x, acc, ld_acc, m, n, batch, x_order, fmt)) return e;
     if (int e = rptc_check_device()) return e;
-    // batches that are not a power of two run as a short sequence of launches
+    // batches beyond eight, or not a power of two, run as a short sequence of launches (8 + 8, 4 + 1, ...)
     int done = 0;
     while (done < batch) {
         int b = 8;

@@ -165,6 +165,13 @@ class RPTCLlama:
         return (self.tp_world > 1 and self.blocks[0].qkv.incoherent and n & (n - 1) == 0 and 256 <= n <= 8192
                 and self.cfg.head_dim == 128 and self.blocks[0].qkv.block_out >= 128 and self.fused_tp)
 
+    def _extra_launches(self) -> int:
+        """Launches beyond one per matvec: a fused matvec takes up to eight activation rows per launch (8 + 8 at sixteen
+        rows, 4 + 1 at five), and so does the output head."""
+        q, r = divmod(self.rows, 8)
+        per_matvec = q + bin(r).count("1") - 1
+        return 4 * per_matvec * len(self.blocks) + (self.rows - 1) // 8
+
     def step_eager(self) -> None:
         if self._glueable():
             self._step_glued()
@@ -235,7 +242,7 @@ class RPTCLlama:
             n_launch += 9
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = n_launch + 2
+        self.launches_per_step = n_launch + 2 + self._extra_launches()
 
     def _step_glued(self) -> None:
         """qkv matvec -> attention -> o matvec -> gate-up matvec -> SwiGLU -> down matvec.  The two matvecs that
@@ -332,7 +339,7 @@ class RPTCLlama:
                 ops.finish_norm_hadamard(None, None, 1.0, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = ((8 if mlp_glued else 9) + 2 * per_reduce) * len(self.blocks) + 4
+        self.launches_per_step = ((8 if mlp_glued else 9) + 2 * per_reduce) * len(self.blocks) + 4 + self._extra_launches()
 
     def _step_fused_tp_glued(self, normed_matvec, mlp_glued: bool, per_reduce: int) -> None:
         """The tensor-parallel chain with the norms inside the matvecs: qkv* -> q/k/v finish -> attention -> o ->
@@ -395,7 +402,7 @@ class RPTCLlama:
         ops.rmsnorm(self.h, self.norm_f, self.xn, cfg.rms_eps)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = n_launch + 3
+        self.launches_per_step = n_launch + 3 + self._extra_launches()
 
     def _finish_row_parallel(self, lin: RPTCLinear) -> None:
         """h += (sum over tensor-parallel ranks of) this rank's partial output of a row-parallel layer."""

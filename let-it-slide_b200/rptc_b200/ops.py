@@ -291,8 +291,10 @@ def dense_gemv(W: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None
         out = torch.empty((x.shape[0], m), dtype=torch.float16, device=x.device)
     o2 = out.unsqueeze(0) if out.dim() == 1 else out
     with torch.cuda.device(W.device):
-        check(lib().rptc_dense_gemv(ptr(W), W.stride(0), ptr(x), _ld(x, n), ptr(o2), _ld(o2, m), m, n, x.shape[0], stream_ptr()),
-              "rptc_dense_gemv")
+        for b0 in range(0, x.shape[0], 8):              # the kernel takes up to eight activation rows per launch
+            xb, ob = x[b0:b0 + 8], o2[b0:b0 + 8]
+            check(lib().rptc_dense_gemv(ptr(W), W.stride(0), ptr(xb), _ld(xb, n), ptr(ob), _ld(ob, m), m, n, xb.shape[0], stream_ptr()),
+                  "rptc_dense_gemv")
     return out[0] if squeeze and out.dim() == 2 else out
 
 

@@ -336,3 +336,46 @@ def test_two_devices_in_one_process():
             assert torch.equal(y8, dense.t()[:8]) and torch.equal(y1, dense.t()[:1]) and torch.equal(yg, dense[:128].t()[:256])
             results.append(dense.cpu())
     assert torch.equal(results[0], results[1])
+
+
+@pytest.mark.parametrize("kv_heads", [4, 2])
+def test_decode_sixteen_rows_at_once(kv_heads):
+    """Decode batch 16 (the reference's kernels take one activation vector only, inference.cu:291 `V == 1`): sixteen
+    sequences step together, every fused matvec runs as two launches of eight rows; logits of every row against the fp32
+    forward, eager and from the captured graph."""
+    from rptc_b200 import ops
+    from rptc_b200.llama import LlamaConfig, RPTCLlama
+    cfg = LlamaConfig(hidden=1024, layers=2, heads=8, kv_heads=kv_heads * 2, ffn=2816, vocab=1024, max_pos=32, weight_scale=0.05)
+    rows, T = 16, 6
+    model = RPTCLlama(cfg, rows=rows, seed=11)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
+    ref = model.reference_logits(tokens)
+    for use_graph in (False, True):
+        model.reset()
+        model.graph = None
+        if use_graph:
+            model.capture(pdl=True)
+        for t in range(T):
+            model.ids.copy_(tokens[:, t].to(torch.int32))
+            model.step()
+            torch.cuda.synchronize()
+            err = (model.logits.float() - ref[:, t]).abs().amax(dim=1) / ref[:, t].abs().amax(dim=1)
+            assert float(err.max()) <= 1e-2, (use_graph, t, err.tolist())
+        assert model.pos.tolist() == [T] * rows
+    ops.device_status()
+
+
+def test_fused_matvec_sixteen_rows_matches_two_calls_of_eight():
+    from rptc_b200 import Format, ops
+    fmt = Format()
+    m, n = 1024, 4096
+    g = torch.Generator(device="cuda").manual_seed(8)
+    codes = torch.randint(-2**31, 2**31 - 1, ops.codes_shape(m, n, 2, fmt.layout), dtype=torch.int32, device="cuda", generator=g)
+    lut = torch.randn(512, dtype=torch.float16, device="cuda", generator=g)
+    x = torch.eye(n, dtype=torch.float16, device="cuda")[100:116]          # sixteen unit vectors: exact
+    y = ops.gemv(codes, lut, x, m, n, fmt)
+    dense = ops.decompress(codes, lut, m, n, fmt)
+    assert torch.equal(y, dense.t()[100:116])
+    y13 = ops.gemv(codes, lut, x[:13], m, n, fmt)                           # 8 + 4 + 1
+    assert torch.equal(y13, dense.t()[100:113])
