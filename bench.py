@@ -16,7 +16,7 @@ stream over buffers larger than L2: `roofline_lut` (the fused GEMV with the 65,5
 decompression-only cases).
 
 `--workload llama2-70b-tp` runs the partitioned shape alone.  `--workload kernels --case SPEC` times single kernels
-(the commands the ncu summaries under profiles/ were taken with):
+(small enough to put under a profiler):
     gemv:MxN:bB[:hash|lut|lite]    gemm:MxN:tT[:hash|lut]    decompress:MxN:kK[:hash|lut]    all-gemv | all-gemm | all-decompress
 `--plain` launches them one by one instead of replaying a CUDA graph (what a profiler should see), `--copies` sets the
 number of distinct weight buffers.
@@ -576,7 +576,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     out = None
     if rank == 0:
         linears = [l for b in model.blocks for l in b.linears()]
-        roof = gemv_roofline(torch, linears, "gemv_pair_kernel<HASH,K=2,batch=1>", sampler)
+        roof = gemv_roofline(torch, linears, "gemv_rows_kernel<HASH,K=2,batch=1>", sampler)
         bt = bytes_per_token(cfg_dims, args.prompt + args.warmup + args.steps // 2, world if tp else 1)
         seqs = 1 if tp else world
         out = {"metric": METRIC if not tp else "2-bit Llama-2-70B-shape tensor-parallel decode tok/s (bs1)",
@@ -599,7 +599,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
         shapes = [(4096, 12288), (4096, 4096), (4096, 22016), (11008, 4096)]           # (in, out) of a 7B block's four linears
         lut_linears = [RPTCLinear.random(i, o, fmt_lut, 0.02, 1000 + 4 * layer + k, "cuda", incoherent=False)
                        for layer in range(32) for k, (i, o) in enumerate(shapes)]
-        out["roofline_lut"] = gemv_roofline(torch, lut_linears, "gemv_pair_kernel<LUT L=16,K=2,batch=1>", sampler)
+        out["roofline_lut"] = gemv_roofline(torch, lut_linears, "gemv_rows_kernel<LUT L=16,K=2,batch=1>", sampler)
         del lut_linears
         torch.cuda.empty_cache()
         gemm = [time_gemm(torch, m, n, t, sampler=sampler) | {"layer": name} for name, m, n in LLAMA7B_LAYERS for t in (512, 2048)]

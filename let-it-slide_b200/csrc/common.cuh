@@ -213,6 +213,10 @@ __device__ __forceinline__ int64_t unit_index(const UnitStrides &s, int64_t u, i
 //              (which is bit 15 of the hash).  The table must start on a 64 KiB boundary of the shared
 //              window so that (hash & 0xFF00) | 4*lane is the whole address computation.
 // LITE code  : 2^S rows of 128 bytes, the pair of entry e at byte 4*lane of row e.
+// HASH code, packed (kCodeHashPacked; a table layout, not a fourth code): the same 256 rows at 128 bytes each, on a
+//              32 KiB boundary; the address is ((hash >> 1) & 0x7F80) | table | 4*lane, one shift more per lookup.
+constexpr int kCodeHashPacked = 3;
+constexpr uint32_t kHashPackedLutBytes = 32768;
 constexpr uint32_t kHashLutBytes = 65536;
 constexpr uint32_t kHashLutWindow = 0x10000;   // shared-window address the HASH table is placed at (literal in lds32_hash)
 static_assert(kHashLutWindow == 65536, "lds32_hash spells this address out");
@@ -228,6 +232,7 @@ template <int CODE>
 __device__ __forceinline__ uint32_t lut_bytes(int L, int S) {
     if (CODE == RPTC_CODE_LUT) return 2u << L;
     if (CODE == RPTC_CODE_HASH) return kHashLutBytes;
+    if (CODE == kCodeHashPacked) return kHashPackedLutBytes;
     return 128u << S;
 }
 
@@ -257,7 +262,8 @@ __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restric
         // A table row is 32 copies of one 4-byte pair (one per bank): eight 128-bit stores.  Thread i takes
         // part i & 7 of row i >> 3, four rows in flight per thread.
         const uint32_t *src = reinterpret_cast<const uint32_t *>(g);
-        const int rows = (CODE == RPTC_CODE_HASH) ? 256 : (1 << S);
+        constexpr bool kHash = CODE == RPTC_CODE_HASH || CODE == kCodeHashPacked;
+        const int rows = kHash ? 256 : (1 << S);
         const uint32_t row_bytes = (CODE == RPTC_CODE_HASH) ? 256u : 128u;
         const int smask = (1 << S) - 1;
         const int total = rows * 8;
@@ -274,7 +280,7 @@ __device__ __forceinline__ void lut_fill(uint32_t table, const __half *__restric
                 if (i < total) {
                     const int e = i >> 3;
                     uint32_t x = v[k];
-                    if (CODE == RPTC_CODE_HASH) x = (x & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
+                    if (kHash) x = (x & 0xFFFF7FFFu) | ((uint32_t)(e >> 7) << 15);
                     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(table + row_bytes * e + 16u * (i & 7)), "r"(x) : "memory");
                 }
             }
@@ -396,6 +402,9 @@ __device__ __forceinline__ uint32_t decode_pair_bits(const uint32_t (&R)[N], con
         if (CODE == RPTC_CODE_HASH) {
             const uint32_t h = t * t + t;
             return lds32_hash(and_or(h, 0xFF00u, lut.base));
+        } else if (CODE == kCodeHashPacked) {
+            const uint32_t h = t * t + t;
+            return lds32(and_or(h >> 1, 0x7F80u, lut.base));
         } else {
             // Bits above the state width never reach the entry index (rptc_lite.py:12-16 uses bits
             // [0,S) and [L-S,L) of the product only), so the raw window needs no masking.

@@ -2,25 +2,29 @@
 //
 //   y[t][row] = sum_c x[t][c] * W[row][c]        x: [tokens][n] fp16,  W decoded on the fly
 //
-// One CTA owns an output tile of 256 tokens x NROWS weight rows (256 when m allows, else 128) and walks
-// the reduction dimension in steps of 64 columns through a ring of shared-memory stages.  With both
-// operands read from shared memory a 128 x 128 x 16 MMA needs 8 KiB of operand reads per 64 tensor-core
-// cycles -- exactly the 128 B/clk a SM's shared memory delivers -- so the wide tile (N = 256, 12 KiB per
-// 128 cycles) is what lets the tensor pipe run ahead of shared memory.  Warp roles:
-//   warps 0-7  decode producers in two groups of four that take alternate steps, so that two stages
-//              are being decoded at any time: thread r of a group owns weight row r of the tile.  Per step
-//              it takes the row's next 128 * K / 2 code bits with 128-bit loads (coalesced per 32-row
-//              block of the TILED layout), rebuilds the shift-register windows with funnel shifts, looks
-//              the weights up, and writes its 128-byte row of the B operand straight into the
-//              128-byte-swizzled K-major layout the tensor core reads.  After the last step the same
-//              warps run the epilogue (group g drains token half g).
-//   warp 8     one lane issues the 2-D TMA loads of the activation tile (two 128-token halves).
-//   warp 9     owns the TMEM allocation; one lane issues tcgen05.mma (M=128, N=128, K=16, fp32
-//              accumulators in TMEM, two token halves) and commits each stage back to the producers.
+// One CTA owns an output tile of 256 tokens x NROWS weight rows (256 when m allows, else 128) and walks the reduction
+// dimension in steps of 64 columns.  With both operands read from shared memory a 128 x 128 x 16 MMA needs 8 KiB of
+// operand reads per 64 tensor-core cycles -- exactly the 128 B/clk a SM's shared memory delivers -- so the wide tile
+// (N = 256, 12 KiB per 128 cycles) is what lets the tensor pipe run ahead of shared memory.  The two operands travel
+// through separate shared-memory rings (activations: up to four stages of 32 KiB; decoded weights: two or three stages of
+// 128 bytes per tile row), each with its own full/empty barriers.  Warp roles:
+//   warps 0-7  decode producers: thread r owns weight row r of the tile (256-row tiles: every thread takes every step;
+//              128-row tiles: two groups of four warps take alternate steps).  Per step a thread takes its row's next
+//              128 * K / 2 code bits with 128-bit loads (coalesced per 32-row block of the TILED layout), rebuilds the
+//              shift-register windows with funnel shifts and looks the 64 weights up INTO REGISTERS; only then does it
+//              wait for the stage, and writes its 128-byte row of the B operand straight into the 128-byte-swizzled
+//              K-major layout the tensor core reads.  After the last step the same warps run the epilogue.
+//   warp 8     one lane issues the 2-D TMA loads of the activation tile (two 128-token halves), as far ahead as the
+//              activation ring allows.
+//   warp 9     owns the TMEM allocation; one lane issues tcgen05.mma (M = 128, N = NROWS, K = 16, fp32 accumulators
+//              in TMEM, two token halves) and commits each stage of either ring back to its producer.
 // Epilogue: tcgen05.ld 32 lanes x 32 columns at a time -> fp16 -> 128-bit global stores.
-// Every wait on an mbarrier is bounded; a wait that runs out raises the device status word and the
-// CTA drains and returns (TMEM is still released).
+// The HASH code's table is kept in its packed form here (32 KiB instead of the GEMV kernels' 64 KiB), which is what
+// makes room for the third activation stage beside two 32 KiB weight stages.
+// Every wait on an mbarrier is bounded; a wait that runs out raises the device status word and the CTA drains and
+// returns (TMEM is still released).
 #include <cuda.h>
+#include <stdlib.h>
 #include <cudaTypedefs.h>
 
 #include "common.cuh"
@@ -31,10 +35,13 @@ constexpr int kTileTokens = 256;       // two M = 128 halves
 constexpr int kStepCols = 64;          // one 128-byte swizzle atom of fp16
 constexpr uint32_t kXHalfBytes = 128 * kStepCols * 2;          // 16 KiB
 constexpr uint32_t kXBytes = 2 * kXHalfBytes;                  // 32 KiB
-constexpr int kMaxGemmStages = 3;
+constexpr int kMaxGemmStages = 4;      // per ring
 constexpr int kGemmThreads = 320;
 constexpr int kProducerWarps = 8, kTmaWarp = 8, kMmaWarp = 9;
 
+// The decoded-weight ring and the activation ring are separate: a TMA load takes about a microsecond to land and so
+// wants the deeper ring, while a weight stage is refilled within a few hundred cycles of being handed back (the
+// producers decode into registers ahead of time and only store once the stage is free).
 struct GemmParams {
     const uint4 *codes;
     const __half *lut;
@@ -44,10 +51,35 @@ struct GemmParams {
     int64_t m, n, tokens;
     int32_t n_units;                  // units per row
     int32_t L, S;
-    int32_t n_stages;
-    uint32_t bar_addr, lut_addr;      // absolute addresses in the shared window
-    uint32_t xa_addr[kMaxGemmStages], xb_addr[kMaxGemmStages], w_addr[kMaxGemmStages];   // the three pieces of a stage
+    int32_t n_xstages, n_wstages;
+    uint32_t bar_addr, lut_addr;      // offsets in the CTA's shared window
+    uint32_t xa_addr[kMaxGemmStages], xb_addr[kMaxGemmStages];   // activation ring: two 128-token halves per stage
+    uint32_t w_addr[kMaxGemmStages];                             // decoded-weight ring
     unsigned int *status;
+};
+
+// Barrier block (8 bytes each) at GemmParams::bar_addr.
+struct GemmBars {
+    uint32_t full_w, full_x, empty_w, empty_x, accum, tmem_slot, done, peer;
+};
+__device__ __forceinline__ GemmBars gemm_bars(uint32_t base) {
+    GemmBars b;
+    b.full_w = base;
+    b.full_x = base + 8 * kMaxGemmStages;
+    b.empty_w = base + 16 * kMaxGemmStages;
+    b.empty_x = base + 24 * kMaxGemmStages;
+    b.peer = base + 32 * kMaxGemmStages;          // two-SM kernel, leader only: the partner's step is complete
+    b.accum = base + 40 * kMaxGemmStages;
+    b.tmem_slot = b.accum + 8;
+    b.done = b.accum + 16;                        // two-SM kernel: the partner has drained its accumulators
+    return b;
+}
+
+// The HASH code is looked up in the packed table (128-byte rows) here: 32 KiB instead of 64 KiB leaves room for one more
+// ring stage, and the extra shift per lookup is hidden behind the tensor pipe.
+template <int CODE>
+struct GemmDecode {
+    static constexpr int kCode = CODE == RPTC_CODE_HASH ? kCodeHashPacked : CODE;
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -78,14 +110,150 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
 // fp32 accumulate, fp16 A and B, both K-major, M = 128
 constexpr uint32_t instr_desc(int n_rows) { return (1u << 4) | ((uint32_t)(n_rows >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); }
 
+// Position in a ring of `n` stages without a division per step.
+struct RingPos {
+    int s;
+    uint32_t phase;
+    __device__ __forceinline__ void advance(int n) {
+        if (++s == n) s = 0, phase ^= 1u;
+    }
+    __device__ __forceinline__ void advance_by(int k, int n) {
+        for (int i = 0; i < k; ++i) advance(n);
+    }
+};
+
+// `window` in the functions below: bits to OR onto every planned shared-memory offset (0 outside a cluster; inside one,
+// the upper address bits that select this CTA's window in the cluster's).
+// ---- decode producers ------------------------------------------------------------------------------------------------
+// GROUPS groups of 256 / GROUPS threads take alternate steps; thread r of a group owns weight row `row0 + r`.  A step's 64
+// weights are decoded into registers BEFORE the wait for the stage, so that between the tensor cores handing a stage back
+// and its next contents being announced lie only eight 128-bit stores and a fence.
+template <int CODE, int K, int GROUPS>
+__device__ __forceinline__ bool produce_weights(const GemmParams &p, uint32_t window, const GemmBars &bars, int64_t row0, int n_steps) {
+    constexpr int DC = GemmDecode<CODE>::kCode;
+    constexpr int UPS = K / 2;                 // 128-bit units per 64-column step
+    constexpr int kPairs = GroupShape<K>::kPairs;
+    static_assert(UPS * kPairs == 32, "a step is 32 weight pairs per row");
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const Lut<DC> lut = lut_view<DC>(p.lut_addr | window, p.L, p.S);
+    const int group = GROUPS == 2 ? warp >> 2 : 0;      // takes steps it = group, group + GROUPS, ...
+    const int r = GROUPS == 2 ? (tid & 127) : tid;      // row of the tile
+    const int64_t row = row0 + r;
+    // TILED layout: unit u of row -> ((row >> 5) * n_units + u) * 32 + (row & 31)
+    const uint4 *src = p.codes + ((row >> 5) * (int64_t)p.n_units) * 32 + (row & 31);
+    auto history = [&](int it) -> uint32_t {             // last word before step `it` (decoded by the other group)
+        if (it == 0) return p.carry_in ? __ldg(p.carry_in + row) : 0u;
+        return __ldg(reinterpret_cast<const uint32_t *>(src + ((int64_t)it * UPS - 1) * 32) + 3);
+    };
+    uint4 nxt[UPS];
+    uint32_t nxt_prev = 0, carry = 0;                    // carry: last word of the previous step when this thread decoded it
+    if (group < n_steps) {
+#pragma unroll
+        for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)group * UPS + q) * 32);
+        nxt_prev = history(group);
+    }
+    RingPos pos = {0, 1u};                               // waits on `empty` pass at once the first time round
+    pos.advance_by(group, p.n_wstages);
+    for (int it = group; it < n_steps; it += GROUPS) {
+        uint4 cur[UPS];
+#pragma unroll
+        for (int q = 0; q < UPS; ++q) cur[q] = nxt[q];
+        uint32_t prevw = (GROUPS == 2 || it == 0) ? nxt_prev : carry;
+        if (it + GROUPS < n_steps) {
+#pragma unroll
+            for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + GROUPS) * UPS + q) * 32);
+            nxt_prev = GROUPS == 2 ? history(it + GROUPS) : 0u;
+        }
+        uint32_t out[32];
+#pragma unroll
+        for (int q = 0; q < UPS; ++q) {
+            const uint32_t w[4] = {cur[q].x, cur[q].y, cur[q].z, cur[q].w};
+            decode_group<DC, K>(w, prevw, lut, [&](int pi, __half2 wp) { out[q * kPairs + pi] = half2_as_u32(wp); });
+            prevw = cur[q].w;
+        }
+        carry = prevw;
+        if (!mbar_wait(bars.empty_w + 8 * pos.s, pos.phase, p.status)) return false;      // the MMAs are done with the stage's old contents
+        const uint32_t wrow = (p.w_addr[pos.s] | window) + (uint32_t)r * 128u;
+#pragma unroll
+        for (uint32_t chunk = 0; chunk < 8; ++chunk)         // 16-byte chunks of the row, 128-byte swizzle
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(wrow + 16u * (chunk ^ ((uint32_t)r & 7u))), "r"(out[4 * chunk]),
+                         "r"(out[4 * chunk + 1]), "r"(out[4 * chunk + 2]), "r"(out[4 * chunk + 3])
+                         : "memory");
+        fence_proxy_async_smem();               // make the generic-proxy stores visible to the tensor cores' reads
+        mbar_arrive(bars.full_w + 8 * pos.s);
+        pos.advance_by(GROUPS, p.n_wstages);
+    }
+    return true;
+}
+
+// ---- activation loads (one thread) ----------------------------------------------------------------------------------
+__device__ __forceinline__ bool load_activations(const GemmParams &p, uint32_t window, const GemmBars &bars, const CUtensorMap *x_map, int tok0,
+                                                 int n_steps) {
+    RingPos pos = {0, 1u};
+    for (int it = 0; it < n_steps; ++it) {
+        if (!mbar_wait(bars.empty_x + 8 * pos.s, pos.phase, p.status)) return false;
+        const uint32_t bar = bars.full_x + 8 * pos.s;
+        mbar_expect_tx(bar, kXBytes);
+        tma_load_2d(p.xa_addr[pos.s] | window, x_map, it * kStepCols, tok0, bar);
+        tma_load_2d(p.xb_addr[pos.s] | window, x_map, it * kStepCols, tok0 + 128, bar);
+        pos.advance(p.n_xstages);
+    }
+    return true;
+}
+
+// ---- epilogue (warps 0-7): TMEM -> fp16 -> global; `tok0` this CTA's first token, `row0` the tile's first weight row ----
+template <int NROWS>
+__device__ __forceinline__ void drain_accumulators(const GemmParams &p, uint32_t tmem_base, int tok0, int64_t row0) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = warp >> 2, quarter = warp & 3;              // a warp may only touch TMEM lanes 32*(warp % 4) ...
+    const int64_t tok = (int64_t)tok0 + h * 128 + quarter * 32 + lane;
+#pragma unroll 1
+    for (int c = 0; c < NROWS / 32; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * NROWS + c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (tok < p.tokens) {
+            __half *dst = p.y + tok * p.ld_y + row0 + c * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
+                asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 8 * j), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                             : "memory");
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void init_ring_barriers(const GemmParams &p, const GemmBars &bars, uint32_t producers_per_stage) {
+    for (int s = 0; s < kMaxGemmStages; ++s) {
+        mbar_init(bars.full_w + 8 * s, producers_per_stage);
+        mbar_init(bars.full_x + 8 * s, 1);
+        mbar_init(bars.empty_w + 8 * s, 1);
+        mbar_init(bars.empty_x + 8 * s, 1);
+        mbar_init(bars.peer + 8 * s, 1);
+    }
+    mbar_init(bars.accum, 1);
+    mbar_init(bars.done, 1);
+    mbar_fence_init();
+}
+
 template <int CODE, int K, int NROWS>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
-    constexpr int UPS = K / 2;                 // 128-bit units per 64-column step
-    constexpr int kTileRows = NROWS;
+    constexpr int DC = GemmDecode<CODE>::kCode;
     constexpr uint32_t kTmemCols = 2 * NROWS;  // two token halves of NROWS fp32 columns
     constexpr uint32_t kInstrDesc = instr_desc(NROWS);
     constexpr int kGroups = NROWS == 256 ? 1 : 2;        // producer groups taking alternate steps
-    constexpr uint32_t kProducersPerStage = 256 / kGroups;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s0 = smem_addr(smem_raw);
@@ -93,168 +261,243 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
         if (tid == 0) atomicExch(p.status, kStatusSmemPlan);
         return;
     }
-    // barriers: full_w[s] (128 producer arrivals), full_x[s] (TMA bytes), empty[s] (MMA commit), accum, tmem slot
-    const uint32_t bar_full_w = p.bar_addr, bar_full_x = p.bar_addr + 8 * kMaxGemmStages, bar_empty = p.bar_addr + 16 * kMaxGemmStages;
-    const uint32_t bar_accum = p.bar_addr + 24 * kMaxGemmStages, tmem_slot = bar_accum + 8;
+    const GemmBars bars = gemm_bars(p.bar_addr);
     const int n_steps = (int)(p.n / kStepCols);
-    const int64_t row0 = (int64_t)blockIdx.x * kTileRows;
+    const int64_t row0 = (int64_t)blockIdx.x * NROWS;
     const int tok0 = blockIdx.y * kTileTokens;
 
-    if (tid == 0) {
-        for (int s = 0; s < p.n_stages; ++s) {
-            mbar_init(bar_full_w + 8 * s, kProducersPerStage);
-            mbar_init(bar_full_x + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1);
-        }
-        mbar_init(bar_accum, 1);
-        mbar_fence_init();
-    }
+    if (tid == 0) init_ring_barriers(p, bars, 256 / kGroups);
     if (warp == kMmaWarp) {                     // TMEM: two fp32 accumulators of NROWS columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars.tmem_slot), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // the lookup table is only needed by the producer warps, but everyone helps to fill it
-    {
-        // lut_fill assumes blockDim.x threads take part
-        lut_fill<CODE>(p.lut_addr, p.lut, p.L, p.S);
-    }
+    lut_fill<DC>(p.lut_addr, p.lut, p.L, p.S);         // only the producer warps read the table, but everyone helps to fill it
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     pdl_allow_next_grid();
     uint32_t tmem_base;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(bars.tmem_slot));
     bool ok = true;
 
     if (warp < kProducerWarps) {
-        // ================= decode producers =================
-        const Lut<CODE> lut = lut_view<CODE>(p.lut_addr, p.L, p.S);
-        const int group = kGroups == 2 ? warp >> 2 : 0;      // takes steps it = group, group + kGroups, ...
-        const int r = kGroups == 2 ? (tid & 127) : tid;      // row of the tile
-        const int64_t row = row0 + r;
-        // TILED layout: unit u of row -> ((row >> 5) * n_units + u) * 32 + (row & 31)
-        const uint4 *src = p.codes + ((row >> 5) * (int64_t)p.n_units) * 32 + (row & 31);
-        auto history = [&](int it) -> uint32_t {             // last word before step `it` (decoded by the other group)
-            if (it == 0) return p.carry_in ? __ldg(p.carry_in + row) : 0u;
-            return __ldg(reinterpret_cast<const uint32_t *>(src + ((int64_t)it * UPS - 1) * 32) + 3);
-        };
-        uint4 nxt[UPS];
-        uint32_t nxt_prev = 0, carry = 0;                    // carry: last word of the previous step when this thread decoded it
-        if (group < n_steps) {
-#pragma unroll
-            for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)group * UPS + q) * 32);
-            nxt_prev = history(group);
-        }
-        for (int it = group; it < n_steps && ok; it += kGroups) {
-            const int s = it % p.n_stages;
-            const uint32_t par = ((uint32_t)(it / p.n_stages) & 1u) ^ 1u;
-            uint4 cur[UPS];
-#pragma unroll
-            for (int q = 0; q < UPS; ++q) cur[q] = nxt[q];
-            uint32_t prevw = (kGroups == 2 || it == 0) ? nxt_prev : carry;
-            if (it + kGroups < n_steps) {
-#pragma unroll
-                for (int q = 0; q < UPS; ++q) nxt[q] = ldg128_stream(src + ((int64_t)(it + kGroups) * UPS + q) * 32);
-                nxt_prev = kGroups == 2 ? history(it + kGroups) : 0u;
-            }
-            ok = mbar_wait(bar_empty + 8 * s, par, p.status);          // the MMA is done with this stage's old contents
-            if (!ok) break;
-            const uint32_t wrow = p.w_addr[s] + (uint32_t)r * 128u;
-#pragma unroll
-            for (int q = 0; q < UPS; ++q) {
-                const uint32_t w[4] = {cur[q].x, cur[q].y, cur[q].z, cur[q].w};
-                uint32_t buf[4];
-                decode_group<CODE, K>(w, prevw, lut, [&](int pi, __half2 wp) {
-                    buf[pi & 3] = half2_as_u32(wp);
-                    if ((pi & 3) == 3) {
-                        const uint32_t chunk = (uint32_t)(q * (GroupShape<K>::kPairs / 4) + (pi >> 2));     // 16-byte chunk of the row
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(wrow + 16u * (chunk ^ ((uint32_t)r & 7u))), "r"(buf[0]),
-                                     "r"(buf[1]), "r"(buf[2]), "r"(buf[3])
-                                     : "memory");
-                    }
-                });
-                prevw = cur[q].w;
-            }
-            carry = prevw;
-            fence_proxy_async_smem();               // make the generic-proxy stores visible to the tensor core's reads
-            mbar_arrive(bar_full_w + 8 * s);
-        }
+        ok = produce_weights<CODE, K, kGroups>(p, 0u, bars, row0, n_steps);
     } else if (warp == kTmaWarp) {
-        // ================= activation loads =================
         pdl_wait_prior_grids();
-        if (lane == 0) {
-            for (int it = 0; it < n_steps && ok; ++it) {
-                const int s = it % p.n_stages;
-                const uint32_t par = ((uint32_t)(it / p.n_stages) & 1u) ^ 1u;
-                ok = mbar_wait(bar_empty + 8 * s, par, p.status);
-                if (!ok) break;
-                mbar_expect_tx(bar_full_x + 8 * s, kXBytes);
-                tma_load_2d(p.xa_addr[s], &x_map, it * kStepCols, tok0, bar_full_x + 8 * s);
-                tma_load_2d(p.xb_addr[s], &x_map, it * kStepCols, tok0 + 128, bar_full_x + 8 * s);
-            }
-        }
-    } else {
+        if (lane == 0) load_activations(p, 0u, bars, &x_map, tok0, n_steps);
+    } else if (lane == 0) {
         // ================= MMA issue =================
-        if (lane == 0) {
-            for (int it = 0; it < n_steps && ok; ++it) {
-                const int s = it % p.n_stages;
-                const uint32_t par = (uint32_t)(it / p.n_stages) & 1u;
-                ok = mbar_wait(bar_full_x + 8 * s, par, p.status) && mbar_wait(bar_full_w + 8 * s, par, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t xa = p.xa_addr[s], xb = p.xb_addr[s], wa = p.w_addr[s];
+        RingPos px = {0, 0u}, pw = {0, 0u};
+        for (int it = 0; it < n_steps && ok; ++it) {
+            ok = mbar_wait(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait(bars.full_w + 8 * pw.s, pw.phase, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t xa = p.xa_addr[px.s], xb = p.xb_addr[px.s], wa = p.w_addr[pw.s];
 #pragma unroll
-                for (int k = 0; k < kStepCols / 16; ++k) {
-                    const uint64_t bdesc = umma_desc_sw128(wa + 32u * k);
-                    tc_mma_f16(tmem_base, umma_desc_sw128(xa + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
-                    tc_mma_f16(tmem_base + (uint32_t)NROWS, umma_desc_sw128(xb + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
-                }
-                tc_commit(bar_empty + 8 * s);       // arrives when the MMAs above have read this stage
+            for (int k = 0; k < kStepCols / 16; ++k) {
+                const uint64_t bdesc = umma_desc_sw128(wa + 32u * k);
+                tc_mma_f16(tmem_base, umma_desc_sw128(xa + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
+                tc_mma_f16(tmem_base + (uint32_t)NROWS, umma_desc_sw128(xb + 32u * k), bdesc, kInstrDesc, (it | k) != 0);
             }
-            if (ok) tc_commit(bar_accum);           // arrives when every MMA has written its accumulator
+            tc_commit(bars.empty_x + 8 * px.s);       // each arrives when the MMAs above have read the stage
+            tc_commit(bars.empty_w + 8 * pw.s);
+            px.advance(p.n_xstages);
+            pw.advance(p.n_wstages);
         }
+        if (ok) tc_commit(bars.accum);              // arrives when every MMA has written its accumulator
     }
 
-    // ================= epilogue (warps 0-7): TMEM -> fp16 -> global =================
     if (warp < kProducerWarps) {
-        if (ok) ok = mbar_wait(bar_accum, 0, p.status);
+        if (ok) ok = mbar_wait(bars.accum, 0, p.status);
         tc_fence_after();
-        if (ok) {
-            const int h = warp >> 2, quarter = warp & 3;              // a warp may only touch TMEM lanes 32*(warp % 4) ...
-            const int64_t tok = (int64_t)tok0 + h * 128 + quarter * 32 + lane;
-#pragma unroll 1
-            for (int c = 0; c < kTileRows / 32; ++c) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * NROWS + c * 32);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (tok < p.tokens) {
-                    __half *dst = p.y + tok * p.ld_y + row0 + c * 32;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
-                        asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 8 * j), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                     : "memory");
-                    }
-                }
-            }
-        }
+        if (ok) drain_accumulators<NROWS>(p, tmem_base, tok0, row0);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- two SMs on one tile (cta_group::2) ---------------------------------------------------------------------------
+// A cluster of two CTAs owns 512 tokens x 256 weight rows.  CTA c (its rank in the pair) holds tokens [256c, 256c + 256)
+// as two M = 128 halves, exactly like the kernel above, but decodes only HALF of the weight tile: rows [128c, 128c + 128).
+// The pair's MMAs have the shape M = 256 (128 token rows from each CTA), N = 256 (128 weight rows from each CTA's shared
+// memory), K = 16: every SM's tensor core still works on 128 x 256 x 16 per instruction, but reads only 4 KiB of B from
+// its own shared memory (the other half comes across from the partner) and decodes, stores and looks up half as many
+// weights per token.  A weight stage is 16 KiB instead of 32, which buys deeper rings.
+// Roles per CTA are those of the kernel above.  Only the even CTA (the leader) issues MMAs; it needs both CTAs'
+// operands, so the partner's MMA warp turns into a relay: it waits for its own step to be complete and arrives on the
+// leader's `peer` barrier across the cluster.  Stages are handed back to both CTAs' producers, and the finished
+// accumulators announced to both CTAs' epilogues, by tcgen05.commit multicast to the pair.  No TMA load is multicast:
+// each CTA loads its own activations.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar), "r"(rank)
+        : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, unsigned int *status) {
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    atomicExch(status, kStatusWaitExpired);
+    return false;
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {      // arrives on `bar` in BOTH CTAs of the pair
+    asm volatile(
+        "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t z = 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+        : "memory");
+}
+// fp32 accumulate, fp16 A and B, both K-major, M = 256 (two CTAs), N = 256
+constexpr uint32_t kInstrDescPair = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+template <int CODE, int K>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+    constexpr int DC = GemmDecode<CODE>::kCode;
+    constexpr int kHalfRows = 128;             // weight rows this CTA decodes
+    constexpr int kPairRows = 256;             // weight rows of the pair's tile = accumulator columns
+    constexpr uint32_t kTmemCols = 512;        // two token halves of 256 fp32 columns
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // In a cluster every CTA's shared-memory window sits at its own place in the cluster's window: shared addresses of
+    // this CTA's memory carry the CTA's rank in their upper bits (rank 1 of a pair starts at 0x01000000).  The host's plan
+    // holds offsets inside a CTA's window, so those bits are ORed onto every planned address that a load, store, copy or
+    // barrier instruction gets; the tensor-core descriptors keep only the offset bits.
+    const uint32_t s_raw = smem_addr(smem_raw);
+    const uint32_t s0 = s_raw & 0x00FFFFFFu, window = s_raw & 0xFF000000u;
+    if (s0 > p.bar_addr) {                     // both CTAs of a pair see the same start and leave together
+        if (tid == 0) atomicExch(p.status, kStatusSmemPlan);
+        return;
+    }
+    const uint32_t rank = cluster_ctarank();
+    {
+        uint32_t nrank;
+        asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nrank));
+        if (nrank != 2u) {                     // not launched as a pair: nothing below may run
+            if (tid == 0) atomicExch(p.status, kStatusSmemPlan);
+            return;
+        }
+    }
+    const GemmBars bars = gemm_bars(p.bar_addr | window);
+    const int n_steps = (int)(p.n / kStepCols);
+    const int64_t tile_row0 = (int64_t)(blockIdx.x >> 1) * kPairRows;      // first weight row of the pair's tile
+    const int64_t row0 = tile_row0 + (int64_t)rank * kHalfRows;             // first weight row this CTA decodes
+    const int tok0 = blockIdx.y * (2 * kTileTokens) + (int)rank * kTileTokens;
+
+    if (tid == 0) init_ring_barriers(p, bars, kHalfRows);
+    // Both CTAs of the pair must be resident, with their barriers initialised, before either touches the pair's tensor
+    // memory or signals across: the paired allocation below addresses the partner SM.
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == kMmaWarp) {                     // TMEM of both SMs: the same warp of each CTA takes part
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars.tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    lut_fill<DC>(p.lut_addr | window, p.lut, p.L, p.S);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_allow_next_grid();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(bars.tmem_slot));
+    bool ok = true;
+
+    if (warp < kProducerWarps) {
+        ok = produce_weights<CODE, K, 2>(p, window, bars, row0, n_steps);      // two groups of four warps take alternate steps
+    } else if (warp == kTmaWarp) {
+        pdl_wait_prior_grids();
+        if (lane == 0) load_activations(p, window, bars, &x_map, tok0, n_steps);
+    } else if (lane == 0) {
+        RingPos px = {0, 0u}, pw = {0, 0u}, pp = {0, 0u};
+        if (rank == 0) {
+            // ================= leader: MMA issue for the pair =================
+            for (int it = 0; it < n_steps && ok; ++it) {
+                ok = mbar_wait(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait(bars.full_w + 8 * pw.s, pw.phase, p.status) &&
+                     mbar_wait_cluster(bars.peer + 8 * pp.s, pp.phase, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t xa = p.xa_addr[px.s], xb = p.xb_addr[px.s], wa = p.w_addr[pw.s];
+#pragma unroll
+                for (int k = 0; k < kStepCols / 16; ++k) {
+                    const uint64_t bdesc = umma_desc_sw128(wa + 32u * k);
+                    tc_mma_f16_pair(tmem_base, umma_desc_sw128(xa + 32u * k), bdesc, kInstrDescPair, (it | k) != 0);
+                    tc_mma_f16_pair(tmem_base + (uint32_t)kPairRows, umma_desc_sw128(xb + 32u * k), bdesc, kInstrDescPair, (it | k) != 0);
+                }
+                tc_commit_pair(bars.empty_x + 8 * px.s);     // both CTAs get their stages back when the MMAs above have read them
+                tc_commit_pair(bars.empty_w + 8 * pw.s);
+                px.advance(p.n_xstages);
+                pw.advance(p.n_wstages);
+                pp.advance(kMaxGemmStages);
+            }
+            if (ok) tc_commit_pair(bars.accum);              // both CTAs' epilogues start when every MMA has written its accumulator
+        } else {
+            // ================= partner: tell the leader when this CTA's step is complete =================
+            // The `peer` ring has kMaxGemmStages slots, at least as many as either data ring, so an arrival for step
+            // it + kMaxGemmStages can only happen after the leader has issued (and so waited for) step it.
+            for (int it = 0; it < n_steps && ok; ++it) {
+                ok = mbar_wait(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait(bars.full_w + 8 * pw.s, pw.phase, p.status);
+                if (!ok) break;
+                fence_proxy_async_smem();
+                mbar_arrive_remote(bars.peer + 8 * pp.s, 0);
+                px.advance(p.n_xstages);
+                pw.advance(p.n_wstages);
+                pp.advance(kMaxGemmStages);
+            }
+        }
+    }
+
+    // ================= epilogue (warps 0-7): this CTA's 256 tokens x the tile's 256 rows =================
+    if (warp < kProducerWarps) {
+        if (ok) ok = mbar_wait(bars.accum, 0, p.status);
+        tc_fence_after();
+        if (ok) drain_accumulators<kPairRows>(p, tmem_base, tok0, tile_row0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        // the pair's TMEM is released together: tell the partner this CTA is done, wait (bounded) for the same from it
+        if (lane == 0) {
+            mbar_arrive_remote(bars.done, rank ^ 1u);
+            mbar_wait_cluster(bars.done, 0, p.status);
+        }
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -280,11 +523,38 @@ static int launch_gemm(const GemmParams &p, const CUtensorMap &map, size_t smem,
 }
 
 template <int CODE, int K>
+static int launch_gemm_pair(const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
+    static SmemOptIn opted;
+    auto kern = gemm_pair_kernel<CODE, K>;
+    if (int e = allow_max_smem(kern, opted)) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;      // the kernel is compiled for pairs: stated here as well
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    RPTC_CUDA(cudaLaunchKernelEx(&cfg, kern, p, map));
+    return RPTC_OK;
+}
+
+template <int CODE, int K>
 static int launch_gemm_rows(int n_rows, const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
     return n_rows == 256 ? launch_gemm<CODE, K, 256>(p, map, smem, grid, stream) : launch_gemm<CODE, K, 128>(p, map, smem, grid, stream);
 }
 
 int check_format(const rptc_format *f);   // api.cu
+// RPTC_GEMM_PAIR=1 in the environment (read once per process) sends shapes that allow it to the two-SM kernel.  It is
+// not the default: measured on B200 it trails the one-SM kernel on every Llama-2-7B layer shape (206 us against 173 us
+// at 12288 x 4096 x 2048 tokens), the hand-over between the two SMs costing more than the halved operand traffic saves.
+static bool g_gemm_pair = false;
 
 }  // namespace rptc
 
@@ -302,6 +572,13 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
         (reinterpret_cast<uintptr_t>(y) & 15) || (ld_x % 8) || (ld_y % 8))
         return RPTC_ERR_ALIGN;
     if (int e = rptc_check_device()) return e;
+    {
+        static const bool want_pair = [] {
+            const char *v = getenv("RPTC_GEMM_PAIR");
+            return v && v[0] == '1';
+        }();
+        g_gemm_pair = want_pair;
+    }
     auto encode = encode_tiled_fn();
     if (!encode) return RPTC_ERR_CUDA;
 
@@ -332,23 +609,26 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
     p.S = fmt->S;
     p.status = device_status_word();
     if (!p.status) return RPTC_ERR_CUDA;
-    // shared-window plan (absolute addresses; the dynamic area is expected to start at or below 0x400): the
-    // pieces of each stage (two activation halves, one weight tile) go first-fit into the space around the table
+    // Shared-window plan (offsets in the CTA's window; the dynamic area is expected to start at or below 0x400).  The
+    // packed HASH table sits on its 32 KiB boundary; ring stages go first-fit into the space around the table.
     const uint32_t kTop = 0x38800;       // 226 KiB: the last byte any plan may touch (dynamic limit is 227 KiB)
+    const uint32_t kHashAt = 0x8000;
     p.bar_addr = 0x400;
     uint32_t free_lo[2], free_hi[2];
     int n_free;
-    if (fmt->code == RPTC_CODE_HASH) {
-        p.lut_addr = kHashLutWindow;
-        free_lo[0] = 0x800, free_hi[0] = kHashLutWindow;
-        free_lo[1] = kHashLutWindow + kHashLutBytes, free_hi[1] = kTop;
-        n_free = 2;
-    } else {
-        p.lut_addr = 0x800;
-        const uint32_t lb = fmt->code == RPTC_CODE_LUT ? (2u << fmt->L) : (128u << fmt->S);
-        free_lo[0] = (0x800 + lb + 1023u) & ~1023u, free_hi[0] = kTop;
-        n_free = 1;
-    }
+    auto reset_plan = [&] {
+        if (fmt->code == RPTC_CODE_HASH) {
+            p.lut_addr = kHashAt;
+            free_lo[0] = 0x800, free_hi[0] = kHashAt;
+            free_lo[1] = kHashAt + kHashPackedLutBytes, free_hi[1] = kTop;
+            n_free = 2;
+        } else {
+            p.lut_addr = 0x800;
+            const uint32_t lb = fmt->code == RPTC_CODE_LUT ? (2u << fmt->L) : (128u << fmt->S);
+            free_lo[0] = (0x800 + lb + 1023u) & ~1023u, free_hi[0] = kTop;
+            n_free = 1;
+        }
+    };
     auto take = [&](uint32_t bytes) -> uint32_t {
         for (int i = 0; i < n_free; ++i)
             if (free_lo[i] + bytes <= free_hi[i]) {
@@ -358,45 +638,71 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
             }
         return 0;
     };
-    // Tile height: 256 rows feed the tensor pipe about 1.35x faster per CTA-step than 128 rows, but need twice
-    // the time per CTA; with few tiles the shorter ones fill more SMs.  Compare whole waves of CTAs.
+    // Two SMs per tile (512 tokens x 256 rows, each CTA decoding 128 of the rows): on request, when there are tokens for both CTAs.
+    const bool pair = g_gemm_pair && tokens > kTileTokens && m % 256 == 0;
+    // Tile height of the one-SM kernel: 256 rows feed the tensor pipe about 1.35x faster per CTA-step than 128 rows, but
+    // need twice the time per CTA; with few tiles the shorter ones fill more SMs.  Compare whole waves of CTAs.
     int n_rows = 128;
-    if (m % 256 == 0) {
+    if (!pair && m % 256 == 0) {
         const int64_t tt = (tokens + kTileTokens - 1) / kTileTokens, sms = num_sms();
         const int64_t waves256 = ((m / 256) * tt + sms - 1) / sms, waves128 = ((m / 128) * tt + sms - 1) / sms;
         if (waves256 * 148 <= waves128 * 100) n_rows = 256;          // 2 / 1.35 = 1.48
     }
-    int stages = 0;
-    for (int attempt = 0; attempt < 2 && stages < 2; ++attempt) {
+    int xs = 0, ws = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
         if (attempt == 1) {              // the wide tile does not fit beside this table: fall back to 128 rows
-            if (n_rows == 128) break;
+            if (n_rows == 128 || (xs >= 2 && ws >= 2)) break;
             n_rows = 128;
-            if (fmt->code == RPTC_CODE_HASH) {
-                free_lo[0] = 0x800, free_lo[1] = kHashLutWindow + kHashLutBytes;
-            } else {
-                const uint32_t lb = fmt->code == RPTC_CODE_LUT ? (2u << fmt->L) : (128u << fmt->S);
-                free_lo[0] = (0x800 + lb + 1023u) & ~1023u;
-            }
         }
-        stages = 0;
-        const int want = n_rows == 256 ? 2 : kMaxGemmStages;
-        while (stages < want) {
+        reset_plan();
+        xs = ws = 0;
+        const uint32_t w_bytes = (uint32_t)(pair ? 128 : n_rows) * 128u;
+        auto add_x = [&]() -> bool {
+            if (xs == kMaxGemmStages) return false;
             const uint32_t save0 = free_lo[0], save1 = free_lo[1];
-            const uint32_t w = take((uint32_t)n_rows * 128u), xa = take(kXHalfBytes), xb = take(kXHalfBytes);
-            if (!w || !xa || !xb) {
+            const uint32_t xa = take(kXHalfBytes), xb = take(kXHalfBytes);
+            if (!xa || !xb) {
                 free_lo[0] = save0, free_lo[1] = save1;
-                break;
+                return false;
             }
-            p.w_addr[stages] = w, p.xa_addr[stages] = xa, p.xb_addr[stages] = xb;
-            ++stages;
+            p.xa_addr[xs] = xa, p.xb_addr[xs] = xb;
+            ++xs;
+            return true;
+        };
+        auto add_w = [&]() -> bool {
+            if (ws == kMaxGemmStages) return false;
+            const uint32_t w = take(w_bytes);
+            if (!w) return false;
+            p.w_addr[ws++] = w;
+            return true;
+        };
+        // two stages of each ring first, then alternately one more of each, the activation ring (the slower to refill) first
+        add_w(), add_w(), add_x(), add_x();
+        for (bool grew = true; grew && xs >= 2 && ws >= 2;) {
+            grew = add_x();
+            if (ws < 3) grew = add_w() || grew;
         }
     }
-    if (stages < 2) return RPTC_ERR_UNSUPPORTED;
-    for (int s = stages; s < kMaxGemmStages; ++s) p.w_addr[s] = p.xa_addr[s] = p.xb_addr[s] = 0;
-    p.n_stages = stages;
+    if (xs < 2 || ws < 2) return RPTC_ERR_UNSUPPORTED;
+    for (int s = xs; s < kMaxGemmStages; ++s) p.xa_addr[s] = p.xb_addr[s] = 0;
+    for (int s = ws; s < kMaxGemmStages; ++s) p.w_addr[s] = 0;
+    p.n_xstages = xs;
+    p.n_wstages = ws;
     const size_t smem = kTop;            // covers every planned address whatever the start of the dynamic area
-    const dim3 grid((unsigned)(m / n_rows), (unsigned)((tokens + kTileTokens - 1) / kTileTokens));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (pair) {
+        const dim3 pgrid((unsigned)(2 * (m / 256)), (unsigned)((tokens + 2 * kTileTokens - 1) / (2 * kTileTokens)));
+        switch (fmt->code) {
+            case RPTC_CODE_LUT:
+                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LUT, 2>(p, map, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LUT, 4>(p, map, smem, pgrid, s);
+            case RPTC_CODE_HASH:
+                return launch_gemm_pair<RPTC_CODE_HASH, 2>(p, map, smem, pgrid, s);
+            case RPTC_CODE_LITE:
+                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LITE, 2>(p, map, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LITE, 4>(p, map, smem, pgrid, s);
+        }
+        return RPTC_ERR_UNSUPPORTED;
+    }
+    const dim3 grid((unsigned)(m / n_rows), (unsigned)((tokens + kTileTokens - 1) / kTileTokens));
     switch (fmt->code) {
         case RPTC_CODE_LUT:
             return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LUT, 2>(n_rows, p, map, smem, grid, s)

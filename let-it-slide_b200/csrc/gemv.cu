@@ -51,9 +51,9 @@ struct GemvParams {
     int32_t n_units, seg_units;
     int32_t L, S, quirk, x_order;
     unsigned int *status;
-    // activations computed in the launch (pair kernel, INPUT != 0): the caller's descriptor
+    // activations computed in the launch (gemv_rows_kernel, MODE 1): the caller's descriptor
     rptc_gemv_input in;
-    // gemv_colblock_kernel: the gated-MLP middle that produces this layer's activations, and a range to zero
+    // gemv_rows_kernel, MODE 2: the gated-MLP middle that produces this layer's activations, and a range to zero
     SwigluParams sw;
     float *clear;
     int64_t clear_count;
@@ -199,18 +199,18 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 }
 
 // ---- batch 1-2: lane = row, products on the tensor cores -----------------------------------------------------------
-// The decomposition of the pair kernel (a granule = one 128-bit unit of two adjacent 32-row blocks, lane l owns rows
-// 64*p + l and 64*p + 32 + l, a warp walks along its rows), with two changes.
+// A granule is one 128-bit unit of two adjacent 32-row blocks; lane l owns rows 64*p + l and 64*p + 32 + l of block
+// pair p, and a warp walks along its rows.
 //
 // Products.  One mma.sync m16n8k16 (fp16 in, fp32 accumulate) takes FOUR decoded pairs of a lane at once: pairs 2i and
 // 2i+1 of the lane's row in block a (a0, a2) and of its row in block b (a1, a3).  Rows g and g+8 of the A tile are then
 // a mix of the four lanes (g, 0..3), i.e. of four different rows of W -- which is harmless, because B separates them
 // again: lane t's k slots meet the activations only in output column n = t (first activation row) and n = 4 + t
 // (second), every other entry of B is zero.  D[g][4b + t] is the partial dot product of row 4g + t of block a with
-// activation row b, D[g+8][4b + t] the same for block b.  B costs less than before: the lane that supplies column
-// n = g of B reads the activations when g % 4 == t (and g / 4 < BATCH) and holds zeros otherwise, so only four (eight)
-// lanes of a warp take part in the shared-memory loads of x.  Against the HFMA2 form this removes 24
-// of 32 multiply instructions per unit and row block and all fp16 partial sums: the accumulation is fp32 throughout.
+// activation row b, D[g+8][4b + t] the same for block b.  The lane that supplies column n = g of B reads the
+// activations when g % 4 == t (and g / 4 < BATCH) and holds zeros otherwise, so only four (eight) lanes of a warp take
+// part in the shared-memory loads of x.  Against packed fp16 multiply-adds this issues a quarter of the multiply
+// instructions per unit and row block, and there is no fp16 partial sum: the accumulation is fp32 throughout.
 //
 // Codes.  Each lane copies its own 16 bytes of a unit from global memory into a per-warp shared-memory ring with
 // cp.async (the 32 rows of a unit are 512 contiguous bytes in the TILED layout: one fully coalesced request per warp),
@@ -542,9 +542,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows_kernel(const GemvPa
     if (!waited_prior) pdl_wait_prior_grids();
 }
 
-// ---- tensor-core form of the pair kernel ---------------------------------------------------------------
-// Same granules, ring and work split as gemv_pair_kernel, but the products run on mma.sync m16n8k16 (fp16 in,
-// fp32 accumulate) with the decoded weights as the A operand and up to eight activation rows as B:
+// ---- batch 4 and 8: word per lane, up to eight activation rows as the B operand -----------------------------------
+// Same granules and work split as gemv_rows_kernel, with the codes brought in by bulk copies into a per-warp ring.  The
+// products run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) with the decoded weights as the A operand:
 //  * lane (g = lane/4, t = lane%4) decodes WORD t of rows g, g+8, g+16, g+24 of the 32-row tile (the tile is
 //    read as four conflict-free 32-bit loads instead of one 128-bit load per row); the 16 stream bits before a
 //    word come from lane t-1 (same unit) or, for t == 0, from lane t+3's word of the unit before -- one shuffle;
@@ -554,9 +554,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows_kernel(const GemvPa
 //  * the accumulator fragment of a lane is rows g, g+8 x batch columns 2t, 2t+1: after a run, lanes with
 //    2t < BATCH add their sums to the caller's accumulator.
 // Per 64 weights a lane issues 4 word loads, 12 window instructions, 4 per pair for the lookup, 8 MMAs and 2
-// activation loads, a third less than the HFMA2 form, there is no fp16 partial sum, and BATCH up to 8 costs
-// only the shared memory for x.
-template <int CODE, int K, int BATCH, int INPUT>
+// activation loads; there is no fp16 partial sum, and BATCH up to 8 costs only the shared memory for x.
+template <int CODE, int K, int BATCH>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvParams p) {
     constexpr int WPU = 128 / K;
     constexpr int PAIRS = WPU / 2;
@@ -667,75 +666,41 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         if (!waited_prior) {
             pdl_wait_prior_grids();
             waited_prior = true;
-            // the codebook loads were issued before the wait; with computed activations the table is written while the
-            // glue's own loads are in flight (below)
-            if (INPUT == 0 || p.n != 4096) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
+            // the codebook loads were issued before the wait
+            lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
         }
         if (useg0 > 0) __syncthreads();
-        if (INPUT != 0) {
-            // one segment by construction (the host refuses wider rows)
-            if (p.in.clear) {
-                float4 *z = reinterpret_cast<float4 *>(p.in.clear);
-                for (int64_t i = (int64_t)blockIdx.x * kGemvThreads + threadIdx.x; 4 * i < p.in.clear_count;
-                     i += (int64_t)gridDim.x * kGemvThreads)
-                    z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-            float *ex = reinterpret_cast<float *>(smem_raw + (xs - s0) + BATCH * x_batch_stride);
-            FinishNormParams q;
-            q.acc = const_cast<float *>(p.in.acc);
-            q.ld_acc = p.in.ld_acc;
-            q.signs_out = static_cast<const __half *>(p.in.signs_out);
-            q.scale_out = p.in.scale_out;
-            q.h = const_cast<__half *>(static_cast<const __half *>(p.in.h_in));
-            q.h_out = static_cast<__half *>(p.in.h_out);
-            q.ld_h = p.in.ld_h;
-            q.w_norm = static_cast<const __half *>(p.in.w_norm);
-            q.eps = p.in.eps;
-            q.signs_in = static_cast<const __half *>(p.in.signs_in);
-            q.transform_in = 1;
-            q.out = reinterpret_cast<__half *>(smem_raw + (xs - s0));
-            q.ld_out = x_batch_stride >> 1;
-            q.n = (int32_t)p.n;
-            q.block = 4096;
+        {
+        const int64_t col0 = (int64_t)useg0 * WPU;
+        const int pairs = nu * PAIRS;
+        if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+            const int vecs = pairs >> 2;
 #pragma unroll 1
             for (int b = 0; b < BATCH; ++b) {
-                    if (p.n == 4096)
-                        finish_norm_row(q, b, ex, ex + 4096, false, blockIdx.x == 0, b == 0, [&]() {
-                            if (b == 0) lut_fill_end<CODE>(lut_tab, lut_pending, p.S);
-                        });
-                    else finish_norm_row_wide<2>(q, b, ex, ex + 4096, blockIdx.x == 0, b == 0);
-                }
-        } else {
-            const int64_t col0 = (int64_t)useg0 * WPU;
-            const int pairs = nu * PAIRS;
-            if (p.x_order == RPTC_XORDER_NATURAL && ((p.ld_x | col0) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
-                const int vecs = pairs >> 2;
-#pragma unroll 1
-                for (int b = 0; b < BATCH; ++b) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
-                    const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
-                    for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
-                        uint4 v[4];
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (int64_t)b * p.ld_x + col0);
+                const uint32_t dst = xs + (uint32_t)b * x_batch_stride;
+                for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * kGemvThreads) {
+                    uint4 v[4];
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
+                    for (int k = 0; k < 4; ++k)
+                        if (i0 + k * kGemvThreads < vecs) v[k] = ld_ordered_u128(src + i0 + k * kGemvThreads);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (i0 + k * kGemvThreads < vecs)
-                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
-                                             "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
-                                             : "memory");
-                    }
-                }
-            } else {
-                for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
-                    const int b = i / pairs, s = i - b * pairs;
-                    int64_t src = (col0 >> 1) + s;
-                    if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
-                    const uint32_t v = ld_ordered_u32(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+                    for (int k = 0; k < 4; ++k)
+                        if (i0 + k * kGemvThreads < vecs)
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * (i0 + k * kGemvThreads)),
+                                         "r"(v[k].x), "r"(v[k].y), "r"(v[k].z), "r"(v[k].w)
+                                         : "memory");
                 }
             }
+        } else {
+            for (int i = threadIdx.x; i < BATCH * pairs; i += kGemvThreads) {
+                const int b = i / pairs, s = i - b * pairs;
+                int64_t src = (col0 >> 1) + s;
+                if (p.x_order == RPTC_XORDER_K2_LEGACY) src = k2_legacy_pair(src, p.n);
+                const uint32_t v = ld_ordered_u32(reinterpret_cast<const uint32_t *>(p.x + (int64_t)b * p.ld_x) + src);
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(xs + (uint32_t)b * x_batch_stride + 4u * s), "r"(v) : "memory");
+            }
+        }
         }
         __syncthreads();
 
@@ -879,16 +844,10 @@ static int launch_gemv(const GemvParams &p, size_t smem, cudaStream_t stream) {
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }
 
-// Smallest batch that takes the tensor-core kernel.  At batch 1 the HFMA2 pair kernel is about 8 % faster (fewer
-// dependent steps between a word and its products); from batch 2 on the tensor-core kernel wins, by 2.5x at 8.
-#ifndef RPTC_GEMV_MMA_MIN_BATCH
-#define RPTC_GEMV_MMA_MIN_BATCH 2
-#endif
-
-template <int CODE, int K, int BATCH, int INPUT = 0>
+template <int CODE, int K, int BATCH>
 static int launch_gemv_mma(const GemvParams &p, size_t smem, cudaStream_t stream) {
     static SmemOptIn opted;
-    auto kern = gemv_mma_kernel<CODE, K, BATCH, INPUT>;
+    auto kern = gemv_mma_kernel<CODE, K, BATCH>;
     if (int e = allow_max_smem(kern, opted)) return e;
     return launch(kern, dim3(num_sms()), dim3(kGemvThreads), smem, stream, p);
 }

@@ -6,10 +6,10 @@
 # parity tests import it as `rptc_kernels_reference` to pin the CPU oracle's "refkernel" mode
 # against what the reference's own kernels really compute.
 #
-#   usage: oracle/build_ref.sh [reference_root]      (default: $RPTC_REFERENCE_ROOT)
+#   usage: oracle/build_ref.sh [reference_root]      (default: $RPTC_REFERENCE_ROOT, else ../reference beside this repository)
 set -euo pipefail
-REF="${1:-${RPTC_REFERENCE_ROOT:-/root/reference}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
+REF="${1:-${RPTC_REFERENCE_ROOT:-$(dirname "$(dirname "$HERE")")/reference}}"
 SRC="$REF/rptc_kernels/csrc/rptc_kernels"
 OUT="$HERE/_ref"
 [ -d "$SRC" ] || { echo "reference sources not found under $SRC" >&2; exit 3; }

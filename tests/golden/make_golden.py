@@ -121,4 +121,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RPTC_REFERENCE_ROOT", "/root/reference"))
+    # the reference checkout: argument, else RPTC_REFERENCE_ROOT, else a directory `reference` beside this repository
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RPTC_REFERENCE_ROOT")
+         or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))

@@ -41,7 +41,8 @@ def test_argument_errors_need_no_gpu():
     f = Format()
     assert lib().rptc_decompress(None, None, None, None, 0, 32, 64, ctypes.byref(f), None) == -1
     assert lib().rptc_gemv(1 << 8, 1 << 8, None, 1 << 8, 64, 1 << 8, 32, 31, 64, 1, 0, ctypes.byref(f), None) == -2
-    assert lib().rptc_gemv(1 << 8, 1 << 8, None, 1 << 8, 64, 1 << 8, 32, 32, 64, 9, 0, ctypes.byref(f), None) == -1
+    assert lib().rptc_gemv(1 << 8, 1 << 8, None, 1 << 8, 64, 1 << 8, 32, 32, 64, 65, 0, ctypes.byref(f), None) == -1    # 1..64 rows
+    assert lib().rptc_gemv(1 << 8, 1 << 8, None, 1 << 8, 64, 1 << 8, 32, 32, 64, 0, 0, ctypes.byref(f), None) == -1
     bad = Format(code=1, K=4)
     assert lib().rptc_decompress(1 << 8, 1 << 8, None, 1 << 8, 64, 32, 64, ctypes.byref(bad), None) == -4
     assert lib().rptc_hadamard(1 << 8, 0, 256, 1 << 8, 256, None, None, 0, 1, 256, 100, 0, 1.0, 0, None) == -1
