@@ -337,7 +337,7 @@ def time_gemv(torch, m, n, batch, kind="hash", copies=None, plain=False, reps=10
             "frac": gbs / measured_peaks()["hbm_gbs"], "copies": copies}
 
 
-def time_gemm(torch, m, n, tokens, kind="hash", plain=False, reps=10, sampler=None) -> dict:
+def time_gemm(torch, m, n, tokens, kind="hash", plain=False, reps=10, sampler=None, unfused=False) -> dict:
     from rptc_b200 import ops
     fmt = _fmt(kind)
     lut = torch.randn(fmt.lut_numel(), dtype=torch.float16, device="cuda")
@@ -346,8 +346,19 @@ def time_gemm(torch, m, n, tokens, kind="hash", plain=False, reps=10, sampler=No
     y = torch.empty((tokens, m), dtype=torch.float16, device="cuda")
     sec = graph_seconds(torch, lambda: ops.gemm(codes, lut, x, m, n, fmt, out=y), reps, plain, sampler)
     tf = 2.0 * tokens * m * n / sec / 1e12
-    return {"kernel": "gemm", "code": kind, "m": m, "n": n, "tokens": tokens, "us": sec * 1e6, "tflops": tf,
-            "frac": tf / measured_peaks()["tflops"]}
+    out = {"kernel": "gemm", "code": kind, "m": m, "n": n, "tokens": tokens, "us": sec * 1e6, "tflops": tf,
+           "frac": tf / measured_peaks()["tflops"]}
+    if unfused:
+        # the two-step alternative the fused kernel replaces: decompress to dense fp16, then a library GEMM (cuBLAS)
+        dense = torch.empty((m, n), dtype=torch.float16, device="cuda")
+
+        def two_step():
+            ops.decompress(codes, lut, m, n, fmt, out=dense)
+            torch.matmul(x, dense.t(), out=y)
+
+        out["decompress_plus_cublas_us"] = graph_seconds(torch, two_step, reps, plain) * 1e6
+        out["cublas_alone_us"] = graph_seconds(torch, lambda: torch.matmul(x, dense.t(), out=y), reps, plain) * 1e6
+    return out
 
 
 def time_decompress(torch, m, n, K, kind="lut", copies=None, plain=False, reps=5, sampler=None) -> dict:
@@ -389,7 +400,7 @@ def run_kernels(args) -> None:
         elif which == "gemm":
             for _, m, n in LLAMA7B_LAYERS:
                 for t in (512, 2048):
-                    print(json.dumps(time_gemm(torch, m, n, t, plain=args.plain)), flush=True)
+                    print(json.dumps(time_gemm(torch, m, n, t, plain=args.plain, unfused=not args.plain)), flush=True)
         elif which == "decompress":
             for m, n in DECOMPRESS_SHAPES:
                 for K in (2, 3, 4):
@@ -403,7 +414,7 @@ def run_kernels(args) -> None:
         if f[0] == "gemv":
             out = time_gemv(torch, m, n, int(f[2].lstrip("b")), kind or "hash", args.copies, args.plain, args.reps)
         elif f[0] == "gemm":
-            out = time_gemm(torch, m, n, int(f[2].lstrip("t")), kind or "hash", args.plain, args.reps)
+            out = time_gemm(torch, m, n, int(f[2].lstrip("t")), kind or "hash", args.plain, args.reps, unfused=not args.plain)
         elif f[0] == "decompress":
             out = time_decompress(torch, m, n, int(f[2].lstrip("k")), kind or "lut", args.copies, args.plain, args.reps)
         else:
@@ -526,6 +537,39 @@ def allreduce_us(torch, dist, model, world: int, reps: int = 3) -> float | None:
     return float(t.item()) / n * 1e6
 
 
+def kernel_timeline(torch, model, steps: int = 4) -> dict:
+    """Where a decode step's time goes, kernel by kernel: the captured step is replayed under torch.profiler (CUPTI kernel
+    records) and every kernel is charged the time between the end of the kernel before it and its own end -- the chain is
+    serial, so these add up to the step.  Diagnostic only (`--timeline`): run after the timed legs, never inside them."""
+    import collections
+    from torch.profiler import ProfilerActivity, profile
+    if model.mailbox is not None or model.host_ids is not None:
+        # the end-to-end leg left the step waiting for tokens from the host: back to device-resident feedback
+        model.mailbox = None
+        model.bind_host_io(None, None)
+        model.capture(pdl=True)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            model.step()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start]
+    ev.sort(key=lambda e: e.time_range.start)
+    own, crit, cnt = collections.defaultdict(float), collections.defaultdict(float), collections.Counter()
+    last_end = None
+    for e in ev:
+        name = e.name.split("(")[0].replace("void ", "").replace("rptc::", "")
+        own[name] += e.time_range.end - e.time_range.start
+        cnt[name] += 1
+        if last_end is not None:
+            crit[name] += max(0.0, e.time_range.end - last_end)
+        last_end = max(last_end or 0, e.time_range.end)
+    total = sum(crit.values())
+    rows = [{"kernel": k, "launches_per_step": cnt[k] / steps, "own_us": own[k] / cnt[k], "critical_us": crit[k] / cnt[k],
+             "critical_us_per_step": crit[k] / steps, "share": crit[k] / total} for k in sorted(crit, key=lambda k: -crit[k])]
+    return {"us_per_step": total / steps, "kernels": rows}
+
+
 def close_model(torch, dist, model, world: int) -> None:
     model.graph = None              # graphs that captured collectives must be gone before their communicator is torn down
     torch.cuda.synchronize()
@@ -551,6 +595,10 @@ def tp_record(args, torch, dist, world, rank, sampler, allreduce: str, rows: int
            "e2e_tok_s": rows * args.steps / (e2e_ms * 1e-3), "scaling": "strong",
            "roofline": {"bound": "hbm", "achieved": bt["packed"] / step_s / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                         "frac": bt["packed"] / step_s / 1e9 / peaks["hbm_gbs"], "what": "packed codes per GPU per token / step time"}}
+    if args.timeline:
+        if world > 1:
+            dist.barrier()
+        rec["timeline"] = kernel_timeline(torch, model)
     close_model(torch, dist, model, world)
     del model
     torch.cuda.empty_cache()
@@ -587,6 +635,12 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
                "e2e": {"value": seqs * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                "gpu_launches": model.launches_per_step * args.steps, "roofline": roof,
                "token_stream_gbs": (bt["packed"] + bt["head"] + bt["kv"]) / (ms / args.steps * 1e-3) / 1e9}
+    if args.timeline and (tp or rank == 0):          # tensor parallel: every rank must run the steps
+        if tp and world > 1:
+            dist.barrier()
+        tl = kernel_timeline(torch, model)
+        if rank == 0:
+            out["timeline"] = tl
     launches_per_step = model.launches_per_step
     close_model(torch, dist, model, world)
     del model
@@ -602,7 +656,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
         out["roofline_lut"] = gemv_roofline(torch, lut_linears, "gemv_rows_kernel<LUT L=16,K=2,batch=1>", sampler)
         del lut_linears
         torch.cuda.empty_cache()
-        gemm = [time_gemm(torch, m, n, t, sampler=sampler) | {"layer": name} for name, m, n in LLAMA7B_LAYERS for t in (512, 2048)]
+        gemm = [time_gemm(torch, m, n, t, sampler=sampler, unfused=True) | {"layer": name} for name, m, n in LLAMA7B_LAYERS for t in (512, 2048)]
         big = next(c for c in gemm if c["m"] == 12288 and c["tokens"] == 2048)
         out["roofline_gemm"] = {"bound": "tensor", "kernel": "gemm_kernel<HASH,K=2> (tcgen05, TMEM accumulators)", "achieved": big["tflops"],
                                 "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": big["frac"], "case": "12288x4096, 2048 tokens",
@@ -676,6 +730,7 @@ def main() -> None:
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="headline only: skip the other kernels' rooflines (N = 1) and the tensor-parallel leg (N > 1)")
     ap.add_argument("--tp-nccl", action="store_true", help="N > 1: also run the tensor-parallel leg with NCCL all-reduces")
+    ap.add_argument("--timeline", action="store_true", help="add each decode leg's per-kernel critical-path times (torch.profiler)")
     ap.add_argument("--case", default=None, help="--workload kernels: which kernel and shape (see the module docstring)")
     ap.add_argument("--plain", action="store_true", help="--workload kernels: plain launches instead of a CUDA graph")
     ap.add_argument("--copies", type=int, default=None, help="--workload kernels: distinct weight buffers per case")

@@ -225,13 +225,14 @@ int rptc_rope_cache_prompt(void *qkv, int64_t ld_qkv, int64_t rows, int64_t toke
 int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,
                      int64_t ld_out, int64_t rows, int hq, int hkv, int d, int max_pos, float scale, const void *signs_in,
                      rptc_stream_t stream);
-/* rptc_qkv_finish + rptc_attn_decode in one launch for multi-head attention (as many kv heads as q heads, head
- * size 128, the qkv layer's output transform in 128-wide blocks): each (row, head) CTA finishes its own q, k, v
- * from the fused qkv accumulator acc = [q heads | k heads | v heads] (cleared), appends k, v at pos[row], attends
- * over positions [0, pos[row]] and writes the head's output (through the 128-wide input transform of the output
- * projection when signs_in is given). */
+/* rptc_qkv_finish + rptc_attn_decode in one launch (head size 128, the qkv layer's output transform in 128-wide
+ * blocks, heads a multiple of kv_heads): each (row, q head) CTA finishes its own q and the k, v of its kv head from
+ * the fused qkv accumulator acc = [q heads | k heads | v heads], the first q head of each group appends k, v at
+ * pos[row], and every CTA attends over positions [0, pos[row]] and writes its head's output (through the 128-wide
+ * input transform of the output projection when signs_in is given).  With heads == kv_heads acc is left zeroed;
+ * otherwise (k and v are read by every q head of their group) acc is left as it is and the caller zeroes it. */
 int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, const int32_t *pos, void *kcache,
-                         void *vcache, void *out, int64_t ld_out, int64_t rows, int heads, int max_pos, float theta,
+                         void *vcache, void *out, int64_t ld_out, int64_t rows, int heads, int kv_heads, int max_pos, float theta,
                          const void *signs_in, rptc_stream_t stream);
 /* Glue between two quantised layers of a decoder block in one launch (rows that are a single Hadamard
  * block, n = 256..4096):  if acc: h += s_out * H(acc) * scale_out (acc cleared);  xn = rmsnorm(h) * w_norm;

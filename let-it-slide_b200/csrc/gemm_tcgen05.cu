@@ -55,12 +55,13 @@ struct GemmParams {
     uint32_t bar_addr, lut_addr;      // offsets in the CTA's shared window
     uint32_t xa_addr[kMaxGemmStages], xb_addr[kMaxGemmStages];   // activation ring: two 128-token halves per stage
     uint32_t w_addr[kMaxGemmStages];                             // decoded-weight ring
+    uint32_t out_addr[8];             // epilogue: panels of 128 tokens x 64 output columns (16 KiB each), laid over the rings
     unsigned int *status;
 };
 
 // Barrier block (8 bytes each) at GemmParams::bar_addr.
 struct GemmBars {
-    uint32_t full_w, full_x, empty_w, empty_x, accum, tmem_slot, done, peer;
+    uint32_t full_w, full_x, empty_w, empty_x, accum, tmem_slot, done;
 };
 __device__ __forceinline__ GemmBars gemm_bars(uint32_t base) {
     GemmBars b;
@@ -68,8 +69,7 @@ __device__ __forceinline__ GemmBars gemm_bars(uint32_t base) {
     b.full_x = base + 8 * kMaxGemmStages;
     b.empty_w = base + 16 * kMaxGemmStages;
     b.empty_x = base + 24 * kMaxGemmStages;
-    b.peer = base + 32 * kMaxGemmStages;          // two-SM kernel, leader only: the partner's step is complete
-    b.accum = base + 40 * kMaxGemmStages;
+    b.accum = base + 32 * kMaxGemmStages;
     b.tmem_slot = b.accum + 8;
     b.done = b.accum + 16;                        // two-SM kernel: the partner has drained its accumulators
     return b;
@@ -86,6 +86,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
                  "l"(map), "r"(x), "r"(y), "r"(bar)
                  : "memory");
+}
+// Tile of shared memory -> global through the tensor map (clipped at the tensor's bounds), tracked by the thread's bulk group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -110,6 +114,23 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
 // fp32 accumulate, fp16 A and B, both K-major, M = 128
 constexpr uint32_t instr_desc(int n_rows) { return (1u << 4) | ((uint32_t)(n_rows >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); }
 
+// ---- a pair of CTAs (cluster of two) working on one tile: signalling across ------------------------------------------
+// In a pair every barrier that gates an MMA lives in the leader (rank 0): both CTAs' producers and both CTAs' TMA loads
+// signal it directly.  A shared::cluster address with bit 24 cleared is the same offset in rank 0's window.
+constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {               // `bar`: shared::cluster address
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// 2-D TMA load into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+
 // Position in a ring of `n` stages without a division per step.
 struct RingPos {
     int s;
@@ -128,7 +149,7 @@ struct RingPos {
 // GROUPS groups of 256 / GROUPS threads take alternate steps; thread r of a group owns weight row `row0 + r`.  A step's 64
 // weights are decoded into registers BEFORE the wait for the stage, so that between the tensor cores handing a stage back
 // and its next contents being announced lie only eight 128-bit stores and a fence.
-template <int CODE, int K, int GROUPS>
+template <int CODE, int K, int GROUPS, bool PAIR = false>
 __device__ __forceinline__ bool produce_weights(const GemmParams &p, uint32_t window, const GemmBars &bars, int64_t row0, int n_steps) {
     constexpr int DC = GemmDecode<CODE>::kCode;
     constexpr int UPS = K / 2;                 // 128-bit units per 64-column step
@@ -180,35 +201,56 @@ __device__ __forceinline__ bool produce_weights(const GemmParams &p, uint32_t wi
                          "r"(out[4 * chunk + 1]), "r"(out[4 * chunk + 2]), "r"(out[4 * chunk + 3])
                          : "memory");
         fence_proxy_async_smem();               // make the generic-proxy stores visible to the tensor cores' reads
-        mbar_arrive(bars.full_w + 8 * pos.s);
+        if (PAIR) {                             // one arrival per warp, on the leader's barrier
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive_cluster((bars.full_w + 8 * pos.s) & kLeaderMask);
+        } else {
+            mbar_arrive(bars.full_w + 8 * pos.s);
+        }
         pos.advance_by(GROUPS, p.n_wstages);
     }
     return true;
 }
 
 // ---- activation loads (one thread) ----------------------------------------------------------------------------------
+template <bool PAIR = false>
 __device__ __forceinline__ bool load_activations(const GemmParams &p, uint32_t window, const GemmBars &bars, const CUtensorMap *x_map, int tok0,
                                                  int n_steps) {
     RingPos pos = {0, 1u};
     for (int it = 0; it < n_steps; ++it) {
         if (!mbar_wait(bars.empty_x + 8 * pos.s, pos.phase, p.status)) return false;
-        const uint32_t bar = bars.full_x + 8 * pos.s;
-        mbar_expect_tx(bar, kXBytes);
-        tma_load_2d(p.xa_addr[pos.s] | window, x_map, it * kStepCols, tok0, bar);
-        tma_load_2d(p.xb_addr[pos.s] | window, x_map, it * kStepCols, tok0 + 128, bar);
+        if (PAIR) {                             // bytes of both CTAs are counted on the leader's barrier
+            const uint32_t bar = (bars.full_x + 8 * pos.s) & kLeaderMask;
+            mbar_expect_tx_cluster(bar, kXBytes);
+            tma_load_2d_pair(p.xa_addr[pos.s] | window, x_map, it * kStepCols, tok0, bar);
+            tma_load_2d_pair(p.xb_addr[pos.s] | window, x_map, it * kStepCols, tok0 + 128, bar);
+        } else {
+            const uint32_t bar = bars.full_x + 8 * pos.s;
+            mbar_expect_tx(bar, kXBytes);
+            tma_load_2d(p.xa_addr[pos.s] | window, x_map, it * kStepCols, tok0, bar);
+            tma_load_2d(p.xb_addr[pos.s] | window, x_map, it * kStepCols, tok0 + 128, bar);
+        }
         pos.advance(p.n_xstages);
     }
     return true;
 }
 
-// ---- epilogue (warps 0-7): TMEM -> fp16 -> global; `tok0` this CTA's first token, `row0` the tile's first weight row ----
+// ---- epilogue (warps 0-7): TMEM -> fp16 -> shared memory -> global ----------------------------------------------------
+// `tok0` is this CTA's first token, `row0` the tile's first weight row.  The rings are free once the last MMA has been
+// committed, so the 256 x NROWS fp16 tile is laid over them as panels of 128 tokens x 64 columns in the 128-byte-swizzled
+// form a TMA store reads (a thread owns a token: its 16-byte chunks land in four-way-interleaved banks, the minimum for
+// 512 bytes per warp), and one thread sends the panels off.  Against per-thread global stores (32 different lines per
+// instruction) this cut the epilogue from 8.3 us to the time the tile takes to leave through the copy engine.
 template <int NROWS>
-__device__ __forceinline__ void drain_accumulators(const GemmParams &p, uint32_t tmem_base, int tok0, int64_t row0) {
+__device__ __forceinline__ void drain_accumulators(const GemmParams &p, uint32_t window, uint32_t tmem_base, int tok0, int64_t row0,
+                                                   const CUtensorMap *y_map, bool ok) {
+    constexpr int kPanelsPerHalf = NROWS / 64;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = warp >> 2, quarter = warp & 3;              // a warp may only touch TMEM lanes 32*(warp % 4) ...
-    const int64_t tok = (int64_t)tok0 + h * 128 + quarter * 32 + lane;
+    const uint32_t t = (uint32_t)(quarter * 32 + lane);       // token inside the half = row of the panel
+    // All eight warps come here, also one whose wait ran out (`ok` false: it skips its part, and nothing is sent).
 #pragma unroll 1
-    for (int c = 0; c < NROWS / 32; ++c) {
+    for (int c = 0; ok && c < NROWS / 32; ++c) {
         uint32_t v[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * NROWS + c * 32);
         asm volatile(
@@ -220,28 +262,47 @@ __device__ __forceinline__ void drain_accumulators(const GemmParams &p, uint32_t
               "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (tok < p.tokens) {
-            __half *dst = p.y + tok * p.ld_y + row0 + c * 32;
+        const uint32_t prow = (p.out_addr[h * kPanelsPerHalf + (c >> 1)] | window) + t * 128u;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t o[4];
+        for (int j = 0; j < 4; ++j) {
+            uint32_t o[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
-                asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 8 * j), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                             : "memory");
-            }
+            for (int e = 0; e < 4; ++e)
+                o[e] = half2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1])));
+            const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + 16u * (chunk ^ (t & 7u))), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                         : "memory");
         }
+    }
+    fence_proxy_async_smem();                                 // the stores above are read by the copy engine
+    uint32_t all_ok;                                          // barrier of the eight epilogue warps, AND of their `ok`
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "barrier.cta.red.and.pred p, 1, 256, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(all_ok)
+        : "r"((uint32_t)ok)
+        : "memory");
+    if (threadIdx.x == 0 && all_ok) {
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            if ((int64_t)tok0 + hh * 128 >= p.tokens) break;  // a half with no tokens at all (rows beyond `tokens` inside a half are clipped)
+#pragma unroll 1
+            for (int q = 0; q < kPanelsPerHalf; ++q)
+                tma_store_2d(y_map, (int)row0 + q * 64, tok0 + hh * 128, p.out_addr[hh * kPanelsPerHalf + q] | window);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // the tile has left before the CTA (and its shared memory) goes
     }
 }
 
-__device__ __forceinline__ void init_ring_barriers(const GemmParams &p, const GemmBars &bars, uint32_t producers_per_stage) {
+__device__ __forceinline__ void init_ring_barriers(const GemmParams &p, const GemmBars &bars, uint32_t w_arrivals, uint32_t x_arrivals) {
     for (int s = 0; s < kMaxGemmStages; ++s) {
-        mbar_init(bars.full_w + 8 * s, producers_per_stage);
-        mbar_init(bars.full_x + 8 * s, 1);
+        mbar_init(bars.full_w + 8 * s, w_arrivals);
+        mbar_init(bars.full_x + 8 * s, x_arrivals);
         mbar_init(bars.empty_w + 8 * s, 1);
         mbar_init(bars.empty_x + 8 * s, 1);
-        mbar_init(bars.peer + 8 * s, 1);
     }
     mbar_init(bars.accum, 1);
     mbar_init(bars.done, 1);
@@ -249,7 +310,8 @@ __device__ __forceinline__ void init_ring_barriers(const GemmParams &p, const Ge
 }
 
 template <int CODE, int K, int NROWS>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap y_map) {
     constexpr int DC = GemmDecode<CODE>::kCode;
     constexpr uint32_t kTmemCols = 2 * NROWS;  // two token halves of NROWS fp32 columns
     constexpr uint32_t kInstrDesc = instr_desc(NROWS);
@@ -266,7 +328,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     const int64_t row0 = (int64_t)blockIdx.x * NROWS;
     const int tok0 = blockIdx.y * kTileTokens;
 
-    if (tid == 0) init_ring_barriers(p, bars, 256 / kGroups);
+    if (tid == 0) init_ring_barriers(p, bars, 256 / kGroups, 1);
     if (warp == kMmaWarp) {                     // TMEM: two fp32 accumulators of NROWS columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars.tmem_slot), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -284,7 +346,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
         ok = produce_weights<CODE, K, kGroups>(p, 0u, bars, row0, n_steps);
     } else if (warp == kTmaWarp) {
         pdl_wait_prior_grids();
-        if (lane == 0) load_activations(p, 0u, bars, &x_map, tok0, n_steps);
+        if (lane == 0) load_activations<false>(p, 0u, bars, &x_map, tok0, n_steps);
     } else if (lane == 0) {
         // ================= MMA issue =================
         RingPos px = {0, 0u}, pw = {0, 0u};
@@ -310,7 +372,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
     if (warp < kProducerWarps) {
         if (ok) ok = mbar_wait(bars.accum, 0, p.status);
         tc_fence_after();
-        if (ok) drain_accumulators<NROWS>(p, tmem_base, tok0, row0);
+        drain_accumulators<NROWS>(p, 0u, tmem_base, tok0, row0, &y_map, ok);
     }
     tc_fence_before();
     __syncthreads();
@@ -328,10 +390,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmParams 
 // its own shared memory (the other half comes across from the partner) and decodes, stores and looks up half as many
 // weights per token.  A weight stage is 16 KiB instead of 32, which buys deeper rings.
 // Roles per CTA are those of the kernel above.  Only the even CTA (the leader) issues MMAs; it needs both CTAs'
-// operands, so the partner's MMA warp turns into a relay: it waits for its own step to be complete and arrives on the
-// leader's `peer` barrier across the cluster.  Stages are handed back to both CTAs' producers, and the finished
-// accumulators announced to both CTAs' epilogues, by tcgen05.commit multicast to the pair.  No TMA load is multicast:
-// each CTA loads its own activations.
+// operands, so the `full` barriers of both rings live in the leader and both CTAs signal them directly: a producer warp
+// arrives (one lane, release at cluster scope, after the warp's fences) on the leader's barrier, and the TMA loads of
+// either CTA count their bytes there (cta_group::2 form of the load).  Stages are handed back to both CTAs' producers,
+// and the finished accumulators announced to both CTAs' epilogues, by tcgen05.commit multicast to the pair.  No TMA load
+// is multicast: each CTA loads its own activations.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -387,7 +450,7 @@ constexpr uint32_t kInstrDescPair = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | (
 
 template <int CODE, int K>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-    gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+    gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap y_map) {
     constexpr int DC = GemmDecode<CODE>::kCode;
     constexpr int kHalfRows = 128;             // weight rows this CTA decodes
     constexpr int kPairRows = 256;             // weight rows of the pair's tile = accumulator columns
@@ -419,7 +482,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int64_t row0 = tile_row0 + (int64_t)rank * kHalfRows;             // first weight row this CTA decodes
     const int tok0 = blockIdx.y * (2 * kTileTokens) + (int)rank * kTileTokens;
 
-    if (tid == 0) init_ring_barriers(p, bars, kHalfRows);
+    if (tid == 0) init_ring_barriers(p, bars, 8, 2);          // four producer warps and one TMA thread per step from each CTA
     // Both CTAs of the pair must be resident, with their barriers initialised, before either touches the pair's tensor
     // memory or signals across: the paired allocation below addresses the partner SM.
     __syncthreads();
@@ -438,17 +501,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     bool ok = true;
 
     if (warp < kProducerWarps) {
-        ok = produce_weights<CODE, K, 2>(p, window, bars, row0, n_steps);      // two groups of four warps take alternate steps
+        ok = produce_weights<CODE, K, 2, true>(p, window, bars, row0, n_steps);      // two groups of four warps take alternate steps
     } else if (warp == kTmaWarp) {
         pdl_wait_prior_grids();
-        if (lane == 0) load_activations(p, window, bars, &x_map, tok0, n_steps);
+        if (lane == 0) load_activations<true>(p, window, bars, &x_map, tok0, n_steps);
     } else if (lane == 0) {
-        RingPos px = {0, 0u}, pw = {0, 0u}, pp = {0, 0u};
         if (rank == 0) {
-            // ================= leader: MMA issue for the pair =================
+            // ================= leader: MMA issue for the pair (the partner's thread has nothing to do here) =================
+            RingPos px = {0, 0u}, pw = {0, 0u};
             for (int it = 0; it < n_steps && ok; ++it) {
-                ok = mbar_wait(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait(bars.full_w + 8 * pw.s, pw.phase, p.status) &&
-                     mbar_wait_cluster(bars.peer + 8 * pp.s, pp.phase, p.status);
+                ok = mbar_wait_cluster(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait_cluster(bars.full_w + 8 * pw.s, pw.phase, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t xa = p.xa_addr[px.s], xb = p.xb_addr[px.s], wa = p.w_addr[pw.s];
@@ -462,22 +524,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 tc_commit_pair(bars.empty_w + 8 * pw.s);
                 px.advance(p.n_xstages);
                 pw.advance(p.n_wstages);
-                pp.advance(kMaxGemmStages);
             }
             if (ok) tc_commit_pair(bars.accum);              // both CTAs' epilogues start when every MMA has written its accumulator
-        } else {
-            // ================= partner: tell the leader when this CTA's step is complete =================
-            // The `peer` ring has kMaxGemmStages slots, at least as many as either data ring, so an arrival for step
-            // it + kMaxGemmStages can only happen after the leader has issued (and so waited for) step it.
-            for (int it = 0; it < n_steps && ok; ++it) {
-                ok = mbar_wait(bars.full_x + 8 * px.s, px.phase, p.status) && mbar_wait(bars.full_w + 8 * pw.s, pw.phase, p.status);
-                if (!ok) break;
-                fence_proxy_async_smem();
-                mbar_arrive_remote(bars.peer + 8 * pp.s, 0);
-                px.advance(p.n_xstages);
-                pw.advance(p.n_wstages);
-                pp.advance(kMaxGemmStages);
-            }
         }
     }
 
@@ -485,7 +533,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     if (warp < kProducerWarps) {
         if (ok) ok = mbar_wait(bars.accum, 0, p.status);
         tc_fence_after();
-        if (ok) drain_accumulators<kPairRows>(p, tmem_base, tok0, tile_row0);
+        drain_accumulators<kPairRows>(p, window, tmem_base, tok0, tile_row0, &y_map, ok);
     }
     tc_fence_before();
     __syncthreads();
@@ -515,15 +563,15 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_tiled_fn() {
 }
 
 template <int CODE, int K, int NROWS>
-static int launch_gemm(const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
+static int launch_gemm(const GemmParams &p, const CUtensorMap &map, const CUtensorMap &ymap, size_t smem, dim3 grid, cudaStream_t stream) {
     static SmemOptIn opted;
     auto kern = gemm_kernel<CODE, K, NROWS>;
     if (int e = allow_max_smem(kern, opted)) return e;
-    return launch(kern, grid, dim3(kGemmThreads), smem, stream, p, map);
+    return launch(kern, grid, dim3(kGemmThreads), smem, stream, p, map, ymap);
 }
 
 template <int CODE, int K>
-static int launch_gemm_pair(const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
+static int launch_gemm_pair(const GemmParams &p, const CUtensorMap &map, const CUtensorMap &ymap, size_t smem, dim3 grid, cudaStream_t stream) {
     static SmemOptIn opted;
     auto kern = gemm_pair_kernel<CODE, K>;
     if (int e = allow_max_smem(kern, opted)) return e;
@@ -541,19 +589,21 @@ static int launch_gemm_pair(const GemmParams &p, const CUtensorMap &map, size_t 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    RPTC_CUDA(cudaLaunchKernelEx(&cfg, kern, p, map));
+    RPTC_CUDA(cudaLaunchKernelEx(&cfg, kern, p, map, ymap));
     return RPTC_OK;
 }
 
 template <int CODE, int K>
-static int launch_gemm_rows(int n_rows, const GemmParams &p, const CUtensorMap &map, size_t smem, dim3 grid, cudaStream_t stream) {
-    return n_rows == 256 ? launch_gemm<CODE, K, 256>(p, map, smem, grid, stream) : launch_gemm<CODE, K, 128>(p, map, smem, grid, stream);
+static int launch_gemm_rows(int n_rows, const GemmParams &p, const CUtensorMap &map, const CUtensorMap &ymap, size_t smem, dim3 grid,
+                            cudaStream_t stream) {
+    return n_rows == 256 ? launch_gemm<CODE, K, 256>(p, map, ymap, smem, grid, stream) : launch_gemm<CODE, K, 128>(p, map, ymap, smem, grid, stream);
 }
 
 int check_format(const rptc_format *f);   // api.cu
 // RPTC_GEMM_PAIR=1 in the environment (read once per process) sends shapes that allow it to the two-SM kernel.  It is
-// not the default: measured on B200 it trails the one-SM kernel on every Llama-2-7B layer shape (206 us against 173 us
-// at 12288 x 4096 x 2048 tokens), the hand-over between the two SMs costing more than the halved operand traffic saves.
+// not the default: measured on B200 it trails the one-SM kernel on every Llama-2-7B layer shape (199 us against 156 us
+// at 12288 x 4096 x 2048 tokens).  Timed with the producers and the loads taken out, the pair still needs 0.85 us per
+// 64-column step (the one-SM kernel: 0.54 us), so the loss is in the paired MMA / commit path itself, not in the decode.
 static bool g_gemm_pair = false;
 
 }  // namespace rptc
@@ -593,6 +643,20 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
     if (r != CUDA_SUCCESS) {
         g_last_cuda_error = (int)r;
         return RPTC_ERR_CUDA;
+    }
+
+    // the output, [tokens][m] fp16, in boxes of 64 columns x 128 tokens (the epilogue's panels)
+    CUtensorMap ymap;
+    {
+        const cuuint64_t ydim[2] = {(cuuint64_t)m, (cuuint64_t)tokens};
+        const cuuint64_t ystride[1] = {(cuuint64_t)ld_y * 2};
+        const cuuint32_t ybox[2] = {64, 128};
+        r = encode(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, y, ydim, ystride, ybox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            g_last_cuda_error = (int)r;
+            return RPTC_ERR_CUDA;
+        }
     }
 
     GemmParams p;
@@ -638,25 +702,13 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
             }
         return 0;
     };
-    // Two SMs per tile (512 tokens x 256 rows, each CTA decoding 128 of the rows): on request, when there are tokens for both CTAs.
-    const bool pair = g_gemm_pair && tokens > kTileTokens && m % 256 == 0;
-    // Tile height of the one-SM kernel: 256 rows feed the tensor pipe about 1.35x faster per CTA-step than 128 rows, but
-    // need twice the time per CTA; with few tiles the shorter ones fill more SMs.  Compare whole waves of CTAs.
-    int n_rows = 128;
-    if (!pair && m % 256 == 0) {
-        const int64_t tt = (tokens + kTileTokens - 1) / kTileTokens, sms = num_sms();
-        const int64_t waves256 = ((m / 256) * tt + sms - 1) / sms, waves128 = ((m / 128) * tt + sms - 1) / sms;
-        if (waves256 * 148 <= waves128 * 100) n_rows = 256;          // 2 / 1.35 = 1.48
-    }
-    int xs = 0, ws = 0;
-    for (int attempt = 0; attempt < 2; ++attempt) {
-        if (attempt == 1) {              // the wide tile does not fit beside this table: fall back to 128 rows
-            if (n_rows == 128 || (xs >= 2 && ws >= 2)) break;
-            n_rows = 128;
-        }
+    // One plan: ring stages for tiles of `rows` weight rows decoded per CTA and `tile_rows` output columns per CTA, first
+    // two stages of each ring, then alternately one more of each (the activation ring, the slower to refill, first); the
+    // epilogue's panels (16 KiB each) are laid over the stages.  False when the tile does not fit beside this table.
+    auto plan = [&](int rows, int tile_rows) -> bool {
         reset_plan();
-        xs = ws = 0;
-        const uint32_t w_bytes = (uint32_t)(pair ? 128 : n_rows) * 128u;
+        int xs = 0, ws = 0;
+        const uint32_t w_bytes = (uint32_t)rows * 128u;
         auto add_x = [&]() -> bool {
             if (xs == kMaxGemmStages) return false;
             const uint32_t save0 = free_lo[0], save1 = free_lo[1];
@@ -676,42 +728,65 @@ extern "C" int rptc_gemm(const void *codes, const void *lut, const uint32_t *car
             p.w_addr[ws++] = w;
             return true;
         };
-        // two stages of each ring first, then alternately one more of each, the activation ring (the slower to refill) first
         add_w(), add_w(), add_x(), add_x();
-        for (bool grew = true; grew && xs >= 2 && ws >= 2;) {
+        if (xs < 2 || ws < 2) return false;
+        for (bool grew = true; grew;) {
             grew = add_x();
             if (ws < 3) grew = add_w() || grew;
         }
+        uint32_t pieces[3 * kMaxGemmStages * 2];
+        int np = 0;
+        for (int i = 0; i < xs; ++i) pieces[np++] = p.xa_addr[i], pieces[np++] = p.xb_addr[i];
+        for (int i = 0; i < ws; ++i)
+            for (uint32_t off = 0; off < w_bytes; off += kXHalfBytes) pieces[np++] = p.w_addr[i] + off;
+        const int need = 2 * (tile_rows / 64);
+        if (np < need) return false;
+        for (int i = 0; i < 8; ++i) p.out_addr[i] = i < need ? pieces[i] : 0;
+        for (int s = xs; s < kMaxGemmStages; ++s) p.xa_addr[s] = p.xb_addr[s] = 0;
+        for (int s = ws; s < kMaxGemmStages; ++s) p.w_addr[s] = 0;
+        p.n_xstages = xs;
+        p.n_wstages = ws;
+        return true;
+    };
+    // Two SMs per tile (512 tokens x 256 rows, each CTA decoding 128 of the rows): on request, when there are tokens for
+    // both CTAs and the tile fits beside the table.
+    const bool pair = g_gemm_pair && tokens > kTileTokens && m % 256 == 0 && plan(128, 256);
+    // Tile height of the one-SM kernel: 256 rows feed the tensor pipe about 1.35x faster per CTA-step than 128 rows, but
+    // need twice the time per CTA; with few tiles the shorter ones fill more SMs.  Compare whole waves of CTAs.
+    int n_rows = 128;
+    if (!pair) {
+        if (m % 256 == 0) {
+            const int64_t tt = (tokens + kTileTokens - 1) / kTileTokens, sms = num_sms();
+            const int64_t waves256 = ((m / 256) * tt + sms - 1) / sms, waves128 = ((m / 128) * tt + sms - 1) / sms;
+            if (waves256 * 148 <= waves128 * 100) n_rows = 256;          // 2 / 1.35 = 1.48
+        }
+        if (n_rows == 256 && !plan(256, 256)) n_rows = 128;              // the wide tile does not fit beside this table
+        if (n_rows == 128 && !plan(128, 128)) return RPTC_ERR_UNSUPPORTED;
     }
-    if (xs < 2 || ws < 2) return RPTC_ERR_UNSUPPORTED;
-    for (int s = xs; s < kMaxGemmStages; ++s) p.xa_addr[s] = p.xb_addr[s] = 0;
-    for (int s = ws; s < kMaxGemmStages; ++s) p.w_addr[s] = 0;
-    p.n_xstages = xs;
-    p.n_wstages = ws;
     const size_t smem = kTop;            // covers every planned address whatever the start of the dynamic area
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (pair) {
         const dim3 pgrid((unsigned)(2 * (m / 256)), (unsigned)((tokens + 2 * kTileTokens - 1) / (2 * kTileTokens)));
         switch (fmt->code) {
             case RPTC_CODE_LUT:
-                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LUT, 2>(p, map, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LUT, 4>(p, map, smem, pgrid, s);
+                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LUT, 2>(p, map, ymap, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LUT, 4>(p, map, ymap, smem, pgrid, s);
             case RPTC_CODE_HASH:
-                return launch_gemm_pair<RPTC_CODE_HASH, 2>(p, map, smem, pgrid, s);
+                return launch_gemm_pair<RPTC_CODE_HASH, 2>(p, map, ymap, smem, pgrid, s);
             case RPTC_CODE_LITE:
-                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LITE, 2>(p, map, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LITE, 4>(p, map, smem, pgrid, s);
+                return fmt->K == 2 ? launch_gemm_pair<RPTC_CODE_LITE, 2>(p, map, ymap, smem, pgrid, s) : launch_gemm_pair<RPTC_CODE_LITE, 4>(p, map, ymap, smem, pgrid, s);
         }
         return RPTC_ERR_UNSUPPORTED;
     }
     const dim3 grid((unsigned)(m / n_rows), (unsigned)((tokens + kTileTokens - 1) / kTileTokens));
     switch (fmt->code) {
         case RPTC_CODE_LUT:
-            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LUT, 2>(n_rows, p, map, smem, grid, s)
-                               : launch_gemm_rows<RPTC_CODE_LUT, 4>(n_rows, p, map, smem, grid, s);
+            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LUT, 2>(n_rows, p, map, ymap, smem, grid, s)
+                               : launch_gemm_rows<RPTC_CODE_LUT, 4>(n_rows, p, map, ymap, smem, grid, s);
         case RPTC_CODE_HASH:
-            return launch_gemm_rows<RPTC_CODE_HASH, 2>(n_rows, p, map, smem, grid, s);
+            return launch_gemm_rows<RPTC_CODE_HASH, 2>(n_rows, p, map, ymap, smem, grid, s);
         case RPTC_CODE_LITE:
-            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LITE, 2>(n_rows, p, map, smem, grid, s)
-                               : launch_gemm_rows<RPTC_CODE_LITE, 4>(n_rows, p, map, smem, grid, s);
+            return fmt->K == 2 ? launch_gemm_rows<RPTC_CODE_LITE, 2>(n_rows, p, map, ymap, smem, grid, s)
+                               : launch_gemm_rows<RPTC_CODE_LITE, 4>(n_rows, p, map, ymap, smem, grid, s);
     }
     return RPTC_ERR_UNSUPPORTED;
 }

@@ -176,16 +176,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * rope_inv_freq(freq, (i8 & 63) + i), &rot_sn[i], &rot_cs[i]);
     }
     if (fused) {
-        // Fused front end (one kv head per q head): this CTA finishes its own q, k and v from the fused qkv
-        // layer's accumulator -- per-head 128-wide output transform, fp16 rounding, rotary embedding -- appends
-        // k and v to the caches and keeps all three in shared memory.  Sixteen threads x eight values per vector.
+        // Fused front end: this CTA finishes its own q and the k and v of its kv head from the fused qkv layer's
+        // accumulator -- per-head 128-wide output transform, fp16 rounding, rotary embedding -- and keeps all three
+        // in shared memory.  With grouped-query attention the q heads of a group each make their own copy of k and
+        // v (a few hundred flops) and the first of them appends the pair to the caches; nobody reads that cache row
+        // in this launch.  Sixteen threads x eight values per vector.
         pdl_wait_prior_grids();
+        const bool appends = pos_ok && head % (hq / hkv) == 0;
         if (warp < 2) {
             const int grp = t >> 4, i8 = (t & 15) * 8;              // 0: q, 1: k, 2: v, 3: idle half warp
             const int col = (grp == 0 ? head : grp == 1 ? hq + kvh : hq + hkv + kvh) * D + i8;
             float v[8], sg[8];
             if (grp < 3) {
-                load8_f32(acc + (int64_t)row * ld_acc + col, v, true);
+                // multi-head: every column has one reader, who zeroes it; grouped-query: k and v have several readers
+                // and a later launch zeroes the accumulator
+                load8_f32(acc + (int64_t)row * ld_acc + col, v, hq == hkv);
                 unpack8(so_raw, sg);
             } else {
 #pragma unroll
@@ -208,10 +213,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
                 store8_f16(qs + i8, o);
             } else if (grp == 1) {
                 store8_f16(ks + i8, o);
-                if (pos_ok) store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+                if (appends) store8_f16(kcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
             } else if (grp == 2) {
                 store8_f16(vs + i8, o);
-                if (pos_ok) store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
+                if (appends) store8_f16(vcache_w + (((int64_t)row * max_pos + ps) * hkv + kvh) * D + i8, o);
             }
         }
         __syncthreads();
@@ -493,11 +498,11 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
 }
 
 extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *signs_out, float scale_out, const int32_t *pos,
-                                    void *kcache, void *vcache, void *out, int64_t ld_out, int64_t rows, int heads, int max_pos,
-                                    float theta, const void *signs_in, rptc_stream_t stream) {
+                                    void *kcache, void *vcache, void *out, int64_t ld_out, int64_t rows, int heads, int kv_heads,
+                                    int max_pos, float theta, const void *signs_in, rptc_stream_t stream) {
     if (!acc || !pos || !kcache || !vcache || !out) return RPTC_ERR_ARG;
-    if (rows <= 0 || rows > 65535 || heads <= 0 || max_pos <= 0 || max_pos > 32768 || ld_acc < (int64_t)3 * heads * 128 ||
-        ld_out < (int64_t)heads * 128)
+    if (rows <= 0 || rows > 65535 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_pos <= 0 || max_pos > 32768 ||
+        ld_acc < (int64_t)(heads + 2 * kv_heads) * 128 || ld_out < (int64_t)heads * 128)
         return RPTC_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
         (signs_out && (reinterpret_cast<uintptr_t>(signs_out) & 15)) || (ld_acc % 4))
@@ -507,7 +512,7 @@ extern "C" int rptc_qkv_attn_decode(float *acc, int64_t ld_acc, const void *sign
     if (!status) return RPTC_ERR_CUDA;
     return launch(attn_decode_kernel, dim3((unsigned)heads, (unsigned)rows), dim3(kAttnThreads), 0, static_cast<cudaStream_t>(stream),
                   static_cast<const __half *>(nullptr), (int64_t)0, pos, static_cast<const __half *>(kcache),
-                  static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, heads, max_pos, 0.08838834764831845f,
+                  static_cast<const __half *>(vcache), static_cast<__half *>(out), ld_out, heads, kv_heads, max_pos, 0.08838834764831845f,
                   static_cast<const __half *>(signs_in), acc, ld_acc, static_cast<const __half *>(signs_out), scale_out, rope_freq(theta, 128),
                   static_cast<__half *>(kcache), static_cast<__half *>(vcache), status);
 }

@@ -113,7 +113,7 @@ _SIGS = {
                                         ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]),
     "rptc_qkv_attn_decode": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p,
                                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
-                                            ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]),
+                                            ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]),
     "rptc_finish_norm_hadamard": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p,
                                                  ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int,
                                                  ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),

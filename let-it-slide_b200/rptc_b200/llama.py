@@ -57,8 +57,8 @@ class Block:
         q, kv, ffn = cfg.heads * cfg.head_dim // tp, cfg.kv_heads * cfg.head_dim // tp, cfg.ffn // tp
         mk = lambda i, o, s: RPTCLinear.random(i, o, fmt, cfg.weight_scale, seed * 16 + s, device, incoherent)
         self.qkv = mk(cfg.hidden, q + 2 * kv, 0)
-        # per-head output transform when attention is multi-head: lets one kernel finish q, k, v of a head and attend
-        self.qkv.block_out = cfg.head_dim if (cfg.heads == cfg.kv_heads and cfg.head_dim == 128) else hadamard_block(math.gcd(q, kv))
+        # per-head output transform: lets one kernel finish q, k, v of a head and attend
+        self.qkv.block_out = cfg.head_dim if cfg.head_dim == 128 else hadamard_block(math.gcd(q, kv))
         self.o = mk(q, cfg.hidden, 1)
         self.o.block_in = min(self.o.block_in, cfg.head_dim)      # one Hadamard block per head: fuses into the attention kernel
         self.gate_up = mk(cfg.hidden, 2 * ffn, 2)
@@ -111,8 +111,11 @@ class RPTCLlama:
         self.logits = torch.zeros((rows, cfg.vocab), **f16)
         self.next_ids = torch.zeros(rows, dtype=torch.int64, device=device)
         f32 = dict(dtype=torch.float32, device=device)
-        self.acc_qkv = torch.zeros((rows, q + 2 * kv), **f32)
-        self.acc_h = torch.zeros((rows, cfg.hidden), **f32)
+        # acc_qkv and acc_h share one allocation: with grouped-query attention the fused attention kernel cannot zero the
+        # k and v columns it reads (several q heads read them), so the launch that zeroes acc_h zeroes acc_qkv with it
+        self._acc_pool2 = torch.zeros(rows * (q + 2 * kv + cfg.hidden), **f32)
+        self.acc_qkv = self._acc_pool2[: rows * (q + 2 * kv)].view(rows, q + 2 * kv)
+        self.acc_h = self._acc_pool2[rows * (q + 2 * kv):].view(rows, cfg.hidden)
         # second residual stream and accumulator of the shortest chain, whose matvecs compute their own inputs; the
         # accumulators that a later launch zeroes (acc_o, acc_gu) share one allocation so that one range covers both
         self.h2 = torch.zeros((rows, cfg.hidden), **f16)
@@ -129,6 +132,7 @@ class RPTCLlama:
         self.fused_tp = True        # False: the 15-launch chain under tensor parallelism
         self.glued_mlp = True       # False: SwiGLU in a launch of its own inside the short chain
         self.glued_tp = True        # False: RMSNorm + input transform of the tensor-parallel chain in launches of their own
+        self.fuse_attention = True  # False: q/k/v finish + RoPE + KV append in a launch of their own, in front of attention
         self.host_ids: torch.Tensor | None = None      # see bind_host_io
         self.host_next: torch.Tensor | None = None
         self.mailbox = None                            # see bind_mailbox
@@ -207,9 +211,9 @@ class RPTCLlama:
                      and self.fmt.K in (2, 4))
         for i, b in enumerate(self.blocks):
             b.qkv.matvec_acc(xt, self.acc_qkv)
-            if self.heads_l == self.kv_heads_l and b.qkv.block_out == 128:
+            if self.fuse_attention and self.heads_l == self.kv_heads_l and b.qkv.block_out == 128:
                 ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
-                                    self.heads_l, cfg.rope_theta, b.o.signs_in)
+                                    self.heads_l, self.kv_heads_l, cfg.rope_theta, b.o.signs_in)
                 n_launch -= 1
             else:
                 ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
@@ -252,7 +256,8 @@ class RPTCLlama:
         cfg, r = self.cfg, self.rows
         self._embed_ids()
         mlp_glued = self._mlp_glueable()
-        mha = self.heads_l == self.kv_heads_l and self.blocks[0].qkv.block_out == 128
+        mha = self.fuse_attention and self.blocks[0].qkv.block_out == 128 and cfg.head_dim == 128
+        gqa = self.heads_l != self.kv_heads_l
         # the launch that opens a block zeroes what the block before it left: acc_o always, acc_gu too when the down
         # projection reads it in every CTA
         stale = self._acc_pool if mlp_glued else self.acc_o
@@ -263,16 +268,18 @@ class RPTCLlama:
                                 self.h, self.h2, b.norm1, cfg.rms_eps, b.qkv.signs_in, clear=stale)
             if mha:
                 ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
-                                    self.heads_l, cfg.rope_theta, b.o.signs_in)
+                                    self.heads_l, self.kv_heads_l, cfg.rope_theta, b.o.signs_in)
             else:
                 ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
                                self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
                 ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
                                 cfg.head_dim, signs_in=b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_o)
+            # acc_h was consumed by this block's first launch; with grouped-query attention acc_qkv is zeroed here too
+            stale_h = self._acc_pool2 if (mha and gqa) else (self.acc_h if i else None)
             ops.gemv_norm_input(b.gate_up.codes, b.gate_up.lut, self.acc_gu, b.gate_up.out_features, cfg.hidden, self.fmt, r,
                                 self.acc_o, b.o.signs_out, b.o.scale, self.h2, self.h, b.norm2, cfg.rms_eps, b.gate_up.signs_in,
-                                clear=self.acc_h if i else None)
+                                clear=stale_h)
             if mlp_glued:
                 ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, r, self.acc_gu,
                                       b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in,
@@ -301,9 +308,9 @@ class RPTCLlama:
         # RMSNorm + input transform inside the matvec that consumes them (the all-reduce has already updated h)
         norm_glued = self.glued_tp and native and cfg.hidden in (4096, 8192)
 
-        def normed_matvec(lin, w_norm, acc):
+        def normed_matvec(lin, w_norm, acc, clear=None):
             ops.gemv_norm_input(lin.codes, lin.lut, acc, lin.out_features, cfg.hidden, self.fmt, self.rows, None, None, 1.0,
-                                self.h, self.h2, w_norm, cfg.rms_eps, lin.signs_in, carry_in=lin.carry_in)
+                                self.h, self.h2, w_norm, cfg.rms_eps, lin.signs_in, clear=clear, carry_in=lin.carry_in)
 
         if norm_glued:
             return self._step_fused_tp_glued(normed_matvec, mlp_glued, per_reduce)
@@ -342,25 +349,32 @@ class RPTCLlama:
         self.launches_per_step = ((8 if mlp_glued else 9) + 2 * per_reduce) * len(self.blocks) + 4 + self._extra_launches()
 
     def _step_fused_tp_glued(self, normed_matvec, mlp_glued: bool, per_reduce: int) -> None:
-        """The tensor-parallel chain with the norms inside the matvecs: qkv* -> q/k/v finish -> attention -> o ->
-        all-reduce -> gate-up* -> down (SwiGLU inside or in front) -> all-reduce."""
+        """The tensor-parallel chain with the norms inside the matvecs: qkv* -> attention (q/k/v finish inside or in
+        front) -> o -> all-reduce -> gate-up* -> down (SwiGLU inside or in front) -> all-reduce."""
         cfg = self.cfg
+        fused_attn = self.fuse_attention and self.blocks[0].qkv.block_out == 128 and cfg.head_dim == 128
+        # grouped-query attention: the fused attention kernel leaves acc_qkv as it is and the gate-up launch zeroes it
+        stale_qkv = self.acc_qkv if (fused_attn and self.heads_l != self.kv_heads_l) else None
         for i, b in enumerate(self.blocks):
             normed_matvec(b.qkv, b.norm1, self.acc_qkv)
-            ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
-                           self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
-            ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
-                            cfg.head_dim, signs_in=b.o.signs_in)
+            if fused_attn:
+                ops.qkv_attn_decode(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.pos, self.kcache[i], self.vcache[i], self.attn,
+                                    self.heads_l, self.kv_heads_l, cfg.rope_theta, b.o.signs_in)
+            else:
+                ops.qkv_finish(self.acc_qkv, b.qkv.signs_out, b.qkv.scale, self.qkv_out, self.kcache[i], self.vcache[i], self.pos,
+                               self.heads_l, self.kv_heads_l, b.qkv.block_out, cfg.rope_theta)
+                ops.attn_decode(self.qkv_out, self.pos, self.kcache[i], self.vcache[i], self.attn, self.heads_l, self.kv_heads_l,
+                                cfg.head_dim, signs_in=b.o.signs_in)
             b.o.matvec_acc(self.attn, self.acc_h)
             self._finish_row_parallel(b.o)
             if mlp_glued:
                 gu, other = (self.acc_gu, self.acc_gu2) if i % 2 == 0 else (self.acc_gu2, self.acc_gu)
-                normed_matvec(b.gate_up, b.norm2, gu)
+                normed_matvec(b.gate_up, b.norm2, gu, clear=stale_qkv)
                 ops.gemv_swiglu_input(b.down.codes, b.down.lut, self.acc_h, cfg.hidden, self.ffn_l, self.fmt, self.rows, gu,
                                       b.gate_up.signs_out, b.gate_up.scale, b.down.signs_in, b.down.block_in, clear=other,
                                       carry_in=b.down.carry_in)
             else:
-                normed_matvec(b.gate_up, b.norm2, self.acc_gu)
+                normed_matvec(b.gate_up, b.norm2, self.acc_gu, clear=stale_qkv)
                 ops.swiglu_hadamard(self.acc_gu, self.mlp, b.gate_up.signs_out, b.down.signs_in, self.ffn_l, b.down.block_in,
                                     b.gate_up.scale, 1.0, clear=True)
                 b.down.matvec_acc(self.mlp, self.acc_h)
@@ -368,7 +382,7 @@ class RPTCLlama:
         ops.finish_norm_hadamard(None, None, 1.0, self.h, self.norm_f, cfg.rms_eps, None, False, self.xn)
         ops.dense_gemv(self.head, self.xn, out=self.logits)
         self._next_token()
-        self.launches_per_step = ((6 if mlp_glued else 7) + 2 * per_reduce) * len(self.blocks) + 4
+        self.launches_per_step = ((6 if mlp_glued else 7) - (1 if fused_attn else 0) + 2 * per_reduce) * len(self.blocks) + 4
 
     def _step_unfused(self) -> None:
         cfg, r = self.cfg, self.rows

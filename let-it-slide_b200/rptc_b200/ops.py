@@ -248,13 +248,14 @@ def attn_decode(qkv: torch.Tensor, pos: torch.Tensor, kcache: torch.Tensor, vcac
 
 
 def qkv_attn_decode(acc: torch.Tensor, signs_out: torch.Tensor | None, scale_out: float, pos: torch.Tensor, kcache: torch.Tensor,
-                    vcache: torch.Tensor, out: torch.Tensor, heads: int, theta: float, signs_in: torch.Tensor | None) -> torch.Tensor:
+                    vcache: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, theta: float,
+                    signs_in: torch.Tensor | None) -> torch.Tensor:
     """Output transform of the fused qkv layer + RoPE + KV append + attention (+ per-head input transform of the
-    output projection) in one launch; multi-head attention only (rptc_qkv_attn_decode)."""
+    output projection) in one launch (rptc_qkv_attn_decode)."""
     rows = acc.shape[0]
     with torch.cuda.device(acc.device):
         check(lib().rptc_qkv_attn_decode(ptr(acc), _ld(acc, acc.shape[1]), ptr(signs_out), scale_out, ptr(pos), ptr(kcache),
-                                         ptr(vcache), ptr(out), _ld(out, out.shape[1]), rows, heads, kcache.shape[1], theta,
+                                         ptr(vcache), ptr(out), _ld(out, out.shape[1]), rows, heads, kv_heads, kcache.shape[1], theta,
                                          ptr(signs_in), stream_ptr()), "rptc_qkv_attn_decode")
     return out
 

@@ -117,3 +117,18 @@ def test_linear_prefill_path_matches_effective_weight():
     y = lin(x).float()
     ref = x.float() @ lin.effective_weight().t()
     assert (y - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
+def test_two_sm_kernel_passes_the_identity_cases():
+    """The cta_group::2 kernel is chosen per process (RPTC_GEMM_PAIR=1 in the environment, read at the first call), so the
+    bit-exact identity cases above run once more in a child process with it switched on (identity activations are 4096 or
+    more tokens: every shape with m % 256 == 0 takes the two-SM kernel there)."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("RPTC_GEMM_PAIR") == "1":
+        pytest.skip("already inside the child process")
+    env = dict(os.environ, RPTC_GEMM_PAIR="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-k", "identity or llama_shapes"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

@@ -87,13 +87,19 @@ def test_short_chains_match_reference_and_separate_glue(rows, hidden, kv_heads):
     T = 6
     model = RPTCLlama(cfg, rows=rows, seed=3)
     assert model._glueable() and model._mlp_glueable()
-    gqa = 0 if kv_heads == hidden // 128 else 1           # grouped-query attention keeps the q/k/v finish in a launch of its own
+    gqa = 0 if kv_heads == hidden // 128 else 1
     g = torch.Generator(device="cuda").manual_seed(5)
     tokens = torch.randint(0, cfg.vocab, (rows, T), device="cuda", generator=g)
     ref = model.reference_logits(tokens)
     logits = {}
-    for launches, glued, glued_mlp in ((8 + gqa, False, False), (7 + gqa, False, True), (6 + gqa, True, False), (5 + gqa, True, True)):
-        model.glued, model.glued_mlp = glued, glued_mlp
+    # (launches per block, glue inside the matvecs, SwiGLU inside the down projection, q/k/v finish inside attention).
+    # The chains with the glue in launches of their own fuse the attention front end for multi-head attention only;
+    # the glued chains fuse it for grouped-query attention too (a later launch zeroes the qkv accumulator).
+    variants = [(8 + gqa, False, False, True), (7 + gqa, False, True, True), (6, True, False, True), (5, True, True, True),
+                (6, True, True, False)]
+    for launches, glued, glued_mlp, fuse_attention in variants:
+        model.glued, model.glued_mlp, model.fuse_attention = glued, glued_mlp, fuse_attention
+        key = (launches, glued, glued_mlp, fuse_attention)
         for use_graph in (False, True):
             model.reset()
             model.graph = None
@@ -106,20 +112,21 @@ def test_short_chains_match_reference_and_separate_glue(rows, hidden, kv_heads):
                 got = model.logits.float()
                 err = (got - ref[:, t]).abs().max().item()
                 # 4096-long dot products of fp16 activations: twice the slack of the small models above
-                assert err <= 2e-2 * ref[:, t].abs().max().item(), (launches, use_graph, t, err)
-                logits[launches, use_graph, t] = got.clone()
-            assert model.launches_per_step == launches * cfg.layers + 4
+                assert err <= 2e-2 * ref[:, t].abs().max().item(), (key, use_graph, t, err)
+                logits[key, use_graph, t] = got.clone()
+            assert model.launches_per_step == launches * cfg.layers + 4, key
             # the accumulators with an owner are handed back zeroed, whichever launch did the clearing
             model.graph = None
             ops.embed(model.embed, model.ids, model.h)        # any launch after the step: orders the check below
             torch.cuda.synchronize()
-            assert not model.acc_qkv.any() and not model.acc_h.any()
+            assert not model.acc_qkv.any() and not model.acc_h.any(), key
             assert glued_mlp or not model.acc_gu.any()        # otherwise left to the next token's first launch
+    model.fuse_attention = True
     for t in range(T):
         scale = ref[:, t].abs().max().item()
-        for launches in (7 + gqa, 6 + gqa, 5 + gqa):
+        for key in variants[1:]:
             # two fp16 pipelines whose partial sums meet in different orders (and, at two rows, in different kernels)
-            assert (logits[launches, True, t] - logits[8 + gqa, True, t]).abs().max().item() <= 1e-2 * scale
+            assert (logits[key, True, t] - logits[variants[0], True, t]).abs().max().item() <= 1e-2 * scale
 
 
 def test_next_token_kernel_matches_argmax():
@@ -270,9 +277,11 @@ def test_a_step_beyond_the_cache_is_refused_on_the_host_and_skipped_on_the_devic
     caches stays untouched.  Nothing faults: the access is skipped, not attempted."""
     from rptc_b200 import RPTCError, ops
     from rptc_b200.llama import LlamaConfig, RPTCLlama
-    for kv_heads in (4, 2):                                   # fused q/k/v finish + attention, and the separate kernels
+    # fused q/k/v finish + attention (multi-head and grouped-query), and the separate kernels
+    for kv_heads, fuse_attention in ((4, True), (2, True), (2, False)):
         cfg = LlamaConfig(hidden=512, layers=2, heads=4, kv_heads=kv_heads, ffn=1024, vocab=512, max_pos=8, weight_scale=0.05)
         model = RPTCLlama(cfg, rows=1, seed=2)
+        model.fuse_attention = fuse_attention
         # caches re-seated inside larger buffers whose tails are the guard regions
         guards = []
         for name in ("kcache", "vcache"):
