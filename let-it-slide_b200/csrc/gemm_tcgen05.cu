@@ -437,12 +437,11 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {      // arrives o
         : "memory");
 }
 __device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    const uint32_t z = 0u;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // fp32 accumulate, fp16 A and B, both K-major, M = 256 (two CTAs), N = 256
@@ -603,7 +602,8 @@ int check_format(const rptc_format *f);   // api.cu
 // RPTC_GEMM_PAIR=1 in the environment (read once per process) sends shapes that allow it to the two-SM kernel.  It is
 // not the default: measured on B200 it trails the one-SM kernel on every Llama-2-7B layer shape (199 us against 156 us
 // at 12288 x 4096 x 2048 tokens).  Timed with the producers and the loads taken out, the pair still needs 0.85 us per
-// 64-column step (the one-SM kernel: 0.54 us), so the loss is in the paired MMA / commit path itself, not in the decode.
+// 64-column step (the one-SM kernel: 0.54 us), so the loss is in the paired MMA path itself, not in the decode; one
+// commit per step instead of two, polling waits and direct signalling of the leader's barriers each changed nothing.
 static bool g_gemm_pair = false;
 
 }  // namespace rptc
