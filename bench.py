@@ -43,10 +43,11 @@ METRIC = "2-bit Llama-2-7B-shape decode tok/s (bs1); dequant-GEMV GB/s vs HBM pe
 # DRAM bytes per launch over algorithmic bytes per launch of the fused GEMV, from one ncu capture of an 8192 x 8192 layer
 # (16.86 MB read for 16.78 MB of packed codes + 32 KB of x and y); the traffic is proportional to the packed bytes.
 GEMV_TRAFFIC_RATIO = 1.003
-# ncu counters of the fused kernels on one 8192 x 8192 (GEMV) and one 12288 x 4096 x 2048 (GEMM) launch; they explain the
-# roofline fractions and are not re-measured by this script (a profiler cannot run inside a timed region).
-NCU_GEMV = {"inst_per_unit": 249.5, "issue_active": 0.629}
-NCU_GEMM = {"tensor_active": 0.548}
+# ncu counters of the fused kernels on one 8192 x 8192 (GEMV: warp instructions per 128-bit unit of a 32-row block, issue
+# slots used; 178 and 0.676 in the steady state of a 28672 x 8192 launch) and one 12288 x 4096 x 2048 (GEMM) launch; they
+# explain the roofline fractions and are not re-measured by this script (a profiler cannot run inside a timed region).
+NCU_GEMV = {"inst_per_unit": 197.0, "issue_active": 0.593, "inst_per_unit_steady": 178.0, "issue_active_steady": 0.676}
+NCU_GEMM = {"tensor_active": 0.684}
 
 
 def measured_peaks() -> dict:
@@ -286,12 +287,16 @@ def gemv_roofline(torch, linears, kernel: str, sampler=None, reps: int = 5) -> d
 
 def issue_bound(roof: dict, sm_mhz: float | None, sms: int = 148) -> None:
     """What the instruction stream permits: SMs x 4 warp instructions per clock x clock / instructions per 128-bit unit of
-    32 rows x 512 bytes per unit (2048 weights at 2 bits).  Counters from the ncu capture named above."""
+    32 rows x 512 bytes per unit (2048 weights at 2 bits): at every issue slot used (`issue_bound_gbs`), at the measured
+    utilisation (`issue_bound_gbs_at_measured_utilisation`), and for the 136 instructions per unit that the code's
+    definition demands (32 lookups, 32 hashes, 32 address splices, 32 window shifts, 8 tensor-core instructions).
+    Counters from the ncu captures named above."""
     f = (sm_mhz or 1965.0) * 1e6
     roof["inst_per_unit"] = NCU_GEMV["inst_per_unit"]
     roof["issue_active"] = NCU_GEMV["issue_active"]
     roof["issue_bound_gbs"] = sms * 4 * f / NCU_GEMV["inst_per_unit"] * 512 / 1e9
-    roof["issue_bound_gbs_essential_152_inst"] = sms * 4 * f / 152.0 * 512 / 1e9
+    roof["issue_bound_gbs_at_measured_utilisation"] = sms * 4 * f * NCU_GEMV["issue_active_steady"] / NCU_GEMV["inst_per_unit_steady"] * 512 / 1e9
+    roof["issue_bound_gbs_essential_136_inst"] = sms * 4 * f / 136.0 * 512 / 1e9
 
 
 LLAMA7B_LAYERS = [("q/k/v/o", 4096, 4096), ("gate/up", 11008, 4096), ("down", 4096, 11008), ("qkv fused", 12288, 4096),
