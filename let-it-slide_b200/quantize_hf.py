@@ -249,6 +249,33 @@ def packed_checkpoint(model: nn.Module) -> dict:
     return {"format": "rptc-factorized-v1", "layers": layers, "state": model.state_dict()}
 
 
+def save_packed_safetensors(model: nn.Module, path) -> None:
+    """The packed checkpoint as one safetensors file: the state dict's tensors, with the layer shapes that
+    `load_packed_checkpoint` needs as JSON in the file's metadata."""
+    import json
+
+    from safetensors.torch import save_file
+    ckpt = packed_checkpoint(model)
+    tensors = {k: v.detach().cpu().contiguous() for k, v in ckpt["state"].items()}
+    save_file(tensors, str(path), metadata={"format": ckpt["format"], "layers": json.dumps(ckpt["layers"])})
+
+
+def load_packed_safetensors(model: nn.Module, path, device="cuda") -> nn.Module:
+    """Reads a file written by `save_packed_safetensors` into `model` (built from its config, weights irrelevant)."""
+    import json
+
+    from safetensors import safe_open
+    state = {}
+    with safe_open(str(path), framework="pt", device="cpu") as f:
+        meta = f.metadata() or {}
+        for k in f.keys():
+            state[k] = f.get_tensor(k)
+    if meta.get("format") != "rptc-factorized-v1":
+        raise ValueError("not a packed RPTC checkpoint")
+    layers = {name: tuple(v) for name, v in json.loads(meta["layers"]).items()}
+    return load_packed_checkpoint(model, {"format": meta["format"], "layers": layers, "state": state}, device=device)
+
+
 def load_packed_checkpoint(model: nn.Module, ckpt: dict, device="cuda") -> nn.Module:
     """Swaps empty packed layers into `model` (built from its config, weights irrelevant) and loads the state."""
     if ckpt.get("format") != "rptc-factorized-v1":

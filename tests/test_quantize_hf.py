@@ -111,6 +111,36 @@ def test_packed_layer_geometry_for_llama2_7b_gate_proj_needs_no_gpu():
         q.FactorizedRPTCLinear(11008, 4096, 16, 33, device="cpu")
 
 
+def test_packed_checkpoint_as_safetensors_needs_no_gpu(tmp_path):
+    """Packed layers inside an ordinary module survive a safetensors round trip bit for bit (shapes travel as metadata)."""
+    pytest.importorskip("safetensors")
+    import quantize_hf as q
+
+    def build():
+        net = torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.Linear(64, 128, bias=False))
+        q.swap_module(net, "0", q.FactorizedRPTCLinear(64, 64, 8, 2, True, device="cpu"))
+        return net
+
+    g = torch.Generator().manual_seed(3)
+    src = build()
+    for name, t in src.state_dict().items():
+        if t.dtype in (torch.int32, torch.int64):
+            t.copy_(torch.randint(-2**31, 2**31 - 1, t.shape, generator=g, dtype=torch.int64).to(t.dtype))
+        elif t.is_floating_point():
+            t.copy_(torch.randn(t.shape, generator=g).to(t.dtype))
+    path = tmp_path / "packed.safetensors"
+    q.save_packed_safetensors(src, path)
+    dst = torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.Linear(64, 128, bias=False))       # no packed layer yet
+    q.load_packed_safetensors(dst, path, device="cpu")
+    assert isinstance(dst[0], q.FactorizedRPTCLinear)
+    for k, v in src.state_dict().items():
+        assert torch.equal(dst.state_dict()[k], v), k
+    with pytest.raises(ValueError):
+        from safetensors.torch import save_file
+        save_file({"w": torch.zeros(2)}, str(tmp_path / "other.safetensors"))
+        q.load_packed_safetensors(dst, tmp_path / "other.safetensors", device="cpu")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("tokens", [1, 12])
 def test_packed_layer_with_banks_that_are_not_whole_row_blocks(tokens):
