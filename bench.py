@@ -542,7 +542,7 @@ def allreduce_us(torch, dist, model, world: int, reps: int = 3) -> float | None:
     return float(t.item()) / n * 1e6
 
 
-def kernel_timeline(torch, model, steps: int = 4) -> dict:
+def kernel_timeline(torch, model, steps: int = 4, dist=None) -> dict:
     """Where a decode step's time goes, kernel by kernel: the captured step is replayed under torch.profiler (CUPTI kernel
     records) and every kernel is charged the time between the end of the kernel before it and its own end -- the chain is
     serial, so these add up to the step.  Diagnostic only (`--timeline`): run after the timed legs, never inside them."""
@@ -555,10 +555,17 @@ def kernel_timeline(torch, model, steps: int = 4) -> dict:
         model.capture(pdl=True)
     torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        if dist is not None:
+            # the profiler starts up seconds apart on different ranks, longer than the all-reduce kernel waits for a peer
+            dist.barrier()
+            torch.cuda.synchronize()
         for _ in range(steps):
             model.step()
         torch.cuda.synchronize()
-    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start]
+    from rptc_b200 import ops
+    ops.device_status()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start
+          and "nccl" not in e.name.lower()]
     ev.sort(key=lambda e: e.time_range.start)
     own, crit, cnt = collections.defaultdict(float), collections.defaultdict(float), collections.Counter()
     last_end = None
@@ -603,7 +610,7 @@ def tp_record(args, torch, dist, world, rank, sampler, allreduce: str, rows: int
     if args.timeline:
         if world > 1:
             dist.barrier()
-        rec["timeline"] = kernel_timeline(torch, model)
+        rec["timeline"] = kernel_timeline(torch, model, dist=dist if world > 1 else None)
     close_model(torch, dist, model, world)
     del model
     torch.cuda.empty_cache()
@@ -643,7 +650,7 @@ def run_ours(args, cfg_kw: dict, cfg_dims: dict) -> None:
     if args.timeline and (tp or rank == 0):          # tensor parallel: every rank must run the steps
         if tp and world > 1:
             dist.barrier()
-        tl = kernel_timeline(torch, model)
+        tl = kernel_timeline(torch, model, dist=dist if (tp and world > 1) else None)
         if rank == 0:
             out["timeline"] = tl
     launches_per_step = model.launches_per_step
