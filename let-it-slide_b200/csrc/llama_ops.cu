@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     __shared__ float pm[kAttnWarps], pl[kAttnWarps];
     __shared__ float tr[128];
     __shared__ __align__(16) __half qs[128], ks[128], vs[128];
+    __shared__ float rot[2][64];                                 // cosines and sines of the new position's 64 rotary angles
     pdl_allow_next_grid();
     constexpr int D = 128;
     const bool fused = acc != nullptr;
@@ -164,16 +165,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     }
     uint2 qraw = make_uint2(0u, 0u);
     if (!fused) qraw = ld_ordered_u64(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 4 * lane);
-    // rotary angles of the new position: they depend on the position only, so they are ready before the wait
-    float rot_cs[8], rot_sn[8];
+    // Rotary angles of the new position: they depend on the position only, so they are made before the wait, one angle
+    // per thread (an accurate sincosf is a hundred instructions; eight in a row in the sixteen front-end threads cost
+    // 1.8 us) and handed over through shared memory.
     uint4 so_raw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
     const float si_mine = (signs_in && t < D) ? __half2float(signs_in[head * D + t]) : 1.f;      // constants: fetched early
     if (fused && warp < 2) {
         const int i8 = (t & 15) * 8;
         const int grp0 = t >> 4;
         if (signs_out && grp0 < 3) so_raw = *reinterpret_cast<const uint4 *>(signs_out + (grp0 == 0 ? head : grp0 == 1 ? hq + kvh : hq + hkv + kvh) * D + i8);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sincosf((ctx - 1) * rope_inv_freq(freq, (i8 & 63) + i), &rot_sn[i], &rot_cs[i]);
+    }
+    if (fused && t >= 64 && t < 128) {                           // warps 2 and 3: warps 0 and 1 have the loads above
+        float sn, cs;
+        sincosf((ctx - 1) * rope_inv_freq(freq, t - 64), &sn, &cs);
+        rot[0][t - 64] = cs;
+        rot[1][t - 64] = sn;
     }
     if (fused) {
         // Fused front end: this CTA finishes its own q and the k and v of its kv head from the fused qkv layer's
@@ -182,6 +188,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         // v (a few hundred flops) and the first of them appends the pair to the caches; nobody reads that cache row
         // in this launch.  Sixteen threads x eight values per vector.
         pdl_wait_prior_grids();
+        __syncthreads();                                            // the angles are in shared memory
         const bool appends = pos_ok && head % (hq / hkv) == 0;
         if (warp < 2) {
             const int grp = t >> 4, i8 = (t & 15) * 8;              // 0: q, 1: k, 2: v, 3: idle half warp
@@ -206,7 +213,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float partner = __shfl_xor_sync(0xFFFFFFFFu, v[i], 8);
-                const float sn = rot_sn[i], cs = rot_cs[i];
+                const float sn = rot[1][(i8 & 63) + i], cs = rot[0][(i8 & 63) + i];
                 o[i] = grp == 2 ? v[i] : (upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn);
             }
             if (grp == 0) {
