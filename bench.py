@@ -47,7 +47,7 @@ GEMV_TRAFFIC_RATIO = 1.003
 # slots used; 178 and 0.676 in the steady state of a 28672 x 8192 launch) and one 12288 x 4096 x 2048 (GEMM) launch; they
 # explain the roofline fractions and are not re-measured by this script (a profiler cannot run inside a timed region).
 NCU_GEMV = {"inst_per_unit": 197.0, "issue_active": 0.593, "inst_per_unit_steady": 178.0, "issue_active_steady": 0.676}
-NCU_GEMM = {"tensor_active": 0.684}
+NCU_GEMM = {"tensor_active": 0.771}
 
 
 def measured_peaks() -> dict:
