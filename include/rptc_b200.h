@@ -220,6 +220,7 @@ int rptc_rope_cache(void *qkv, int64_t ld_qkv, const int32_t *pos, void *kcache,
 int rptc_rope_cache_prompt(void *qkv, int64_t ld_qkv, int64_t rows, int64_t tokens, void *kcache, void *vcache, int hq, int hkv,
                            int d, int max_pos, float theta, rptc_stream_t stream);
 /* Single-query attention of each row's q heads over cache positions [0, pos[row]]; d must be 128.
+ * qkv, kcache and vcache must be 16-byte aligned and ld_qkv a multiple of 8 (rows are read 16 bytes at a time).
  * signs_in (fp16 [hq*128] or NULL): when given, each head's output is also put through the input-side
  * transform of the output projection with one 128-wide Hadamard block per head, H(s * o) / sqrt(128). */
 int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *pos, const void *kcache, const void *vcache, void *out,

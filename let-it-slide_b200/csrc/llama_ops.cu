@@ -124,7 +124,9 @@ __global__ void __launch_bounds__(256) rope_cache_prompt_kernel(__half *__restri
 // interleaved over the 16 warps) before anything that depends on the kernel in front, then keeps a running
 // maximum / sum / weighted V sum of its own (online softmax); the 16 partial states meet in shared memory.
 // Contexts beyond 256 take further chunks of 256 positions through the same registers.
-constexpr int kAttnThreads = 512, kAttnWarps = 16, kAttnUnroll = 16;     // 256 positions in flight
+// A warp takes two positions at a time, one per half-warp: lane (half, dl) holds dims 8*dl .. 8*dl+7 of its half's
+// position (one 16-byte load per row and lane, four shuffle stages per pair of scores).
+constexpr int kAttnThreads = 512, kAttnWarps = 16, kAttnUnroll = 8;      // 8 slots x 2 positions x 16 warps = 256 positions in flight
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half *__restrict__ qkv, int64_t ld_qkv,
                                                                   const int32_t *__restrict__ pos, const __half *__restrict__ kcache,
                                                                   const __half *__restrict__ vcache, __half *__restrict__ out,
@@ -154,17 +156,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     const int ctx = min(max(pos_raw, 0), max_pos - 1) + 1;
     const int n_old = fused ? ctx - 1 : ctx;                     // rows to read from the cache
     const int64_t stride = (int64_t)hkv * D;
-    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
-    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 4 * lane;
-    uint2 kk[kAttnUnroll], vv[kAttnUnroll];
+    const int half = lane >> 4, dl = lane & 15;
+    const __half *kb = kcache + ((int64_t)row * max_pos * hkv + kvh) * D + 8 * dl;
+    const __half *vb = vcache + ((int64_t)row * max_pos * hkv + kvh) * D + 8 * dl;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    uint4 kk[kAttnUnroll], vv[kAttnUnroll];
 #pragma unroll
     for (int u = 0; u < kAttnUnroll; ++u) {
-        const int j = warp + u * kAttnWarps;
-        kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
-        vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
+        const int j = 2 * (warp + u * kAttnWarps) + half;      // slot (warp + 16 u): positions 2 slot, 2 slot + 1
+        kk[u] = j < n_old ? ld_ordered_u128(kb + j * stride) : zero4;
+        vv[u] = j < n_old ? ld_ordered_u128(vb + j * stride) : zero4;
     }
-    uint2 qraw = make_uint2(0u, 0u);
-    if (!fused) qraw = ld_ordered_u64(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 4 * lane);
+    uint4 qraw = zero4;
+    if (!fused) qraw = ld_ordered_u128(qkv + (int64_t)row * ld_qkv + (int64_t)head * D + 8 * dl);
     // Rotary angles of the new position: they depend on the position only, so they are made before the wait, one angle
     // per thread (an accurate sincosf is a hundred instructions; eight in a row in the sixteen front-end threads cost
     // 1.8 us) and handed over through shared memory.
@@ -227,61 +231,94 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
             }
         }
         __syncthreads();
-        qraw = *reinterpret_cast<const uint2 *>(qs + 4 * lane);
+        qraw = *reinterpret_cast<const uint4 *>(qs + 8 * dl);
     }
-    const float2 q01 = __half22float2(u32_as_half2(qraw.x)), q23 = __half22float2(u32_as_half2(qraw.y));
-    // ---- this warp's positions: running maximum m, sum l and weighted V sum a (dims 4*lane .. 4*lane+3) ----
-    float m = -1e30f, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    auto fold = [&](float s, bool valid, uint2 vraw) {       // one position into the running state
-        const float m_new = valid ? fmaxf(m, s) : m;
-        const float corr = __expf(m - m_new), p = valid ? __expf(s - m_new) : 0.f;
-        const float2 v01 = __half22float2(u32_as_half2(vraw.x)), v23 = __half22float2(u32_as_half2(vraw.y));
-        l = l * corr + p;
-        a0 = a0 * corr + p * v01.x, a1 = a1 * corr + p * v01.y, a2 = a2 * corr + p * v23.x, a3 = a3 * corr + p * v23.y;
-        m = m_new;
+    float q[8];
+    unpack8(qraw, q);
+    auto dot8 = [&](const uint4 &raw) {                       // this lane's eight dims of q . k
+        float k[8];
+        unpack8(raw, k);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d += q[i] * k[i];
+        return d;
     };
-    for (int j0 = warp; j0 < n_old || j0 == warp; j0 += kAttnUnroll * kAttnWarps) {
-        const int j_next = j0 + kAttnUnroll * kAttnWarps;       // this warp's first position of the next chunk
-        float s[kAttnUnroll];
+    auto half_sum = [](float v) {                             // sum over the sixteen lanes of a half-warp
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        return v;
+    };
+    // ---- this half-warp's positions: running maximum m, sum l and weighted V sum a (dims 8*dl .. 8*dl+7) ----
+    float m = -1e30f, l = 0.f, a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s0 = warp; 2 * s0 < n_old || s0 == warp; s0 += kAttnUnroll * kAttnWarps) {
+        const int s_next = s0 + kAttnUnroll * kAttnWarps;       // this warp's first slot of the next chunk
+        float sc[kAttnUnroll];
         float mc = -1e30f;
 #pragma unroll
         for (int u = 0; u < kAttnUnroll; ++u) {
-            const float2 k01 = __half22float2(u32_as_half2(kk[u].x)), k23 = __half22float2(u32_as_half2(kk[u].y));
-            s[u] = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale;
-            if (j0 + u * kAttnWarps < n_old) mc = fmaxf(mc, s[u]);
+            sc[u] = half_sum(dot8(kk[u])) * scale;
+            if (2 * (s0 + u * kAttnWarps) + half < n_old) mc = fmaxf(mc, sc[u]);
         }
-        if (j_next < n_old) {      // the K registers are free: the next chunk's K rows travel under this chunk's V pass
+        if (2 * s_next < n_old) {      // the K registers are free: the next chunk's K rows travel under this chunk's V pass
 #pragma unroll
             for (int u = 0; u < kAttnUnroll; ++u) {
-                const int j = j_next + u * kAttnWarps;
-                kk[u] = j < n_old ? ld_ordered_u64(kb + j * stride) : make_uint2(0u, 0u);
+                const int j = 2 * (s_next + u * kAttnWarps) + half;
+                kk[u] = j < n_old ? ld_ordered_u128(kb + j * stride) : zero4;
             }
         }
         // one rescale per chunk: the chunk's maximum first, then plain accumulation
         const float m_new = fmaxf(m, mc), corr = __expf(m - m_new);
-        l *= corr, a0 *= corr, a1 *= corr, a2 *= corr, a3 *= corr;
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] *= corr;
         m = m_new;
 #pragma unroll
         for (int u = 0; u < kAttnUnroll; ++u) {
-            const float p = (j0 + u * kAttnWarps < n_old) ? __expf(s[u] - m) : 0.f;
-            const float2 v01 = __half22float2(u32_as_half2(vv[u].x)), v23 = __half22float2(u32_as_half2(vv[u].y));
+            const float p = (2 * (s0 + u * kAttnWarps) + half < n_old) ? __expf(sc[u] - m) : 0.f;
+            float v[8];
+            unpack8(vv[u], v);
             l += p;
-            a0 += p * v01.x, a1 += p * v01.y, a2 += p * v23.x, a3 += p * v23.y;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] += p * v[i];
         }
-        if (j_next < n_old) {      // and its V rows under the next chunk's scores
+        if (2 * s_next < n_old) {      // and its V rows under the next chunk's scores
 #pragma unroll
             for (int u = 0; u < kAttnUnroll; ++u) {
-                const int j = j_next + u * kAttnWarps;
-                vv[u] = j < n_old ? ld_ordered_u64(vb + j * stride) : make_uint2(0u, 0u);
+                const int j = 2 * (s_next + u * kAttnWarps) + half;
+                vv[u] = j < n_old ? ld_ordered_u128(vb + j * stride) : zero4;
             }
         }
     }
-    if (fused && warp == 0) {      // the position made above, from shared memory
-        const uint2 kr = *reinterpret_cast<const uint2 *>(ks + 4 * lane), vr = *reinterpret_cast<const uint2 *>(vs + 4 * lane);
-        const float2 k01 = __half22float2(u32_as_half2(kr.x)), k23 = __half22float2(u32_as_half2(kr.y));
-        fold(warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale, true, vr);
+    if (fused && warp == 0) {      // the position made above, from shared memory: the first half-warp folds it in
+        const uint4 kr = *reinterpret_cast<const uint4 *>(ks + 8 * dl), vr = *reinterpret_cast<const uint4 *>(vs + 8 * dl);
+        const float sn = half_sum(dot8(kr)) * scale;           // all lanes take part in the shuffles
+        if (half == 0) {
+            const float m_new = fmaxf(m, sn), corr = __expf(m - m_new), p = __expf(sn - m_new);
+            float v[8];
+            unpack8(vr, v);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = a[i] * corr + p * v[i];
+            m = m_new;
+        }
     }
-    *reinterpret_cast<float4 *>(&part[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+    {
+        // the two half-warps' states into one (an empty half has m = -1e30 and l = 0: its weight underflows to zero)
+        const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m, 16);
+        const float m_w = fmaxf(m, m_o), c = __expf(m - m_w);
+        l *= c;
+        l += __shfl_xor_sync(0xFFFFFFFFu, l, 16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a[i] *= c;
+            a[i] += __shfl_xor_sync(0xFFFFFFFFu, a[i], 16);
+        }
+        m = m_w;
+    }
+    if (half == 0) {
+        *reinterpret_cast<float4 *>(&part[warp][8 * dl]) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4 *>(&part[warp][8 * dl + 4]) = make_float4(a[4], a[5], a[6], a[7]);
+    }
     if (lane == 0) pm[warp] = m, pl[warp] = l;
     __syncthreads();
     if (t < D) {
@@ -493,7 +530,9 @@ extern "C" int rptc_attn_decode(const void *qkv, int64_t ld_qkv, const int32_t *
     if (!qkv || !pos || !kcache || !vcache || !out) return RPTC_ERR_ARG;
     if (d != 128) return RPTC_ERR_UNSUPPORTED;
     if (rows <= 0 || hq <= 0 || hkv <= 0 || (hq % hkv) || max_pos <= 0 || max_pos > 32768) return RPTC_ERR_SHAPE;
-    if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(kcache) & 7) || (ld_qkv & 3)) return RPTC_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
+        (ld_qkv & 7))
+        return RPTC_ERR_ALIGN;      // rows of q, k and v are read sixteen bytes at a time
     if (int e = rptc_check_device()) return e;
     unsigned int *status = device_status_word();
     if (!status) return RPTC_ERR_CUDA;
