@@ -45,7 +45,7 @@ __device__ __forceinline__ void ld_pair_sys(const uint64_t *p, uint64_t &a, uint
 }
 
 __global__ void __launch_bounds__(512) peer_finish_kernel(const PeerFinishParams p) {
-    __shared__ float ex[4096];
+    __shared__ __align__(16) float ex[4096];
     __shared__ int timed_out;
     pdl_allow_next_grid();
     pdl_wait_prior_grids();

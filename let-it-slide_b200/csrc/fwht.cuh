@@ -94,8 +94,11 @@ __device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex, bool 
         // transforms them in registers, and puts them back (two barriers instead of one per stride).
         const int G = block >> 8;                      // 2, 4, 8 or 16
         if (guard) __syncthreads();          // the buffer may still be read from an earlier transform
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ex[8 * t + i] = v[i];
+        // a thread's eight values as two 16-byte accesses (`ex` is 16-byte aligned): scalar accesses 32 bytes apart
+        // would meet in the same banks eight at a time
+        float4 *ex4 = reinterpret_cast<float4 *>(ex) + 2 * t;
+        ex4[0] = make_float4(v[0], v[1], v[2], v[3]);
+        ex4[1] = make_float4(v[4], v[5], v[6], v[7]);
         __syncthreads();
         const int n_items = (int)blockDim.x * 8 / G;       // (block index, r) pairs in the chunk
         for (int item = t; item < n_items; item += blockDim.x) {
@@ -122,8 +125,8 @@ __device__ __forceinline__ void fwht8(float (&v)[8], int block, float *ex, bool 
                 if (g < G) base[256 * g] = z[g];
         }
         __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = ex[8 * t + i];
+        const float4 lo = ex4[0], hi = ex4[1];
+        v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
     }
 }
 

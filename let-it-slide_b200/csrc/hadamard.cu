@@ -25,7 +25,7 @@ struct HadParams {
 };
 
 __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
-    __shared__ float ex[4096];
+    __shared__ __align__(16) float ex[4096];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     const int t = threadIdx.x;
@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const HadParams p) {
 }
 
 __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams p) {
-    __shared__ float ex[4096];
+    __shared__ __align__(16) float ex[4096];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     const int64_t row = blockIdx.y;
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(512) swiglu_hadamard_kernel(const SwigluParams
 
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) finish_norm_hadamard_kernel(const FinishNormParams p) {
-    __shared__ float ex[8 * THREADS];
+    __shared__ __align__(16) float ex[8 * THREADS];
     __shared__ float red[36];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
@@ -97,7 +97,7 @@ struct QkvFinishParams {
 };
 
 __global__ void __launch_bounds__(512) qkv_finish_kernel(const QkvFinishParams p) {
-    __shared__ float ex[4096];
+    __shared__ __align__(16) float ex[4096];
     pdl_allow_next_grid();
     pdl_wait_prior_grids();
     const int t = threadIdx.x;
