@@ -173,7 +173,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
     // per thread (an accurate sincosf is a hundred instructions; eight in a row in the sixteen front-end threads cost
     // 1.8 us) and handed over through shared memory.
     uint4 so_raw = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
-    const float si_mine = (signs_in && t < D) ? __half2float(signs_in[head * D + t]) : 1.f;      // constants: fetched early
+    // constants: fetched early, as raw bits -- a conversion here would stall the thread until the load (and the sixteen
+    // cache loads queued in front of it) has come back, and with it the dependency wait and everything behind it
+    const unsigned short si_raw = (signs_in && t < D) ? __ldg(reinterpret_cast<const unsigned short *>(signs_in) + head * D + t) : (unsigned short)0x3C00;
     if (fused && warp < 2) {
         const int i8 = (t & 15) * 8;
         const int grp0 = t >> 4;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const __half 
         if (signs_in) {
             // input-side transform of the output projection, one 128-wide Hadamard block per head:
             // o <- H_128(s * o) / sqrt(128); thread t holds element t (threads 0..127 = warps 0..3)
-            o *= si_mine;
+            o *= __half2float(__ushort_as_half(si_raw));
 #pragma unroll
             for (int mm = 1; mm < 32; mm <<= 1) {
                 const float other = __shfl_xor_sync(0xFFFFFFFFu, o, mm);
