@@ -139,6 +139,16 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+// 16 bytes from shared memory into `v` where `take` is set; elsewhere `v` keeps what it held.  One predicated load,
+// no branch (a conditional around a volatile load is compiled as a branch with its reconvergence bookkeeping).
+__device__ __forceinline__ void lds128_if(uint4 &v, uint32_t addr, bool take) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %5, 0;\n\t"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "r"(addr), "r"((uint32_t)take));
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));

@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_rows_kernel(const GemvPa
 #pragma unroll
             for (int pi = 0; pi < PAIRS; pi += 4) {
                 // only the four (eight) lanes whose column of B is in use read activations; the others hold zeros
-                if (feeds_x) xv = lds128(xu + 4u * pi);
+                lds128_if(xv, xu + 4u * pi, feeds_x);
                 uint32_t wa[4], wb[4];
                 decode_quad_bits<CODE, K>(Ra, lut, pi, wa);
                 decode_quad_bits<CODE, K>(Rb, lut, pi, wb);
